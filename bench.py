@@ -1,0 +1,289 @@
+#!/usr/bin/env python
+"""Benchmark of the fused Leech-lattice dequant-GEMV on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+Workload (`config.workload` = "qwen3-4b-layer-gemv"): BASELINE config 1 — the seven
+projections of a Qwen3-4B layer (q 4096x2560, k/v 1024x2560, o 2560x4096, gate/up
+9728x2560, down 2560x9728) at batch 1 with f16 activations, on seeded synthetic
+codes. One step = one pass over the seven projections of L distinct layers
+(default 36 = every projection of the model once, 252 GEMVs, 904 MB of codes), so
+every step streams far more than the 126 MB L2 and no matrix is re-read warm.
+
+Reported: `value` = algorithmic GB/s (codes + f32 tails + f64 row scales + x + y
+bytes over the device time of the pass, inputs resident in HBM); `e2e` = the same
+metric through the host-buffer C ABI call (x copied in from pinned host memory and
+y copied back inside the timed region, per GEMV); `roofline` for the GEMV kernel;
+`cpu_baseline` = the CPU oracle (the C++ restatement of the reference's Rust path)
+timed on this box's host cores on a bounded sample. `--impl reference` times that
+CPU path alone, as the reference arm.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = "qwen3-4b"
+PROJS = ["q", "k", "v", "o", "gate", "up", "down"]
+CONFIG_ID = 1
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured", float(d.get("sm_max_mhz", 1965.0))
+    return 6650.0, "fallback", 1965.0
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def algorithmic_bytes(mats, x_bytes, y_bytes):
+    """codes + f32 tail + f64 row scales + x + y, per GEMV, summed."""
+    return sum(m.codes.size + m.tail.size * 4 + m.d_out * 8 + m.d_in * x_bytes + m.d_out * y_bytes for m in mats)
+
+
+def cpu_pass(ref, mats, xs, threads):
+    t0 = time.perf_counter()
+    for m, x in zip(mats, xs):
+        ref.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales, m.tail, x, threads=threads)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(layers_sample=1, min_seconds=6.0, max_seconds=30.0):
+    """The oracle's decode + scale + dot on all host threads, over the seven projections of
+    `layers_sample` layers, repeated until min_seconds have passed."""
+    from oracle import ref
+    from llvq_b200 import synth
+    threads = ref.hw_threads()
+    mats = [m for l in range(layers_sample) for m in synth.make_layer(MODEL, CONFIG_ID, l).values()]
+    xs = [synth.make_activation(m.d_in, 0x1000 + i, np.float16).astype(np.float64) for i, m in enumerate(mats)]
+    nbytes = algorithmic_bytes(mats, 2, 2)
+    cpu_pass(ref, mats[:1], xs[:1], threads)  # builds the tables
+    times, t_start = [], time.perf_counter()
+    while (time.perf_counter() - t_start < min_seconds or len(times) < 2) and time.perf_counter() - t_start < max_seconds:
+        times.append(cpu_pass(ref, mats, xs, threads))
+    t = statistics.median(times)
+    blocks = sum(m.n_blocks for m in mats)
+    return {"value": nbytes / t / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{layers_sample} layer(s) x 7 projections = {blocks} blocks, median of {len(times)} passes",
+            "ns_per_block_per_core": t * threads / blocks * 1e9, "ms_per_pass": t * 1e3}, nbytes
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU path (oracle port) on the host cores; rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    times = []
+    from oracle import ref
+    from llvq_b200 import synth
+    threads = ref.hw_threads()
+    mats = list(synth.make_layer(MODEL, CONFIG_ID, 0).values())
+    xs = [synth.make_activation(m.d_in, 0x1000 + i, np.float16).astype(np.float64) for i, m in enumerate(mats)]
+    nbytes = algorithmic_bytes(mats, 2, 2)
+    for _ in range(args.warmup):
+        cpu_pass(ref, mats, xs, threads)
+    for _ in range(args.steps):
+        times.append(cpu_pass(ref, mats, xs, threads))
+    t = sum(times) / len(times)
+    val = nbytes / t / 1e9
+    sample = "each step = the 7 projections of one layer (4 185 600 blocks) on all host threads"
+    print(json.dumps({
+        "impl": "reference", "metric": "dequant_gemv_algorithmic_GBps", "value": val, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "qwen3-4b-layer-gemv", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=36, help="distinct layers per step")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from llvq_b200 import FusedRuntime, _lib, synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the measured path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    rt = FusedRuntime(local_rank)
+    lib = _lib.load()
+
+    # Weak scaling: every rank holds its own `layers` distinct layers (no data-path collective;
+    # the projections of different layers are independent units).
+    t_gen = time.perf_counter()
+    projs, xs_host, mats_meta = [], [], []
+    for l in range(args.layers):
+        layer = synth.make_layer(MODEL, CONFIG_ID, rank * 1000 + l)
+        for name in PROJS:
+            m = layer[name]
+            projs.append(rt.upload(m, tail_f16=True))
+            mats_meta.append((m.codes.size, m.tail.size, m.d_out, m.d_in))
+            xs_host.append(torch.from_numpy(synth.make_activation(m.d_in, 0x2000 + len(xs_host), np.float16)).pin_memory())
+    gen_s = time.perf_counter() - t_gen
+    xs_dev = [x.cuda() for x in xs_host]
+    ys_dev = [torch.empty(p.d_out, dtype=torch.float16, device="cuda") for p in projs]
+    ys_host = [torch.empty(p.d_out, dtype=torch.float16).pin_memory() for p in projs]
+    step_bytes = sum(c + t * 4 + do * 8 + di * 2 + do * 2 for c, t, do, di in mats_meta)
+    step_blocks = sum(p.n_blocks for p in projs)
+    codes_bytes = sum(c for c, _, _, _ in mats_meta)
+
+    def step_device():
+        for p, x, y in zip(projs, xs_dev, ys_dev):
+            rt.forward(p, x, out=y)
+
+    def step_e2e():
+        for p, x, y in zip(projs, xs_host, ys_host):
+            rt.forward_host(p, x.numpy(), y.numpy())
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.llvq_launch_count()
+    ms_total = timed(step_device, args.steps)
+    launches = lib.llvq_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    assert not rt.poll_range_error(), "a synthetic index fell outside the ball"
+
+    for _ in range(2):
+        step_e2e()
+    e2e_steps = max(1, min(args.steps, 5))
+    ms_e2e = timed(step_e2e, e2e_steps)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    ms_step = ms_total / args.steps
+    value = world * step_bytes / (ms_step * 1e-3) / 1e9
+    e2e_value = world * step_bytes / (ms_e2e / e2e_steps * 1e-3) / 1e9
+    peak, peak_kind, sm_max = measured_peaks()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    per_gpu_gbs = step_bytes / (ms_step * 1e-3) / 1e9
+    # Two-term roofline of the path: T_roof = max(T_bytes, T_alu) with the agreed algorithmic
+    # decode work of 184 lane-operations per block on SMs x 128 lanes at the max SM clock.
+    t_bytes = step_bytes / (peak * 1e9)
+    t_alu = step_blocks * 184.0 / (sms * 128 * sm_max * 1e6)
+    out = {
+        "metric": "dequant_gemv_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "qwen3-4b-layer-gemv", "layers_per_step": args.layers, "gemvs_per_step": len(projs),
+                   "blocks_per_step": step_blocks, "algorithmic_bytes_per_step": step_bytes, "activations": "f16",
+                   "l2": "every step streams %.0f MB of distinct codes (> 126 MB L2)" % (codes_bytes / 1e6),
+                   "parallelism": f"replicas x{world}" if world > 1 else "single"},
+        "token_equiv_per_s": world * (args.layers / 36.0) / (ms_step * 1e-3),
+        "gblocks_per_s": world * step_blocks / (ms_step * 1e-3) / 1e9,
+        "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
+                     "traffic": None, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBps": per_gpu_gbs / 8000.0,
+                     "kernel": "gemv", "launches": launches, "avg_launch_us": ms_total * 1e3 / max(launches, 1),
+                     "two_term": {"t_bytes_ms": t_bytes * 1e3, "t_alu_ms": t_alu * 1e3,
+                                  "frac": max(t_bytes, t_alu) * 1e3 / ms_step, "ops_per_block": 184}},
+        "e2e": {"value": e2e_value, "unit": "GB/s",
+                "h2d_bytes_per_step": sum(di * 2 for _, _, _, di in mats_meta),
+                "d2h_bytes_per_step": sum(do * 2 for _, _, do, _ in mats_meta), "ms_per_step": ms_e2e / e2e_steps},
+        "gpu_launches": int(launches), "clocks": clocks, "setup_s": gen_s,
+    }
+    if not args.no_cpu_baseline:
+        cb, _ = cpu_baseline()
+        out["cpu_baseline"] = cb
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

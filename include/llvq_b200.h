@@ -1,0 +1,182 @@
+/*
+ * llvq_b200 — C ABI of the B200 (sm_100a) fused Leech-lattice dequant-GEMV.
+ *
+ * A projection stays in HBM exactly as the `.llvq` archive stores it: one 48-bit
+ * big-endian record per 24-weight block (47-bit index into the ball
+ * Lambda24(12) u {0}, then 1 gain bit), row-major d_out x (d_in / 24), plus one
+ * row scale per row, two gain centroids and d_in % 24 un-quantised tail columns.
+ * The kernels decode every index in registers, bit-exactly as the reference's CPU
+ * decoder does, and never materialise dense weights.
+ *
+ * Conventions shared by every entry point
+ *   - returns LLVQ_OK (0) or a negative llvq_status; the message of the last
+ *     failure on the calling thread is llvq_last_error(). Nothing aborts.
+ *   - "dev" pointers are device memory of the runtime's GPU, "host" pointers are
+ *     ordinary host memory. Output buffers are caller-allocated and may be
+ *     uninitialised: every element is stored, never accumulated into.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream). Calls only enqueue work; they do not synchronise unless stated.
+ *   - one host thread drives one runtime at a time (the reference launches from
+ *     a single thread on a single stream, llvq-cuda/src/gpu.rs:243-272).
+ *
+ * Each declaration names the reference interface it stands in for (path:line in
+ * pjmalandrino/llvq).
+ */
+#ifndef LLVQ_B200_H
+#define LLVQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum llvq_status {
+    LLVQ_OK = 0,
+    LLVQ_ERR_INVALID = -1,     /* bad argument: null pointer, size, alignment, shell cap */
+    LLVQ_ERR_CUDA = -2,        /* a CUDA runtime call failed; see llvq_last_error() */
+    LLVQ_ERR_CODEBOOK = -3,    /* device tables do not reproduce the published codebook */
+    LLVQ_ERR_RANGE = -4,       /* an index in the code stream lies outside the ball */
+    LLVQ_ERR_UNSUPPORTED = -5  /* valid request this build does not serve */
+} llvq_status;
+
+typedef struct llvq_runtime llvq_runtime; /* per-GPU tables; FusedRuntime, llvq-llm/src/fused_cuda.rs:145 */
+typedef struct llvq_matrix llvq_matrix;   /* one resident projection; FusedProj, llvq-llm/src/fused_cuda.rs:119 */
+typedef void* llvq_stream_t;              /* cudaStream_t */
+
+/* Published fingerprint of the v1 index map
+ * (llvq-artifact/tests/codebook_fingerprint.rs:58). */
+#define LLVQ_PUBLISHED_FINGERPRINT 0x338f420f11866319ull
+
+/* Tail storage on the device. The reference's inference path narrows the tail
+ * to binary16 once on the host (llvq-llm/src/fused.rs:655-659); its bench path
+ * keeps f32 (llvq-cuda/kernels/matvec.cu:139-142). */
+enum { LLVQ_TAIL_F32 = 0, LLVQ_TAIL_F16 = 1 };
+
+/* One quantised matrix as the archive holds it: RawMatrix,
+ * llvq-artifact/src/format.rs:215-229 (record layout format.rs:148-205). All
+ * pointers are host memory and are copied; the caller keeps ownership. */
+typedef struct llvq_matrix_desc {
+    int32_t d_out;            /* rows */
+    int32_t d_in;             /* columns; d_in / 24 blocks + d_in % 24 tail columns */
+    int32_t shell_cap;        /* must be 12 (47-bit index); anything else is LLVQ_ERR_UNSUPPORTED */
+    int32_t tail_mode;        /* LLVQ_TAIL_F32 or LLVQ_TAIL_F16 */
+    const uint8_t* codes;     /* d_out * (d_in / 24) * 6 bytes, archive order, MSB-first */
+    const double* centroids;  /* exactly 2 (one gain bit), ascending */
+    const double* row_scales; /* d_out */
+    const float* tail;        /* d_out * (d_in % 24), row-major; may be NULL when d_in % 24 == 0 */
+} llvq_matrix_desc;
+
+/* Message of the last failure on this thread ("" when none). Mirrors the
+ * Result<_, String> every reference entry returns (llvq-llm/src/fused_cuda.rs:770-787). */
+const char* llvq_last_error(void);
+
+/* Library version, "major.minor.patch". */
+const char* llvq_version(void);
+
+/* ---- runtime ------------------------------------------------------------- */
+
+/* Build the Golay, class and unranking tables on `device` and verify them
+ * against LLVQ_PUBLISHED_FINGERPRINT by decoding the fingerprint's probe indices
+ * on the GPU. Replaces FusedRuntime::new (llvq-llm/src/fused_cuda.rs:182-347)
+ * minus its NVRTC step, and the header check of read_header
+ * (llvq-artifact/src/format.rs:588-619). Synchronises. */
+int llvq_runtime_create(int device, llvq_runtime** out);
+void llvq_runtime_destroy(llvq_runtime* rt);
+
+/* Fingerprint of the index map the device tables implement
+ * (codebook_fingerprint, llvq-artifact/src/codebook.rs:129-185). */
+int llvq_codebook_fingerprint(llvq_runtime* rt, uint64_t* out);
+
+/* Class count and ball size of the cap-`shell_cap` codebook (12 or 13):
+ * enumerate_classes / index_bits, llvq-search/src/classes.rs:144,
+ * llvq-quant/src/quantizer.rs:572-576. */
+int llvq_codebook_info(llvq_runtime* rt, int shell_cap, int32_t* n_classes, uint64_t* ball_size);
+
+/* Host-only views of the index map, usable without a GPU. `ci` runs over the 383
+ * classes in format order (the first 301 make the cap-12 ball); `out` receives
+ * the 64-byte record the device decoders read (struct DevClass of
+ * llvq_b200/csrc/codebook.h), the counterpart of CascadeClass,
+ * llvq-search/src/fastdec.rs:89-133. llvq_codebook_golay copies the 4096
+ * codewords in format order (Golay::codewords, llvq-core/src/golay.rs:99). */
+int llvq_codebook_class_record(int32_t ci, void* out);
+int llvq_codebook_golay(uint32_t* out);
+
+/* Reads and clears the runtime's sticky range flag: *flag is 1 when any kernel
+ * since the last poll met an index outside the ball (the reference surfaces this
+ * as Error::IndexOutOfRange at load, llvq-artifact/src/format.rs:389-392).
+ * Synchronises the device. */
+int llvq_runtime_poll_error(llvq_runtime* rt, int32_t* flag);
+
+/* ---- matrices ------------------------------------------------------------ */
+
+/* Copy one matrix to the GPU as stored (no transcode): upload_matrix,
+ * llvq-llm/src/fused_cuda.rs:1058-1144. Synchronises. */
+int llvq_matrix_upload(llvq_runtime* rt, const llvq_matrix_desc* desc, llvq_matrix** out);
+
+/* Row-concatenate `n` matrices that share d_in (q|k|v or gate|up) into one
+ * resident object served by one launch; every segment keeps its own centroid
+ * pair. Same idea as tv_planes_seg, llvq-cuda/kernels/planes_seg.cu:65-133. */
+int llvq_matrix_upload_group(llvq_runtime* rt, const llvq_matrix_desc* descs, int32_t n, llvq_matrix** out);
+
+void llvq_matrix_free(llvq_matrix* m);
+int llvq_matrix_dims(const llvq_matrix* m, int32_t* d_out, int32_t* d_in);
+
+/* Bytes one GEMV must move at minimum: codes + tail + row scales (as stored in
+ * the archive: f64) + x + y. Used by the benchmark's roofline. */
+int llvq_matrix_algorithmic_bytes(const llvq_matrix* m, int32_t x_elem_bytes, int32_t y_elem_bytes, uint64_t* out);
+
+/* ---- fused dequant-GEMV, device buffers ----------------------------------- */
+
+/* y[d_out] = W x, f32 activation, f32 result: tv_slot / tv_planes,
+ * llvq-cuda/kernels/matvec.cu:102, llvq-cuda/kernels/planes.cu:27. */
+int llvq_gemv_f32(llvq_matrix* m, const float* x_dev, float* y_dev, llvq_stream_t stream);
+
+/* f16 activation, f16 result (activations of the f16 model path). x_dev and
+ * y_dev are IEEE binary16 passed as uint16_t. */
+int llvq_gemv_h(llvq_matrix* m, const uint16_t* x_dev, uint16_t* y_dev, llvq_stream_t stream);
+
+/* f32 (rotated) activation, f16 result: the exact signature of tv_planes_h,
+ * llvq-llm/kernels/tv_planes_h.cu:38-72, which FusedRuntime::forward_rotated
+ * launches (llvq-llm/src/fused_cuda.rs:384-402). */
+int llvq_gemv_f32x_h(llvq_matrix* m, const float* x_dev, uint16_t* y_dev, llvq_stream_t stream);
+
+/* ---- batched dequant-GEMM -------------------------------------------------- */
+
+/* Y[B, d_out] = X[B, d_in] W^T for a batch of B activations (row-major, f16 in,
+ * f16 out). The reference serves a batch as B serial matvec launches
+ * (group_forward / drive_rows, llvq-llm/src/model.rs:497-536); here every code
+ * is decoded once per batch. */
+int llvq_gemm_h(llvq_matrix* m, const uint16_t* x_dev, uint16_t* y_dev, int32_t batch, llvq_stream_t stream);
+
+/* ---- host-buffer convenience (what a plugin holding host tensors calls) ---- */
+
+/* Same as llvq_gemv_f32 / llvq_gemv_h but x and y are host memory: the call
+ * copies x in, launches, copies y out and synchronises the stream. */
+int llvq_gemv_f32_host(llvq_matrix* m, const float* x_host, float* y_host, llvq_stream_t stream);
+int llvq_gemv_h_host(llvq_matrix* m, const uint16_t* x_host, uint16_t* y_host, llvq_stream_t stream);
+
+/* ---- decode probes --------------------------------------------------------- */
+
+/* Decode n packed 6-byte records on the GPU to their lattice points: 24 int8
+ * per block, the shell m (||p||^2 = 16 m; 0 for the origin, 255 for an index
+ * outside the ball) and the gain bit. The integer dump the reference's
+ * preflight uses to diff a kernel against the Rust decoder
+ * (llvq-cuda/kernels/preflight.cu:28-60). All pointers are device memory. */
+int llvq_decode_blocks(llvq_runtime* rt, const uint8_t* codes_dev, size_t n, int8_t* points_dev,
+                       uint8_t* shell_dev, uint8_t* gain_dev, llvq_stream_t stream);
+
+/* Decode n raw indices (up to the cap-13 ball, 48 bits) on the GPU:
+ * Indexer::decode, llvq-search/src/index.rs:334-435. shell_dev as above. */
+int llvq_decode_indices(llvq_runtime* rt, const uint64_t* idx_dev, size_t n, int8_t* points_dev,
+                        uint8_t* shell_dev, llvq_stream_t stream);
+
+/* Number of kernels this library has launched on the calling process so far
+ * (all runtimes). The benchmark reports the difference across its timed region. */
+uint64_t llvq_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLVQ_B200_H */

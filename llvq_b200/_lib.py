@@ -1,0 +1,77 @@
+"""ctypes binding of libllvq_b200.so — the same declarations as include/llvq_b200.h."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import _build
+
+OK = 0
+ERR_INVALID, ERR_CUDA, ERR_CODEBOOK, ERR_RANGE, ERR_UNSUPPORTED = -1, -2, -3, -4, -5
+TAIL_F32, TAIL_F16 = 0, 1
+PUBLISHED_FINGERPRINT = 0x338F420F11866319
+
+
+class MatrixDesc(C.Structure):
+    """llvq_matrix_desc of include/llvq_b200.h."""
+    _fields_ = [
+        ("d_out", C.c_int32), ("d_in", C.c_int32), ("shell_cap", C.c_int32), ("tail_mode", C.c_int32),
+        ("codes", C.c_void_p), ("centroids", C.c_void_p), ("row_scales", C.c_void_p), ("tail", C.c_void_p),
+    ]
+
+
+class LlvqError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"llvq status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+_SIGNATURES = {
+    "llvq_last_error": (C.c_char_p, []),
+    "llvq_version": (C.c_char_p, []),
+    "llvq_launch_count": (C.c_uint64, []),
+    "llvq_runtime_create": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
+    "llvq_runtime_destroy": (None, [C.c_void_p]),
+    "llvq_runtime_poll_error": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
+    "llvq_codebook_fingerprint": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
+    "llvq_codebook_info": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_uint64)]),
+    "llvq_codebook_class_record": (C.c_int, [C.c_int32, C.c_void_p]),
+    "llvq_codebook_golay": (C.c_int, [C.c_void_p]),
+    "llvq_matrix_upload": (C.c_int, [C.c_void_p, C.POINTER(MatrixDesc), C.POINTER(C.c_void_p)]),
+    "llvq_matrix_upload_group": (C.c_int, [C.c_void_p, C.POINTER(MatrixDesc), C.c_int32, C.POINTER(C.c_void_p)]),
+    "llvq_matrix_free": (None, [C.c_void_p]),
+    "llvq_matrix_dims": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "llvq_matrix_algorithmic_bytes": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_uint64)]),
+    "llvq_gemv_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llvq_gemv_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llvq_gemv_f32x_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llvq_gemm_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
+    "llvq_gemv_f32_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llvq_gemv_h_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llvq_decode_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llvq_decode_indices": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
+}
+
+_lib = None
+
+
+def load(build: bool = True) -> C.CDLL:
+    """Load the library (building it first when asked and stale). Fails loudly when it is missing."""
+    global _lib
+    if _lib is None:
+        path = _build.build() if build else _build.LIB
+        if not os.path.exists(path):
+            raise RuntimeError(f"{path} is missing: the CUDA library was not built; there is no fallback")
+        L = C.CDLL(path)
+        for name, (res, args) in _SIGNATURES.items():
+            f = getattr(L, name)
+            f.restype = res
+            f.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise LlvqError(status, load().llvq_last_error().decode())

@@ -1,0 +1,456 @@
+// C ABI of llvq_b200 (see include/llvq_b200.h). Host-side objects own the device
+// buffers; every entry point validates its arguments, records a message on
+// failure and returns a status instead of aborting.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/llvq_b200.h"
+#include "codebook.h"
+#include "kernels_generic.cuh"
+
+using namespace llvq;
+
+namespace {
+
+thread_local std::string g_error;
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_error = buf;
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                          \
+    do {                                                                                        \
+        cudaError_t e_ = (expr);                                                                \
+        if (e_ != cudaSuccess)                                                                  \
+            return fail(LLVQ_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), \
+                        __FILE__, __LINE__);                                                    \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        cudaGetDevice(&cur);
+        if (prev >= 0 && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+constexpr int kLutShift = 35;
+
+}  // namespace
+
+struct llvq_runtime {
+    int device = 0;
+    Codebook cb;
+    DevTables T{};
+    void* d_cls = nullptr;
+    void* d_ends = nullptr;
+    void* d_lut = nullptr;
+    void* d_golay = nullptr;
+    int* d_err = nullptr;  // sticky "index outside the ball" flag written by kernels
+    uint64_t fingerprint = 0;
+    int max_smem_optin = 0;
+};
+
+struct llvq_matrix {
+    llvq_runtime* rt = nullptr;
+    int d_out = 0, d_in = 0, nb = 0, tail_w = 0, tail_mode = 0;
+    unsigned char* codes = nullptr;
+    float2* cent = nullptr;
+    float* rscale = nullptr;
+    void* tail = nullptr;
+    size_t codes_bytes = 0;
+    // staging for the host-buffer entry points
+    void* x_stage = nullptr;
+    void* y_stage = nullptr;
+    MatrixView view() const {
+        MatrixView v;
+        v.codes = codes;
+        v.cent = cent;
+        v.rscale = rscale;
+        v.tail = tail;
+        v.d_out = d_out;
+        v.d_in = d_in;
+        v.nb = nb;
+        v.tail_w = tail_w;
+        v.tail_f16 = tail_mode == LLVQ_TAIL_F16;
+        return v;
+    }
+};
+
+namespace {
+
+size_t generic_smem_bytes(int nb) { return ((size_t)kDim * nb + 32 + (size_t)kGenRows * nb) * sizeof(float); }
+
+template <typename XT, typename YT>
+int launch_gemv_generic(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
+    llvq_runtime* rt = m->rt;
+    const size_t smem = generic_smem_bytes(m->nb);
+    if (smem > (size_t)rt->max_smem_optin)
+        return fail(LLVQ_ERR_UNSUPPORTED, "d_in %d needs %zu bytes of shared memory (limit %d)", m->d_in, smem,
+                    rt->max_smem_optin);
+    auto kern = gemv_generic_kernel<XT, YT>;
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int grid = (m->d_out + kGenRows - 1) / kGenRows;
+    kern<<<grid, kGenThreads, smem, s>>>(rt->T, m->view(), x, y, kN12, rt->d_err);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+template <typename XT, typename YT>
+int gemv_entry(llvq_matrix* m, const XT* x, YT* y, llvq_stream_t stream) {
+    if (!m || !x || !y) return fail(LLVQ_ERR_INVALID, "gemv: null argument");
+    if (((uintptr_t)x % sizeof(XT)) || ((uintptr_t)y % sizeof(YT))) return fail(LLVQ_ERR_INVALID, "gemv: misaligned buffer");
+    DeviceGuard g(m->rt->device);
+    return launch_gemv_generic<XT, YT>(m, x, y, (cudaStream_t)stream);
+}
+
+int check_desc(const llvq_matrix_desc& d) {
+    if (d.d_out <= 0 || d.d_in <= 0) return fail(LLVQ_ERR_INVALID, "matrix: d_out %d, d_in %d", d.d_out, d.d_in);
+    if (d.shell_cap != 12)
+        return fail(LLVQ_ERR_UNSUPPORTED, "matrix: shell cap %d; only the 47-bit cap-12 ball is served", d.shell_cap);
+    if (d.tail_mode != LLVQ_TAIL_F32 && d.tail_mode != LLVQ_TAIL_F16) return fail(LLVQ_ERR_INVALID, "matrix: tail_mode %d", d.tail_mode);
+    if (!d.centroids || !d.row_scales) return fail(LLVQ_ERR_INVALID, "matrix: null centroids or row scales");
+    if (d.d_in / kDim > 0 && !d.codes) return fail(LLVQ_ERR_INVALID, "matrix: null code stream");
+    if (d.d_in % kDim > 0 && !d.tail) return fail(LLVQ_ERR_INVALID, "matrix: null tail with %d tail columns", d.d_in % kDim);
+    return LLVQ_OK;
+}
+
+void free_matrix_buffers(llvq_matrix* m) {
+    cudaFree(m->codes);
+    cudaFree(m->cent);
+    cudaFree(m->rscale);
+    cudaFree(m->tail);
+    cudaFree(m->x_stage);
+    cudaFree(m->y_stage);
+}
+
+int upload_impl(llvq_runtime* rt, const llvq_matrix_desc* descs, int n, llvq_matrix** out) {
+    if (!rt || !descs || !out || n <= 0) return fail(LLVQ_ERR_INVALID, "upload: null argument");
+    long long d_out = 0;
+    for (int i = 0; i < n; ++i) {
+        int st = check_desc(descs[i]);
+        if (st) return st;
+        if (descs[i].d_in != descs[0].d_in || descs[i].tail_mode != descs[0].tail_mode)
+            return fail(LLVQ_ERR_INVALID, "upload_group: segment %d differs in d_in or tail_mode", i);
+        d_out += descs[i].d_out;
+    }
+    if (d_out > (1ll << 30)) return fail(LLVQ_ERR_INVALID, "upload: %lld rows", d_out);
+    DeviceGuard g(rt->device);
+    std::unique_ptr<llvq_matrix> m(new llvq_matrix);
+    m->rt = rt;
+    m->d_out = (int)d_out;
+    m->d_in = descs[0].d_in;
+    m->nb = m->d_in / kDim;
+    m->tail_w = m->d_in % kDim;
+    m->tail_mode = descs[0].tail_mode;
+    m->codes_bytes = (size_t)m->d_out * m->nb * 6;
+
+    // Host staging: concatenate the segments row-wise; narrow scales to f32 with one
+    // rounding (llvq-llm/src/fused.rs:1210-1212) and the tail to binary16 when asked
+    // (fused.rs:655-659).
+    std::vector<unsigned char> codes(m->codes_bytes + 64, 0);
+    std::vector<float2> cent((size_t)m->d_out);
+    std::vector<float> rs((size_t)m->d_out);
+    std::vector<float> tail32((size_t)m->d_out * m->tail_w);
+    size_t row = 0;
+    for (int i = 0; i < n; ++i) {
+        const llvq_matrix_desc& d = descs[i];
+        std::memcpy(codes.data() + row * m->nb * 6, d.codes ? d.codes : codes.data(), (size_t)d.d_out * m->nb * 6);
+        for (int r = 0; r < d.d_out; ++r) {
+            cent[row + r] = make_float2((float)d.centroids[0], (float)d.centroids[1]);
+            rs[row + r] = (float)d.row_scales[r];
+        }
+        if (m->tail_w) std::memcpy(tail32.data() + row * m->tail_w, d.tail, (size_t)d.d_out * m->tail_w * sizeof(float));
+        row += d.d_out;
+    }
+    auto bail = [&](int st) {
+        free_matrix_buffers(m.get());
+        return st;
+    };
+#define UP_TRY(expr)                                                                                             \
+    do {                                                                                                         \
+        cudaError_t e_ = (expr);                                                                                 \
+        if (e_ != cudaSuccess) return bail(fail(LLVQ_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_))); \
+    } while (0)
+    UP_TRY(cudaMalloc(&m->codes, codes.size()));
+    UP_TRY(cudaMemcpy(m->codes, codes.data(), codes.size(), cudaMemcpyHostToDevice));
+    UP_TRY(cudaMalloc(&m->cent, cent.size() * sizeof(float2)));
+    UP_TRY(cudaMemcpy(m->cent, cent.data(), cent.size() * sizeof(float2), cudaMemcpyHostToDevice));
+    UP_TRY(cudaMalloc(&m->rscale, rs.size() * sizeof(float)));
+    UP_TRY(cudaMemcpy(m->rscale, rs.data(), rs.size() * sizeof(float), cudaMemcpyHostToDevice));
+    if (m->tail_w) {
+        if (m->tail_mode == LLVQ_TAIL_F16) {
+            std::vector<__half> t16(tail32.size());
+            for (size_t i = 0; i < tail32.size(); ++i) t16[i] = __float2half_rn(tail32[i]);
+            UP_TRY(cudaMalloc(&m->tail, t16.size() * sizeof(__half)));
+            UP_TRY(cudaMemcpy(m->tail, t16.data(), t16.size() * sizeof(__half), cudaMemcpyHostToDevice));
+        } else {
+            UP_TRY(cudaMalloc(&m->tail, tail32.size() * sizeof(float)));
+            UP_TRY(cudaMemcpy(m->tail, tail32.data(), tail32.size() * sizeof(float), cudaMemcpyHostToDevice));
+        }
+    } else {
+        UP_TRY(cudaMalloc(&m->tail, 16));  // never read; keeps the pointer valid
+    }
+    UP_TRY(cudaMalloc(&m->x_stage, (size_t)m->d_in * sizeof(float) + 16));
+    UP_TRY(cudaMalloc(&m->y_stage, (size_t)m->d_out * sizeof(float) + 16));
+#undef UP_TRY
+    *out = m.release();
+    return LLVQ_OK;
+}
+
+template <typename XT, typename YT>
+int gemv_host(llvq_matrix* m, const XT* xh, YT* yh, llvq_stream_t stream) {
+    if (!m || !xh || !yh) return fail(LLVQ_ERR_INVALID, "gemv_host: null argument");
+    DeviceGuard g(m->rt->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    CUDA_TRY(cudaMemcpyAsync(m->x_stage, xh, (size_t)m->d_in * sizeof(XT), cudaMemcpyHostToDevice, s));
+    int st = launch_gemv_generic<XT, YT>(m, (const XT*)m->x_stage, (YT*)m->y_stage, s);
+    if (st) return st;
+    CUDA_TRY(cudaMemcpyAsync(yh, m->y_stage, (size_t)m->d_out * sizeof(YT), cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaStreamSynchronize(s));
+    return LLVQ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* llvq_last_error(void) { return g_error.c_str(); }
+const char* llvq_version(void) { return "0.1.0"; }
+uint64_t llvq_launch_count(void) { return g_launches.load(); }
+
+void llvq_runtime_destroy(llvq_runtime* rt) {
+    if (!rt) return;
+    DeviceGuard g(rt->device);
+    cudaFree(rt->d_cls);
+    cudaFree(rt->d_ends);
+    cudaFree(rt->d_lut);
+    cudaFree(rt->d_golay);
+    cudaFree(rt->d_err);
+    delete rt;
+}
+
+int llvq_runtime_create(int device, llvq_runtime** out) {
+    if (!out) return fail(LLVQ_ERR_INVALID, "runtime_create: null out");
+    *out = nullptr;
+    int ndev = 0;
+    CUDA_TRY(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev) return fail(LLVQ_ERR_INVALID, "runtime_create: device %d of %d", device, ndev);
+    DeviceGuard g(device);
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(LLVQ_ERR_UNSUPPORTED, "runtime_create: device %d is sm_%d%d; this library is built for sm_100a only",
+                    device, prop.major, prop.minor);
+    std::unique_ptr<llvq_runtime> rt(new llvq_runtime);
+    rt->device = device;
+    rt->max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+    const Codebook& cb = rt->cb;
+    if (cb.classes.size() != (size_t)kMaxClasses || cb.n_classes12 != 301 || cb.total13 != kN13 || cb.total12 != kN12)
+        return fail(LLVQ_ERR_CODEBOOK, "class enumeration does not cover the ball: %zu classes, N=%llu", cb.classes.size(),
+                    (unsigned long long)cb.total13);
+    std::vector<DevClass> dc;
+    cb.dev_classes(dc);
+    std::vector<uint16_t> lut;
+    cb.class_lut(kLutShift, lut);
+    auto bail = [&](int st) {
+        llvq_runtime_destroy(rt.release());
+        return st;
+    };
+#define RT_TRY(expr)                                                                                             \
+    do {                                                                                                         \
+        cudaError_t e_ = (expr);                                                                                 \
+        if (e_ != cudaSuccess) return bail(fail(LLVQ_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_))); \
+    } while (0)
+    RT_TRY(cudaMalloc(&rt->d_cls, dc.size() * sizeof(DevClass)));
+    RT_TRY(cudaMemcpy(rt->d_cls, dc.data(), dc.size() * sizeof(DevClass), cudaMemcpyHostToDevice));
+    RT_TRY(cudaMalloc(&rt->d_ends, cb.ends.size() * sizeof(uint64_t)));
+    RT_TRY(cudaMemcpy(rt->d_ends, cb.ends.data(), cb.ends.size() * sizeof(uint64_t), cudaMemcpyHostToDevice));
+    RT_TRY(cudaMalloc(&rt->d_lut, lut.size() * sizeof(uint16_t)));
+    RT_TRY(cudaMemcpy(rt->d_lut, lut.data(), lut.size() * sizeof(uint16_t), cudaMemcpyHostToDevice));
+    RT_TRY(cudaMalloc(&rt->d_golay, sizeof cb.golay));
+    RT_TRY(cudaMemcpy(rt->d_golay, cb.golay, sizeof cb.golay, cudaMemcpyHostToDevice));
+    RT_TRY(cudaMalloc((void**)&rt->d_err, sizeof(int)));
+    RT_TRY(cudaMemset(rt->d_err, 0, sizeof(int)));
+    rt->T.cls = (const DevClass*)rt->d_cls;
+    rt->T.ends = (const unsigned long long*)rt->d_ends;
+    rt->T.lut = (const unsigned short*)rt->d_lut;
+    rt->T.golay = (const unsigned int*)rt->d_golay;
+    rt->T.lut_shift = kLutShift;
+
+    // Verify the device tables against the published fingerprint: decode the probe
+    // indices on the GPU and fold them into the reference's digest.
+    std::vector<uint64_t> probes;
+    probe_indices(cb, probes);
+    const size_t np = probes.size();
+    unsigned long long* d_idx = nullptr;
+    signed char* d_pts = nullptr;
+    unsigned char* d_shell = nullptr;
+    RT_TRY(cudaMalloc(&d_idx, np * sizeof(uint64_t)));
+    RT_TRY(cudaMalloc(&d_pts, np * kDim));
+    RT_TRY(cudaMalloc(&d_shell, np));
+    RT_TRY(cudaMemcpy(d_idx, probes.data(), np * sizeof(uint64_t), cudaMemcpyHostToDevice));
+    decode_indices_kernel<<<(unsigned)((np + 127) / 128), 128>>>(rt->T, d_idx, np, d_pts, d_shell, kN13);
+    g_launches++;
+    RT_TRY(cudaGetLastError());
+    std::vector<int8_t> pts(np * kDim);
+    std::vector<uint8_t> shell(np), ok(np);
+    RT_TRY(cudaMemcpy(pts.data(), d_pts, np * kDim, cudaMemcpyDeviceToHost));
+    RT_TRY(cudaMemcpy(shell.data(), d_shell, np, cudaMemcpyDeviceToHost));
+    cudaFree(d_idx);
+    cudaFree(d_pts);
+    cudaFree(d_shell);
+#undef RT_TRY
+    for (size_t i = 0; i < np; ++i) ok[i] = shell[i] != 255;
+    rt->fingerprint = fingerprint_from_points(cb, probes, pts.data(), ok.data());
+    if (rt->fingerprint != LLVQ_PUBLISHED_FINGERPRINT)
+        return bail(fail(LLVQ_ERR_CODEBOOK, "device codebook fingerprint %016llx differs from the published %016llx",
+                         (unsigned long long)rt->fingerprint, (unsigned long long)LLVQ_PUBLISHED_FINGERPRINT));
+    *out = rt.release();
+    return LLVQ_OK;
+}
+
+int llvq_codebook_fingerprint(llvq_runtime* rt, uint64_t* out) {
+    if (!rt || !out) return fail(LLVQ_ERR_INVALID, "codebook_fingerprint: null argument");
+    *out = rt->fingerprint;
+    return LLVQ_OK;
+}
+
+int llvq_codebook_info(llvq_runtime* rt, int shell_cap, int32_t* n_classes, uint64_t* ball_size) {
+    if (!rt) return fail(LLVQ_ERR_INVALID, "codebook_info: null runtime");
+    if (shell_cap != 12 && shell_cap != 13) return fail(LLVQ_ERR_INVALID, "codebook_info: shell cap %d", shell_cap);
+    if (n_classes) *n_classes = shell_cap == 12 ? rt->cb.n_classes12 : (int)rt->cb.classes.size();
+    if (ball_size) *ball_size = shell_cap == 12 ? rt->cb.total12 : rt->cb.total13;
+    return LLVQ_OK;
+}
+
+int llvq_codebook_class_record(int32_t ci, void* out) {
+    static const Codebook cb;
+    static const std::vector<DevClass> dc = [] {
+        std::vector<DevClass> v;
+        cb.dev_classes(v);
+        return v;
+    }();
+    if (!out || ci < 0 || ci >= (int)dc.size()) return fail(LLVQ_ERR_INVALID, "class_record: class %d", ci);
+    std::memcpy(out, &dc[ci], sizeof(DevClass));
+    return LLVQ_OK;
+}
+
+int llvq_codebook_golay(uint32_t* out) {
+    static const Codebook cb;
+    if (!out) return fail(LLVQ_ERR_INVALID, "codebook_golay: null out");
+    std::memcpy(out, cb.golay, sizeof cb.golay);
+    return LLVQ_OK;
+}
+
+int llvq_runtime_poll_error(llvq_runtime* rt, int32_t* flag) {
+    if (!rt || !flag) return fail(LLVQ_ERR_INVALID, "poll_error: null argument");
+    DeviceGuard g(rt->device);
+    CUDA_TRY(cudaDeviceSynchronize());
+    int v = 0;
+    CUDA_TRY(cudaMemcpy(&v, rt->d_err, sizeof v, cudaMemcpyDeviceToHost));
+    CUDA_TRY(cudaMemset(rt->d_err, 0, sizeof v));
+    *flag = v;
+    return LLVQ_OK;
+}
+
+int llvq_matrix_upload(llvq_runtime* rt, const llvq_matrix_desc* desc, llvq_matrix** out) {
+    return upload_impl(rt, desc, 1, out);
+}
+
+int llvq_matrix_upload_group(llvq_runtime* rt, const llvq_matrix_desc* descs, int32_t n, llvq_matrix** out) {
+    return upload_impl(rt, descs, n, out);
+}
+
+void llvq_matrix_free(llvq_matrix* m) {
+    if (!m) return;
+    DeviceGuard g(m->rt->device);
+    free_matrix_buffers(m);
+    delete m;
+}
+
+int llvq_matrix_dims(const llvq_matrix* m, int32_t* d_out, int32_t* d_in) {
+    if (!m) return fail(LLVQ_ERR_INVALID, "matrix_dims: null matrix");
+    if (d_out) *d_out = m->d_out;
+    if (d_in) *d_in = m->d_in;
+    return LLVQ_OK;
+}
+
+int llvq_matrix_algorithmic_bytes(const llvq_matrix* m, int32_t x_elem_bytes, int32_t y_elem_bytes, uint64_t* out) {
+    if (!m || !out) return fail(LLVQ_ERR_INVALID, "algorithmic_bytes: null argument");
+    *out = (uint64_t)m->codes_bytes + (uint64_t)m->d_out * m->tail_w * 4 + (uint64_t)m->d_out * 8 +
+           (uint64_t)m->d_in * x_elem_bytes + (uint64_t)m->d_out * y_elem_bytes;
+    return LLVQ_OK;
+}
+
+int llvq_gemv_f32(llvq_matrix* m, const float* x, float* y, llvq_stream_t s) { return gemv_entry<float, float>(m, x, y, s); }
+int llvq_gemv_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, llvq_stream_t s) {
+    return gemv_entry<__half, __half>(m, (const __half*)x, (__half*)y, s);
+}
+int llvq_gemv_f32x_h(llvq_matrix* m, const float* x, uint16_t* y, llvq_stream_t s) {
+    return gemv_entry<float, __half>(m, x, (__half*)y, s);
+}
+
+int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, llvq_stream_t s) {
+    if (!m || !x || !y || batch <= 0) return fail(LLVQ_ERR_INVALID, "gemm_h: bad argument");
+    // Until the batched kernel lands the batch is served row by row, exactly as the
+    // reference's drive_rows does.
+    for (int b = 0; b < batch; ++b) {
+        int st = gemv_entry<__half, __half>(m, (const __half*)x + (size_t)b * m->d_in, (__half*)y + (size_t)b * m->d_out, s);
+        if (st) return st;
+    }
+    return LLVQ_OK;
+}
+
+int llvq_gemv_f32_host(llvq_matrix* m, const float* x, float* y, llvq_stream_t s) { return gemv_host<float, float>(m, x, y, s); }
+int llvq_gemv_h_host(llvq_matrix* m, const uint16_t* x, uint16_t* y, llvq_stream_t s) {
+    return gemv_host<__half, __half>(m, (const __half*)x, (__half*)y, s);
+}
+
+int llvq_decode_blocks(llvq_runtime* rt, const uint8_t* codes, size_t n, int8_t* points, uint8_t* shell, uint8_t* gain,
+                       llvq_stream_t stream) {
+    if (!rt || !codes || !points || !shell) return fail(LLVQ_ERR_INVALID, "decode_blocks: null argument");
+    if (n == 0) return LLVQ_OK;
+    if (n > (size_t)1 << 36) return fail(LLVQ_ERR_INVALID, "decode_blocks: n too large");
+    DeviceGuard g(rt->device);
+    decode_blocks_kernel<<<(unsigned)((n + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
+        rt->T, codes, n, (signed char*)points, shell, gain, kN12);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+int llvq_decode_indices(llvq_runtime* rt, const uint64_t* idx, size_t n, int8_t* points, uint8_t* shell, llvq_stream_t stream) {
+    if (!rt || !idx || !points || !shell) return fail(LLVQ_ERR_INVALID, "decode_indices: null argument");
+    if (n == 0) return LLVQ_OK;
+    if (n > (size_t)1 << 36) return fail(LLVQ_ERR_INVALID, "decode_indices: n too large");
+    DeviceGuard g(rt->device);
+    decode_indices_kernel<<<(unsigned)((n + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
+        rt->T, (const unsigned long long*)idx, n, (signed char*)points, shell, kN13);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+}  // extern "C"

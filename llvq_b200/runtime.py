@@ -1,0 +1,193 @@
+"""Host-side mirror of the reference's operator surface for the fused path.
+
+`FusedRuntime` / `FusedProj` follow llvq-llm/src/fused_cuda.rs:119-160,182-402: a
+runtime owns the per-GPU tables, a projection owns its resident device buffers
+and `forward_rotated(proj, x)` is the one call the model makes per projection.
+Everything is a thin layer over the C ABI of include/llvq_b200.h; PyTorch only
+provides device memory and streams. There is no CPU path: without the CUDA
+library or a GPU these classes raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import MatrixDesc, TAIL_F16, TAIL_F32, check
+
+
+def _desc(m, tail_mode: int, keep: list) -> MatrixDesc:
+    codes = np.ascontiguousarray(m.codes, np.uint8)
+    cen = np.ascontiguousarray(m.centroids, np.float64)
+    rs = np.ascontiguousarray(m.row_scales, np.float64)
+    tail = np.ascontiguousarray(m.tail, np.float32).reshape(-1)
+    if cen.size != 2:
+        # the fused path serves exactly one gain bit (llvq-llm/src/fused.rs:1171-1177)
+        raise ValueError(f"{m.name}: {cen.size} centroids; the fused path needs exactly 2")
+    keep += [codes, cen, rs, tail]
+    return MatrixDesc(m.d_out, m.d_in, int(getattr(m, "shell_cap", 12)), tail_mode,
+                      codes.ctypes.data if codes.size else None, cen.ctypes.data, rs.ctypes.data,
+                      tail.ctypes.data if tail.size else None)
+
+
+class FusedProj:
+    """One resident projection (or a row-concatenated group of projections)."""
+
+    def __init__(self, rt: "FusedRuntime", handle: int, name: str, splits: Sequence[int]):
+        self.rt, self._h, self.name = rt, C.c_void_p(handle), name
+        self.splits = list(splits)  # d_out of every segment, in order
+        d_out, d_in = C.c_int32(), C.c_int32()
+        check(rt.lib.llvq_matrix_dims(self._h, C.byref(d_out), C.byref(d_in)))
+        self.d_out, self.d_in = d_out.value, d_in.value
+
+    def algorithmic_bytes(self, x_bytes: int, y_bytes: int) -> int:
+        out = C.c_uint64()
+        check(self.rt.lib.llvq_matrix_algorithmic_bytes(self._h, x_bytes, y_bytes, C.byref(out)))
+        return out.value
+
+    @property
+    def n_blocks(self) -> int:
+        return self.d_out * (self.d_in // 24)
+
+    def free(self) -> None:
+        if self._h:
+            self.rt.lib.llvq_matrix_free(self._h)
+            self._h = C.c_void_p(None)
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class FusedRuntime:
+    """Per-GPU decoder tables, verified against the published codebook fingerprint on creation."""
+
+    def __init__(self, device: int = 0):
+        self.lib = _lib.load()
+        self.device = device
+        h = C.c_void_p()
+        check(self.lib.llvq_runtime_create(device, C.byref(h)))
+        self._h = h
+
+    # -- codebook ---------------------------------------------------------------
+    def fingerprint(self) -> int:
+        out = C.c_uint64()
+        check(self.lib.llvq_codebook_fingerprint(self._h, C.byref(out)))
+        return out.value
+
+    def codebook_info(self, shell_cap: int = 12):
+        n, size = C.c_int32(), C.c_uint64()
+        check(self.lib.llvq_codebook_info(self._h, shell_cap, C.byref(n), C.byref(size)))
+        return n.value, size.value
+
+    def poll_range_error(self) -> bool:
+        flag = C.c_int32()
+        check(self.lib.llvq_runtime_poll_error(self._h, C.byref(flag)))
+        return bool(flag.value)
+
+    # -- upload -----------------------------------------------------------------
+    def upload(self, m, tail_f16: bool = False) -> FusedProj:
+        keep: list = []
+        d = _desc(m, TAIL_F16 if tail_f16 else TAIL_F32, keep)
+        h = C.c_void_p()
+        check(self.lib.llvq_matrix_upload(self._h, C.byref(d), C.byref(h)))
+        return FusedProj(self, h.value, m.name, [m.d_out])
+
+    def upload_group(self, ms: Sequence, tail_f16: bool = False) -> FusedProj:
+        keep: list = []
+        arr = (MatrixDesc * len(ms))(*[_desc(m, TAIL_F16 if tail_f16 else TAIL_F32, keep) for m in ms])
+        h = C.c_void_p()
+        check(self.lib.llvq_matrix_upload_group(self._h, arr, len(ms), C.byref(h)))
+        return FusedProj(self, h.value, "|".join(m.name for m in ms), [m.d_out for m in ms])
+
+    # -- forward ----------------------------------------------------------------
+    @staticmethod
+    def _stream():
+        import torch
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def forward_rotated(self, proj: FusedProj, xr, out=None):
+        """f32 activation [d_in] -> f16 result [d_out]; FusedRuntime::forward_rotated."""
+        import torch
+        self._check_x(proj, xr, torch.float32)
+        y = out if out is not None else torch.empty(proj.d_out, dtype=torch.float16, device=xr.device)
+        check(self.lib.llvq_gemv_f32x_h(proj._h, xr.data_ptr(), y.data_ptr(), self._stream()))
+        return y
+
+    def forward(self, proj: FusedProj, x, out=None):
+        """Same dtype in and out: f32 -> f32 (kernel bench path) or f16 -> f16 (model path)."""
+        import torch
+        if x.dtype == torch.float32:
+            fn = self.lib.llvq_gemv_f32
+        elif x.dtype == torch.float16:
+            fn = self.lib.llvq_gemv_h
+        else:
+            raise TypeError(f"activation dtype {x.dtype}: the fused path takes f32 or f16")
+        self._check_x(proj, x, x.dtype)
+        y = out if out is not None else torch.empty(proj.d_out, dtype=x.dtype, device=x.device)
+        check(fn(proj._h, x.data_ptr(), y.data_ptr(), self._stream()))
+        return y
+
+    def forward_batch(self, proj: FusedProj, x, out=None):
+        """f16 [B, d_in] -> f16 [B, d_out]; every code is decoded once per batch."""
+        import torch
+        if x.dim() != 2 or x.shape[1] != proj.d_in or x.dtype != torch.float16 or not x.is_contiguous():
+            raise ValueError("forward_batch: x must be a contiguous f16 [B, d_in] tensor")
+        y = out if out is not None else torch.empty(x.shape[0], proj.d_out, dtype=torch.float16, device=x.device)
+        check(self.lib.llvq_gemm_h(proj._h, x.data_ptr(), y.data_ptr(), x.shape[0], self._stream()))
+        return y
+
+    def forward_host(self, proj: FusedProj, x_host: np.ndarray, y_host: np.ndarray):
+        """Host buffers in and out (copies inside the call); returns after the result has landed."""
+        if x_host.dtype == np.float32:
+            fn = self.lib.llvq_gemv_f32_host
+        elif x_host.dtype == np.float16:
+            fn = self.lib.llvq_gemv_h_host
+        else:
+            raise TypeError("forward_host: f32 or f16 activations")
+        if x_host.size != proj.d_in or y_host.size != proj.d_out or y_host.dtype != x_host.dtype:
+            raise ValueError("forward_host: shape or dtype mismatch")
+        check(fn(proj._h, x_host.ctypes.data, y_host.ctypes.data, self._stream()))
+        return y_host
+
+    @staticmethod
+    def _check_x(proj: FusedProj, x, dtype) -> None:
+        # the reference's own preconditions: contiguous, len == d_in (fused_cuda.rs:768-787)
+        if not x.is_cuda or x.dtype != dtype or not x.is_contiguous() or x.numel() != proj.d_in:
+            raise ValueError(f"{proj.name}: activation must be a contiguous CUDA {dtype} tensor of {proj.d_in} elements")
+
+    # -- probes -----------------------------------------------------------------
+    def decode_blocks(self, codes_dev):
+        """uint8 CUDA tensor of 6-byte records -> (points int8 [n,24], shell u8 [n], gain u8 [n])."""
+        import torch
+        n = codes_dev.numel() // 6
+        pts = torch.empty((n, 24), dtype=torch.int8, device=codes_dev.device)
+        shell = torch.empty(n, dtype=torch.uint8, device=codes_dev.device)
+        gain = torch.empty(n, dtype=torch.uint8, device=codes_dev.device)
+        check(self.lib.llvq_decode_blocks(self._h, codes_dev.data_ptr(), n, pts.data_ptr(), shell.data_ptr(),
+                                          gain.data_ptr(), self._stream()))
+        return pts, shell, gain
+
+    def decode_indices(self, idx_dev):
+        """int64/uint64 CUDA tensor of indices (cap-13 ball) -> (points int8 [n,24], shell u8 [n])."""
+        import torch
+        n = idx_dev.numel()
+        pts = torch.empty((n, 24), dtype=torch.int8, device=idx_dev.device)
+        shell = torch.empty(n, dtype=torch.uint8, device=idx_dev.device)
+        check(self.lib.llvq_decode_indices(self._h, idx_dev.data_ptr(), n, pts.data_ptr(), shell.data_ptr(), self._stream()))
+        return pts, shell
+
+    def close(self) -> None:
+        if self._h:
+            self.lib.llvq_runtime_destroy(self._h)
+            self._h = C.c_void_p(None)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,59 @@
+// Host shim: compiles the library's scalar decoders (the very source the CUDA
+// kernels include) as plain C++ so the test-suite can run them without a GPU and
+// diff them against the CPU oracle. The reference tests its kernels the same way
+// (llvq-cuda/tests/host_shim.h, decoder_matches_rust.rs). Test-only.
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#include "../../llvq_b200/csrc/codebook.cpp"
+#include "../../llvq_b200/csrc/decode_generic.cuh"
+
+using namespace llvq;
+
+namespace {
+struct HostTables {
+    Codebook cb;
+    std::vector<DevClass> cls;
+    std::vector<uint16_t> lut;
+    DevTables T;
+    HostTables() {
+        cb.dev_classes(cls);
+        cb.class_lut(35, lut);
+        T.cls = cls.data();
+        T.ends = (const unsigned long long*)cb.ends.data();
+        T.lut = lut.data();
+        T.golay = cb.golay;
+        T.lut_shift = 35;
+    }
+};
+HostTables& tables() {
+    static HostTables t;
+    return t;
+}
+}  // namespace
+
+extern "C" {
+
+void shim_decode_indices(const uint64_t* idx, int64_t n, int8_t* points, uint8_t* shell, int cap) {
+    const DevTables& T = tables().T;
+    const unsigned long long limit = cap == 13 ? kN13 : kN12;
+    for (int64_t b = 0; b < n; ++b) {
+        int8_t* out = points + b * kDim;
+        float scale;
+        shell[b] = (uint8_t)decode_generic(T, idx[b], limit, [&](int pos, int val) { out[pos] = (int8_t)val; }, &scale);
+    }
+}
+
+uint64_t shim_fingerprint(void) {
+    HostTables& t = tables();
+    std::vector<uint64_t> probes;
+    probe_indices(t.cb, probes);
+    std::vector<int8_t> pts(probes.size() * kDim);
+    std::vector<uint8_t> shell(probes.size()), ok(probes.size());
+    shim_decode_indices(probes.data(), (int64_t)probes.size(), pts.data(), shell.data(), 13);
+    for (size_t i = 0; i < probes.size(); ++i) ok[i] = shell[i] != 255;
+    return fingerprint_from_points(t.cb, probes, pts.data(), ok.data());
+}
+
+}  // extern "C"

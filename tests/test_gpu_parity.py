@@ -1,0 +1,246 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Bit-exact for the lattice decode; for the GEMV the tolerances BASELINE.json states:
+relative L2 <= 1e-5 with f32 activations, <= 1e-3 with f16 activations, plus the
+reference's own per-row criterion max |got - ref| / sum |w_i x_i| < 1e-5 for f32
+(llvq-cuda/src/bin/matvec.rs:63,114-120).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import probe_indices
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-5
+TOL_F16 = 1e-3
+
+
+def rel_l2(got, ref):
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    return float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-300))
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def gpu_gemv(rt, m, x, mode="same", tail_f16=False):
+    torch = _torch()
+    proj = rt.upload(m, tail_f16=tail_f16)
+    xd = torch.from_numpy(x).cuda()
+    y = rt.forward_rotated(proj, xd) if mode == "f32x_h" else rt.forward(proj, xd)
+    torch.cuda.synchronize()
+    out = y.cpu().numpy()
+    proj.free()
+    return out
+
+
+def test_runtime_reproduces_published_fingerprint(rt, oracle):
+    assert rt.fingerprint() == oracle.PUBLISHED_FINGERPRINT
+    assert rt.codebook_info(12) == (301, oracle.N12)
+    assert rt.codebook_info(13) == (383, oracle.N13)
+
+
+def test_decode_indices_every_class_boundary(rt, oracle):
+    torch = _torch()
+    idx = probe_indices(oracle, per_class_random=50, cap=13)
+    pts, shell = rt.decode_indices(torch.from_numpy(idx.view(np.int64)).cuda())
+    pts, shell = pts.cpu().numpy(), shell.cpu().numpy()
+    for k, i in enumerate(idx):
+        assert np.array_equal(pts[k], oracle.decode_index(int(i), 13)), int(i)
+    extra = np.array([oracle.N13, oracle.N13 + 1, (1 << 48) - 1, 1 << 63], np.uint64)
+    pts, shell = rt.decode_indices(torch.from_numpy(extra.view(np.int64)).cuda())
+    assert shell.cpu().tolist() == [13, 255, 255, 255] and not pts[1:].cpu().numpy().any()
+
+
+def test_decode_blocks_bit_exact_on_uniform_draws(rt, oracle):
+    torch = _torch()
+    from llvq_b200 import synth
+    g = synth.SplitMix64(0xB10C)
+    n = 2_000_000
+    idx = g.take(n) % np.uint64(oracle.N12 + 1)
+    gain = g.take(n) & np.uint64(1)
+    codes = synth.pack_codes(idx, gain)
+    pts, shell, gn = rt.decode_blocks(torch.from_numpy(codes).cuda())
+    ref_pts, ref_shell, ref_gain, bad = oracle.decode_codes(codes)
+    assert bad == 0
+    assert np.array_equal(pts.cpu().numpy(), ref_pts)
+    assert np.array_equal(shell.cpu().numpy(), ref_shell)
+    assert np.array_equal(gn.cpu().numpy(), ref_gain)
+
+
+def test_decode_blocks_edge_records(rt, oracle):
+    torch = _torch()
+    from llvq_b200 import synth
+    idx = np.concatenate([probe_indices(oracle, cap=12), np.array([oracle.N12 + 1, (1 << 47) - 1], np.uint64)])
+    gain = (np.arange(idx.size) & 1).astype(np.uint64)
+    codes = synth.pack_codes(idx, gain)
+    pts, shell, gn = rt.decode_blocks(torch.from_numpy(codes).cuda())
+    ref_pts, ref_shell, ref_gain, bad = oracle.decode_codes(codes, use_ref=True)
+    assert bad == 2
+    assert np.array_equal(pts.cpu().numpy(), ref_pts)
+    assert np.array_equal(shell.cpu().numpy(), ref_shell) and shell[-1].item() == 255
+    assert np.array_equal(gn.cpu().numpy(), ref_gain)
+    # empty input is a no-op
+    e_pts, e_shell, e_gain = rt.decode_blocks(torch.empty(0, dtype=torch.uint8, device="cuda"))
+    assert e_pts.shape == (0, 24)
+
+
+@pytest.mark.parametrize("d_out,d_in", [(8, 24), (16, 127), (9, 24 * 7 + 3), (1, 48), (40, 23), (64, 2560), (24, 9728)])
+def test_gemv_f32_small_and_ragged(rt, oracle, d_out, d_in):
+    from llvq_b200 import synth
+    m = synth.make_matrix(d_out, d_in, 1000 + d_out * 7 + d_in)
+    x = synth.make_activation(d_in, 77 + d_in)
+    y = gpu_gemv(rt, m, x)
+    ref, absdot = oracle.gemv_f64(m.codes, d_out, d_in, m.centroids, m.row_scales, m.tail, x.astype(np.float64),
+                                  use_ref=True, want_absdot=True)
+    assert rel_l2(y, ref) <= TOL_F32
+    assert np.max(np.abs(y - ref) / np.maximum(absdot, 1e-300)) < 1e-5
+
+
+def test_gemv_config0_up_proj_f32(rt, oracle):
+    """BASELINE config 0: W 9728 x 2560 (106 blocks + 16 tail columns), f32 activation."""
+    from llvq_b200 import synth
+    m = synth.make_matrix(9728, 2560, synth.matrix_seed(0, 0, synth.PROJ_IDS["up"]), "up")
+    x = synth.make_activation(2560, synth.matrix_seed(0, 0, 5))
+    y = gpu_gemv(rt, m, x)
+    ref, absdot = oracle.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales, m.tail, x.astype(np.float64),
+                                  want_absdot=True)
+    assert rel_l2(y, ref) <= TOL_F32
+    assert np.max(np.abs(y - ref) / absdot) < 1e-5
+    assert not rt.poll_range_error()
+
+
+def test_gemv_config1_layer_f16(rt, oracle):
+    """BASELINE config 1: the seven projections of one Qwen3-4B layer, f16 activations and results."""
+    from llvq_b200 import synth
+    layer = synth.make_layer("qwen3-4b", 1, 0)
+    for name, m in layer.items():
+        x = synth.make_activation(m.d_in, synth.matrix_seed(1, 0, synth.PROJ_IDS[name]), np.float16)
+        y = gpu_gemv(rt, m, x, tail_f16=True)
+        tail16 = m.tail.astype(np.float16).astype(np.float32)
+        ref = oracle.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales, tail16, x.astype(np.float64))
+        assert y.dtype == np.float16
+        assert rel_l2(y, ref) <= TOL_F16, name
+
+
+def test_gemv_f32x_h_matches_reference_signature(rt, oracle):
+    from llvq_b200 import synth
+    m = synth.make_matrix(1024, 2560, 31337)
+    x = synth.make_activation(2560, 4242)
+    y = gpu_gemv(rt, m, x, mode="f32x_h", tail_f16=True)
+    tail16 = m.tail.astype(np.float16).astype(np.float32)
+    ref = oracle.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales, tail16, x.astype(np.float64))
+    assert y.dtype == np.float16 and rel_l2(y, ref) <= TOL_F16
+
+
+def test_group_upload_equals_separate_projections(rt, oracle):
+    torch = _torch()
+    from llvq_b200 import synth
+    parts = [synth.make_matrix(d, 24 * 20 + 8, 900 + i) for i, d in enumerate((64, 16, 24))]
+    x = synth.make_activation(parts[0].d_in, 5)
+    xd = torch.from_numpy(x).cuda()
+    grp = rt.upload_group(parts)
+    assert grp.d_out == 104 and grp.splits == [64, 16, 24]
+    yg = rt.forward(grp, xd).cpu().numpy()
+    ys = np.concatenate([gpu_gemv(rt, p, x) for p in parts])
+    assert np.array_equal(yg, ys)  # same kernel, same rows: identical bits
+    ref = np.concatenate([oracle.gemv_f64(p.codes, p.d_out, p.d_in, p.centroids, p.row_scales, p.tail, x.astype(np.float64))
+                          for p in parts])
+    assert rel_l2(yg, ref) <= TOL_F32
+
+
+def test_output_buffer_is_fully_overwritten(rt):
+    torch = _torch()
+    from llvq_b200 import synth
+    m = synth.make_matrix(72, 24 * 9, 11)
+    proj = rt.upload(m)
+    xd = torch.from_numpy(synth.make_activation(m.d_in, 3)).cuda()
+    a = rt.forward(proj, xd, out=torch.full((72,), float("nan"), device="cuda"))
+    b = rt.forward(proj, xd, out=torch.full((72,), 1e30, device="cuda"))
+    assert torch.isfinite(a).all() and torch.equal(a, b)
+
+
+def test_linearity_at_full_size(rt):
+    """Size-independent property on the 9728 x 2560 shape: W(a x1 + x2) = a W x1 + W x2 within f32 rounding."""
+    torch = _torch()
+    from llvq_b200 import synth
+    m = synth.make_matrix(9728, 2560, 123456)
+    proj = rt.upload(m)
+    x1 = torch.from_numpy(synth.make_activation(2560, 1)).cuda()
+    x2 = torch.from_numpy(synth.make_activation(2560, 2)).cuda()
+    y1, y2 = rt.forward(proj, x1).double(), rt.forward(proj, x2).double()
+    y12 = rt.forward(proj, 0.5 * x1 + x2).double()
+    err = (y12 - (0.5 * y1 + y2)).norm() / y12.norm()
+    assert err.item() < 1e-5
+    z = rt.forward(proj, torch.zeros(2560, device="cuda"))
+    assert not z.any()
+
+
+def test_host_buffer_entry_point(rt, oracle):
+    from llvq_b200 import synth
+    m = synth.make_matrix(128, 24 * 30 + 4, 2024)
+    proj = rt.upload(m)
+    for dt, tol in ((np.float32, TOL_F32), (np.float16, TOL_F16)):
+        x = synth.make_activation(m.d_in, 9, dt)
+        y = np.empty(m.d_out, dt)
+        rt.forward_host(proj, x, y)
+        ref = oracle.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales, m.tail, x.astype(np.float64))
+        assert rel_l2(y, ref) <= tol
+
+
+def test_index_outside_the_ball_raises_the_range_flag(rt, oracle):
+    torch = _torch()
+    from llvq_b200 import synth
+    m = synth.make_matrix(8, 48, 5)
+    idx, gain = synth.unpack_codes(m.codes)
+    idx[3] = oracle.N12 + 5
+    m.codes = synth.pack_codes(idx, gain)
+    proj = rt.upload(m)
+    assert not rt.poll_range_error()
+    y = rt.forward(proj, torch.ones(48, device="cuda"))
+    assert rt.poll_range_error() and not rt.poll_range_error()  # sticky until polled, then cleared
+    assert torch.isfinite(y).all()  # the refused block contributes zero; nothing traps
+
+
+def test_argument_errors_are_statuses_not_crashes(rt):
+    torch = _torch()
+    from llvq_b200 import LlvqError, _lib, synth
+    m = synth.make_matrix(8, 48, 1)
+    m.shell_cap = 13
+    with pytest.raises(LlvqError) as e:
+        rt.upload(m)
+    assert e.value.status == _lib.ERR_UNSUPPORTED and "cap" in e.value.message
+    m.shell_cap = 12
+    m.centroids = np.array([1.0, 2.0, 3.0])
+    with pytest.raises(ValueError):
+        rt.upload(m)
+    m.centroids = np.array([1.0, 2.0])
+    proj = rt.upload(m)
+    with pytest.raises(ValueError):
+        rt.forward(proj, torch.ones(47, device="cuda"))
+    with pytest.raises(ValueError):
+        rt.forward(proj, torch.ones(96, device="cuda")[::2])
+    with pytest.raises(TypeError):
+        rt.forward(proj, torch.ones(48, device="cuda", dtype=torch.bfloat16))
+    L = _lib.load()
+    assert L.llvq_gemv_f32(proj._h, C.c_void_p(2), C.c_void_p(4), None) == _lib.ERR_INVALID  # misaligned
+    h = C.c_void_p()
+    assert L.llvq_runtime_create(99, C.byref(h)) == _lib.ERR_INVALID
+
+
+def test_batch_forward_matches_row_by_row(rt, oracle):
+    torch = _torch()
+    from llvq_b200 import synth
+    m = synth.make_matrix(256, 24 * 40 + 16, 77)
+    proj = rt.upload(m, tail_f16=True)
+    for batch in (1, 3, 16, 64):
+        x = synth.make_activation(m.d_in, 500 + batch, np.float16, batch=batch)
+        y = rt.forward_batch(proj, torch.from_numpy(x).cuda()).cpu().numpy()
+        tail16 = m.tail.astype(np.float16).astype(np.float32)
+        ref = oracle.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales, tail16, x.astype(np.float64))
+        assert y.shape == (batch, 256) and rel_l2(y, ref) <= TOL_F16
