@@ -14,6 +14,7 @@
 
 #include "../../include/llvq_b200.h"
 #include "codebook.h"
+#include "gemv_sorted.cuh"
 #include "kernels_generic.cuh"
 
 using namespace llvq;
@@ -66,7 +67,11 @@ struct llvq_runtime {
     void* d_ends = nullptr;
     void* d_lut = nullptr;
     void* d_golay = nullptr;
-    int* d_err = nullptr;  // sticky "index outside the ball" flag written by kernels
+    int* d_err = nullptr;  // sticky flag written by kernels: bit 0 index outside the ball, bit 1 copy timeout
+    FastTables F{};
+    void* d_fcls = nullptr;
+    void* d_lut_on = nullptr;
+    void* d_lut_off = nullptr;
     uint64_t fingerprint = 0;
     int max_smem_optin = 0;
 };
@@ -117,12 +122,28 @@ int launch_gemv_generic(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
     return LLVQ_OK;
 }
 
+// The class-sorted kernel serves every matrix whose 8-row code slab fits in shared
+// memory (d_in up to roughly 90 000); beyond that the generic kernel takes over.
+template <typename XT, typename YT>
+int launch_gemv(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
+    llvq_runtime* rt = m->rt;
+    const size_t smem = sorted_smem_bytes(m->nb);
+    if (smem > (size_t)rt->max_smem_optin) return launch_gemv_generic<XT, YT>(m, x, y, s);
+    auto kern = gemv_sorted_kernel<XT, YT>;
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int grid = (m->d_out + kRows - 1) / kRows;
+    kern<<<grid, kThreads, smem, s>>>(rt->F, rt->T, m->view(), x, y, rt->d_err);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
 template <typename XT, typename YT>
 int gemv_entry(llvq_matrix* m, const XT* x, YT* y, llvq_stream_t stream) {
     if (!m || !x || !y) return fail(LLVQ_ERR_INVALID, "gemv: null argument");
     if (((uintptr_t)x % sizeof(XT)) || ((uintptr_t)y % sizeof(YT))) return fail(LLVQ_ERR_INVALID, "gemv: misaligned buffer");
     DeviceGuard g(m->rt->device);
-    return launch_gemv_generic<XT, YT>(m, x, y, (cudaStream_t)stream);
+    return launch_gemv<XT, YT>(m, x, y, (cudaStream_t)stream);
 }
 
 int check_desc(const llvq_matrix_desc& d) {
@@ -225,7 +246,7 @@ int gemv_host(llvq_matrix* m, const XT* xh, YT* yh, llvq_stream_t stream) {
     DeviceGuard g(m->rt->device);
     cudaStream_t s = (cudaStream_t)stream;
     CUDA_TRY(cudaMemcpyAsync(m->x_stage, xh, (size_t)m->d_in * sizeof(XT), cudaMemcpyHostToDevice, s));
-    int st = launch_gemv_generic<XT, YT>(m, (const XT*)m->x_stage, (YT*)m->y_stage, s);
+    int st = launch_gemv<XT, YT>(m, (const XT*)m->x_stage, (YT*)m->y_stage, s);
     if (st) return st;
     CUDA_TRY(cudaMemcpyAsync(yh, m->y_stage, (size_t)m->d_out * sizeof(YT), cudaMemcpyDeviceToHost, s));
     CUDA_TRY(cudaStreamSynchronize(s));
@@ -248,6 +269,9 @@ void llvq_runtime_destroy(llvq_runtime* rt) {
     cudaFree(rt->d_lut);
     cudaFree(rt->d_golay);
     cudaFree(rt->d_err);
+    cudaFree(rt->d_fcls);
+    cudaFree(rt->d_lut_on);
+    cudaFree(rt->d_lut_off);
     delete rt;
 }
 
@@ -298,6 +322,22 @@ int llvq_runtime_create(int device, llvq_runtime** out) {
     rt->T.lut = (const unsigned short*)rt->d_lut;
     rt->T.golay = (const unsigned int*)rt->d_golay;
     rt->T.lut_shift = kLutShift;
+
+    FastTablesHost fh;
+    build_fast_tables(cb, fh);
+    RT_TRY(cudaMalloc(&rt->d_fcls, fh.cls.size() * sizeof(FastClass)));
+    RT_TRY(cudaMemcpy(rt->d_fcls, fh.cls.data(), fh.cls.size() * sizeof(FastClass), cudaMemcpyHostToDevice));
+    RT_TRY(cudaMalloc(&rt->d_lut_on, fh.lut_on.size() * sizeof(unsigned int)));
+    RT_TRY(cudaMemcpy(rt->d_lut_on, fh.lut_on.data(), fh.lut_on.size() * sizeof(unsigned int), cudaMemcpyHostToDevice));
+    RT_TRY(cudaMalloc(&rt->d_lut_off, fh.lut_off.size() * sizeof(unsigned int)));
+    RT_TRY(cudaMemcpy(rt->d_lut_off, fh.lut_off.data(), fh.lut_off.size() * sizeof(unsigned int), cudaMemcpyHostToDevice));
+    rt->F.cls = (const FastClass*)rt->d_fcls;
+    rt->F.ends = rt->T.ends;
+    rt->F.lut = rt->T.lut;
+    rt->F.golay = rt->T.golay;
+    rt->F.lut_on = (const unsigned int*)rt->d_lut_on;
+    rt->F.lut_off = (const unsigned int*)rt->d_lut_off;
+    rt->F.lut_shift = kLutShift;
 
     // Verify the device tables against the published fingerprint: decode the probe
     // indices on the GPU and fold them into the reference's digest.
@@ -430,8 +470,9 @@ int llvq_gemv_h_host(llvq_matrix* m, const uint16_t* x, uint16_t* y, llvq_stream
 
 int llvq_decode_blocks(llvq_runtime* rt, const uint8_t* codes, size_t n, int8_t* points, uint8_t* shell, uint8_t* gain,
                        llvq_stream_t stream) {
-    if (!rt || !codes || !points || !shell) return fail(LLVQ_ERR_INVALID, "decode_blocks: null argument");
+    if (!rt) return fail(LLVQ_ERR_INVALID, "decode_blocks: null runtime");
     if (n == 0) return LLVQ_OK;
+    if (!codes || !points || !shell) return fail(LLVQ_ERR_INVALID, "decode_blocks: null argument");
     if (n > (size_t)1 << 36) return fail(LLVQ_ERR_INVALID, "decode_blocks: n too large");
     DeviceGuard g(rt->device);
     decode_blocks_kernel<<<(unsigned)((n + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
@@ -442,8 +483,9 @@ int llvq_decode_blocks(llvq_runtime* rt, const uint8_t* codes, size_t n, int8_t*
 }
 
 int llvq_decode_indices(llvq_runtime* rt, const uint64_t* idx, size_t n, int8_t* points, uint8_t* shell, llvq_stream_t stream) {
-    if (!rt || !idx || !points || !shell) return fail(LLVQ_ERR_INVALID, "decode_indices: null argument");
+    if (!rt) return fail(LLVQ_ERR_INVALID, "decode_indices: null runtime");
     if (n == 0) return LLVQ_OK;
+    if (!idx || !points || !shell) return fail(LLVQ_ERR_INVALID, "decode_indices: null argument");
     if (n > (size_t)1 << 36) return fail(LLVQ_ERR_INVALID, "decode_indices: n too large");
     DeviceGuard g(rt->device);
     decode_indices_kernel<<<(unsigned)((n + 127) / 128), 128, 0, (cudaStream_t)stream>>>(

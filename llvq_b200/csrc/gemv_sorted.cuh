@@ -1,0 +1,285 @@
+// Class-sorted fused dequant-GEMV for sm_100a.
+//
+// One CTA owns kRows consecutive output rows. Their packed codes (a contiguous,
+// 16-byte aligned slab of the archive stream) are brought into shared memory by
+// one bulk asynchronous copy (cp.async.bulk, completion on an mbarrier). The row
+// tile is then processed in chunks of up to kChunk column blocks:
+//
+//   phase 1  every thread takes blocks of the chunk: 48-bit big-endian record ->
+//            (index, gain) -> class search -> local rank -> decode family. Blocks
+//            are counted per family with warp-aggregated shared-memory atomics.
+//   phase 1b items are written into one queue, grouped by family.
+//   phase 2  warps pull batches of 32 same-family items and run that family's
+//            branch-free decoder (decode_fast.cuh) with the dot product against
+//            the staged activation fused into its position loop; the block's
+//            contribution, scaled by gain centroid / sqrt(16 m), goes to part[].
+//   phase 3  one warp per row adds the chunk's partials in a fixed order.
+//
+// Sorting by family is what keeps the 32 lanes of a warp on one instruction
+// stream: blocks of the odd coset (24-slot unranking) and of the even coset
+// (table look-ups) cost very different amounts of work.
+//
+// The activation chunk is staged transposed, xs[pos][block] with an odd row
+// stride, so that lanes holding different blocks read different banks; that
+// transposition is why x takes ordinary loads rather than a bulk copy.
+#pragma once
+#include <cuda_fp16.h>
+
+#include "decode_fast.cuh"
+#include "decode_generic.cuh"
+#include "kernels_generic.cuh"
+
+namespace llvq {
+
+constexpr int kRows = 8;                             // rows per CTA
+constexpr int kChunk = 128;                          // column blocks per chunk
+constexpr int kChunkPad = kChunk + 1;                // xs row stride (odd: conflict-free transposition)
+constexpr int kThreads = 256;                        // 8 warps, one per row in phase 3
+constexpr int kItems = kRows * kChunk;               // 1024 blocks per chunk
+constexpr int kItemsPerThread = kItems / kThreads;   // 4
+constexpr unsigned int kSpinLimit = 1u << 22;        // bounded wait on the bulk copy
+
+struct SortedSmem {
+    unsigned long long mbar;
+    int count[4];   // items per family in this chunk
+    int base[4];    // first queue slot of each family
+    int ticket;     // next batch to hand out
+    int error;
+    float2 cent[kRows];
+    float rscale[kRows];
+    float xs_tail[32];
+    float part[kItems];
+    uint4 items[kItems];
+    float xs[kDim * kChunkPad];
+    // followed by the code slab (dynamic size)
+};
+
+__device__ __forceinline__ unsigned int smem_addr(const void* p) {
+    return (unsigned int)__cvta_generic_to_shared(p);
+}
+
+// Returns false when the copy did not complete within the spin limit.
+__device__ __forceinline__ bool bulk_load_codes(unsigned char* dst, const unsigned char* src, unsigned int bytes,
+                                                unsigned long long* mbar, int tid) {
+    const unsigned int bar = smem_addr(mbar);
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid == 0) {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+        asm volatile(
+            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
+            "l"(src), "r"(bytes), "r"(bar)
+            : "memory");
+    }
+    unsigned int done = 0;  // every thread polls; the verdict is made uniform by the caller
+    for (unsigned int spin = 0; spin < kSpinLimit && !done; ++spin) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar)
+            : "memory");
+    }
+    return done != 0;
+}
+
+// 48-bit big-endian record at byte offset 6 * f of the slab (2-byte aligned).
+__device__ __forceinline__ unsigned long long slab_code48(const unsigned char* slab, int f) {
+    const unsigned short* h = reinterpret_cast<const unsigned short*>(slab + 6 * f);
+    const unsigned int h0 = h[0], h1 = h[1], h2 = h[2];
+    const unsigned int hi = __byte_perm(h0, 0, 0x4401);                 // bytes 0,1 -> big-endian 16 bits
+    const unsigned int lo = __byte_perm(h1, h2, 0x0145);                // bytes 2..5 -> big-endian 32 bits
+    return ((unsigned long long)hi << 32) | lo;
+}
+
+template <typename XT, typename YT>
+__global__ void __launch_bounds__(kThreads, 2)
+gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restrict__ x, YT* __restrict__ y,
+                   int* __restrict__ err_flag) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    SortedSmem& S = *reinterpret_cast<SortedSmem*>(smem_raw);
+    unsigned char* slab = smem_raw + sizeof(SortedSmem);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nb = mv.nb;
+    const int row0 = blockIdx.x * kRows;
+    const int rows = min(kRows, mv.d_out - row0);
+
+    if (tid < kRows) {
+        const int r = min(row0 + tid, mv.d_out - 1);
+        S.cent[tid] = mv.cent[r];
+        S.rscale[tid] = mv.rscale[r];
+    }
+    if (tid < 32) S.xs_tail[tid] = tid < mv.tail_w ? to_f32<XT>(x[nb * kDim + tid]) : 0.0f;
+    if (tid == 0) S.error = 0;
+
+    if (nb > 0) {
+        // the slab start is 16-byte aligned because row0 is a multiple of 8 (48 * nb bytes per 8 rows)
+        const unsigned int bytes = ((unsigned int)rows * nb * 6 + 15u) & ~15u;
+        const bool landed = bulk_load_codes(slab, mv.codes + (size_t)row0 * nb * 6, bytes, &S.mbar, tid);
+        if (!__syncthreads_and(landed)) {
+            if (tid == 0) atomicOr(err_flag, 2);
+            return;  // the copy never landed: report, do not touch the slab
+        }
+    }
+
+    float row_acc = 0.0f;  // phase 3: lane-replicated sum of the row owned by this warp
+
+    for (int cb0 = 0; cb0 < nb; cb0 += kChunk) {
+        const int cbn = min(kChunk, nb - cb0);
+        const int n_items = rows * cbn;
+
+        // ---- stage the activation chunk (transposed) and reset the queue ----
+        for (int i = tid; i < cbn * kDim; i += kThreads) {
+            const int b = i / kDim, pos = i - b * kDim;
+            S.xs[pos * kChunkPad + b] = to_f32<XT>(x[(size_t)cb0 * kDim + i]);
+        }
+        if (tid < 4) S.count[tid] = 0;
+        if (tid == 0) S.ticket = 0;
+        __syncthreads();
+
+        // ---- phase 1: classify ----
+        unsigned long long loc[kItemsPerThread];
+        unsigned int meta[kItemsPerThread];  // ci | gain << 16 | path << 20 | valid << 24
+        unsigned int where[kItemsPerThread];  // lr << 16 | b_local
+        int slot[kItemsPerThread];
+#pragma unroll
+        for (int k = 0; k < kItemsPerThread; ++k) {
+            const int f = tid + k * kThreads;
+            const bool active = f < n_items;
+            const int lr = active ? f / cbn : 0;
+            const int bl = active ? f - lr * cbn : 0;
+            unsigned int path = 0, valid = 0;
+            meta[k] = 0;
+            loc[k] = 0;
+            where[k] = (unsigned int)lr << 16 | (unsigned int)bl;
+            if (active) {
+                const unsigned long long v = slab_code48(slab, lr * nb + cb0 + bl);
+                const Classified c = classify12(F, v >> 1);
+                if (c.ci >= 0) {
+                    valid = 1;
+                    path = c.path;
+                    // the generic decoder wants the index itself
+                    loc[k] = path == kPathSlow ? (v >> 1) : c.local;
+                    meta[k] = (unsigned int)c.ci | (unsigned int)(v & 1ull) << 16 | path << 20 | 1u << 24;
+                } else {
+                    S.part[lr * kChunk + bl] = 0.0f;  // origin, or refused index: contributes nothing
+                    if (c.ci == -2) S.error = 1;
+                }
+            }
+            // warp-aggregated slot allocation inside the family's queue
+            slot[k] = 0;
+#pragma unroll
+            for (unsigned int p = 0; p < 4; ++p) {
+                const unsigned int mask = __ballot_sync(0xffffffffu, valid && path == p);
+                if (mask) {
+                    int first = 0;
+                    if (lane == (__ffs(mask) - 1)) first = atomicAdd(&S.count[p], __popc(mask));
+                    first = __shfl_sync(0xffffffffu, first, __ffs(mask) - 1);
+                    if (valid && path == p) slot[k] = first + __popc(mask & ((1u << lane) - 1u));
+                }
+            }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            // queue order = processing order: generic first (longest single items), then odd, then even
+            S.base[kPathSlow] = 0;
+            S.base[kPathOdd3] = S.count[kPathSlow];
+            S.base[kPathOdd2] = S.base[kPathOdd3] + S.count[kPathOdd3];
+            S.base[kPathEven] = S.base[kPathOdd2] + S.count[kPathOdd2];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kItemsPerThread; ++k) {
+            if (meta[k] >> 24) {
+                const unsigned int p = (meta[k] >> 20) & 3u;
+                S.items[S.base[p] + slot[k]] =
+                    make_uint4((unsigned int)loc[k], (unsigned int)(loc[k] >> 32), meta[k], where[k]);
+            }
+        }
+        __syncthreads();
+
+        // ---- phase 2: decode + dot, one family per batch ----
+        const int n_slow = S.count[kPathSlow], n_o3 = S.count[kPathOdd3], n_o2 = S.count[kPathOdd2],
+                  n_ev = S.count[kPathEven];
+        const int b_slow = (n_slow + 31) >> 5, b_o3 = (n_o3 + 31) >> 5, b_o2 = (n_o2 + 31) >> 5, b_ev = (n_ev + 31) >> 5;
+        const int total_batches = b_slow + b_o3 + b_o2 + b_ev;
+        for (;;) {
+            int t = 0;
+            if (lane == 0) t = atomicAdd(&S.ticket, 1);
+            t = __shfl_sync(0xffffffffu, t, 0);
+            if (t >= total_batches) break;
+            unsigned int fam;
+            int first, count;
+            if (t < b_slow) {
+                fam = kPathSlow; first = S.base[kPathSlow] + 32 * t; count = n_slow - 32 * t;
+            } else if (t < b_slow + b_o3) {
+                const int u = t - b_slow;
+                fam = kPathOdd3; first = S.base[kPathOdd3] + 32 * u; count = n_o3 - 32 * u;
+            } else if (t < b_slow + b_o3 + b_o2) {
+                const int u = t - b_slow - b_o3;
+                fam = kPathOdd2; first = S.base[kPathOdd2] + 32 * u; count = n_o2 - 32 * u;
+            } else {
+                const int u = t - b_slow - b_o3 - b_o2;
+                fam = kPathEven; first = S.base[kPathEven] + 32 * u; count = n_ev - 32 * u;
+            }
+            if (lane < count) {  // the last batch of a family may be ragged
+            const uint4 it = S.items[first + lane];
+            const unsigned long long local = (unsigned long long)it.y << 32 | it.x;
+            const int ci = (int)(it.z & 0xffffu);
+            const unsigned int gain = (it.z >> 16) & 1u;
+            const int lr = (int)(it.w >> 16), bl = (int)(it.w & 0xffffu);
+            const float* xb = S.xs + bl;
+            float acc = 0.0f, scale;
+            auto dot = [&](int pos, float v) { acc = fmaf(v, xb[pos * kChunkPad], acc); };
+            const FastClass* rec = F.cls + ci;
+            if (fam == kPathEven) {
+                const Quad q1 = load_quad(rec, 1), q2 = load_quad(rec, 2), q3 = load_quad(rec, 3);
+                const Quad q0 = load_quad(rec, 0);
+                scale = bits_to_float(q3.x);
+                even_fast(F, local, q0.z, q1, q2, dot);
+            } else if (fam == kPathSlow) {
+                decode_generic(G, local, kN12, [&](int pos, int v) { acc = fmaf((float)v, xb[pos * kChunkPad], acc); },
+                               &scale);
+            } else {
+                const Quad q0 = load_quad(rec, 0), q1 = load_quad(rec, 1);
+                unsigned int g, r;
+                divmod_odd(local, q0.z, bits_to_float(q1.w), &g, &r);
+                const unsigned int cw = __ldg(F.golay + g);
+                scale = bits_to_float(q1.z);
+                if (fam == kPathOdd2)
+                    odd_fast<2>(r, q0.z, q1.x, q1.y, cw, dot);
+                else
+                    odd_fast<3>(r, q0.z, q1.x, q1.y, cw, dot);
+            }
+            const float2 cg = S.cent[lr];
+            S.part[lr * kChunk + bl] = acc * (scale * (gain ? cg.y : cg.x));
+            }
+        }
+        __syncthreads();
+
+        // ---- phase 3: fixed-order row sums ----
+        if (warp < rows) {
+            float s = 0.0f;
+            for (int b = lane; b < cbn; b += 32) s += S.part[warp * kChunk + b];
+            row_acc += warp_sum(s);
+        }
+        // the next chunk's staging overwrites xs/items only; part is rewritten after two barriers
+    }
+
+    if (warp < rows) {
+        const int r = row0 + warp;
+        const float t = tail_dot(mv, r, S.xs_tail, lane);
+        if (lane == 0) store_y<YT>(y, r, fmaf(row_acc, S.rscale[warp], t));
+    }
+    __syncthreads();
+    if (tid == 0 && S.error) atomicOr(err_flag, 1);
+}
+
+inline size_t sorted_smem_bytes(int nb) { return sizeof(SortedSmem) + (((size_t)kRows * nb * 6 + 15) & ~(size_t)15) + 16; }
+
+}  // namespace llvq

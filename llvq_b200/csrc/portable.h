@@ -8,9 +8,11 @@
 #if defined(__CUDACC__)
 #define LLVQ_DEV __device__ __forceinline__
 #define LLVQ_HD __host__ __device__ __forceinline__
+#define LLVQ_CONSTEXPR __host__ __device__ constexpr
 #else
 #define LLVQ_DEV inline
 #define LLVQ_HD inline
+#define LLVQ_CONSTEXPR constexpr
 #endif
 
 namespace llvq {

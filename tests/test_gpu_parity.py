@@ -85,7 +85,7 @@ def test_decode_blocks_edge_records(rt, oracle):
     assert np.array_equal(pts.cpu().numpy(), ref_pts)
     assert np.array_equal(shell.cpu().numpy(), ref_shell) and shell[-1].item() == 255
     assert np.array_equal(gn.cpu().numpy(), ref_gain)
-    # empty input is a no-op
+    # empty input is a no-op, even with null pointers
     e_pts, e_shell, e_gain = rt.decode_blocks(torch.empty(0, dtype=torch.uint8, device="cuda"))
     assert e_pts.shape == (0, 24)
 
