@@ -74,6 +74,7 @@ struct llvq_runtime {
     void* d_lut_off = nullptr;
     uint64_t fingerprint = 0;
     int max_smem_optin = 0;
+    int sm_count = 0;
 };
 
 struct llvq_matrix {
@@ -123,12 +124,13 @@ int launch_gemv_generic(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
 }
 
 // The class-sorted kernel serves every matrix whose 8-row code slab fits in shared
-// memory (d_in up to roughly 90 000); beyond that the generic kernel takes over.
+// memory (d_in up to roughly 90 000) and whose activation pointer allows 16-byte
+// loads; anything else goes to the generic kernel.
 template <typename XT, typename YT>
 int launch_gemv(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
     llvq_runtime* rt = m->rt;
     const size_t smem = sorted_smem_bytes(m->nb);
-    if (smem > (size_t)rt->max_smem_optin) return launch_gemv_generic<XT, YT>(m, x, y, s);
+    if (smem > (size_t)rt->max_smem_optin || ((uintptr_t)x & 15u)) return launch_gemv_generic<XT, YT>(m, x, y, s);
     auto kern = gemv_sorted_kernel<XT, YT>;
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int grid = (m->d_out + kRows - 1) / kRows;
@@ -290,6 +292,7 @@ int llvq_runtime_create(int device, llvq_runtime** out) {
     std::unique_ptr<llvq_runtime> rt(new llvq_runtime);
     rt->device = device;
     rt->max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+    rt->sm_count = prop.multiProcessorCount;
     const Codebook& cb = rt->cb;
     if (cb.classes.size() != (size_t)kMaxClasses || cb.n_classes12 != 301 || cb.total13 != kN13 || cb.total12 != kN12)
         return fail(LLVQ_ERR_CODEBOOK, "class enumeration does not cover the ball: %zu classes, N=%llu", cb.classes.size(),

@@ -426,8 +426,7 @@ void build_fast_tables(const Codebook& cb, FastTablesHost& out) {
                 f.b0 = on_base[key_on];
                 f.b1 = off_base[key_off];
                 const int v0 = c.val_a[0], v1 = c.n_a > 1 ? c.val_a[1] : c.val_a[0];
-                f.b2 = (unsigned int)(uint8_t)v0 | (unsigned int)(uint8_t)v1 << 8 |
-                       (unsigned int)(uint8_t)(int8_t)-v0 << 16 | (unsigned int)(uint8_t)(int8_t)-v1 << 24;
+                f.b2 = (unsigned int)v0 | (unsigned int)v1 << 8 | (unsigned int)v0 << 16 | (unsigned int)v1 << 24;
                 unsigned int vt_off = 0;
                 for (int j = 0; j < c.n_b; ++j) vt_off |= (unsigned int)c.val_b[j] << (8 * j);
                 f.b3 = vt_off;

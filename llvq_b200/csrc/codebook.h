@@ -115,7 +115,8 @@ constexpr unsigned int kOffLutCap = 131072;  // largest off-support arrangement 
 //             m_off, m_on = magic multipliers for division by a_off / a_on
 //             sh   = s_off | s_on << 8 | golay_base << 16
 //   q2  even: on_base, off_base = first entry of the class's arrangement tables;
-//             vt_on  = bytes {+v0, +v1, -v0, -v1} indexed by (sign << 1 | kind)
+//             vt_on  = bytes {v0, v1, v0, v1}: |value| indexed by the low 2 bits of a
+//                      support slot's code (sign << 1 | kind)
 //             vt_off = bytes {f0, f1, f2, 0} indexed by off-support kind (zero run = 0)
 //   q3  even: scale as float bits
 struct alignas(16) FastClass {

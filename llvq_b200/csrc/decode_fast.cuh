@@ -196,6 +196,18 @@ LLVQ_HD void odd_fast(unsigned int rank, unsigned int m_arr, unsigned int cum, u
     }
 }
 
+// Byte permute of the 8 bytes {a, b} (CUDA __byte_perm semantics, selector nibbles 0-7).
+LLVQ_HD unsigned int byte_perm32(unsigned int a, unsigned int b, unsigned int sel) {
+#if defined(__CUDA_ARCH__)
+    return __byte_perm(a, b, sel);
+#else
+    const unsigned long long v = (unsigned long long)b << 32 | a;
+    unsigned int r = 0;
+    for (int i = 0; i < 4; ++i) r |= (unsigned int)((v >> (8 * ((sel >> (4 * i)) & 7u))) & 0xffu) << (8 * i);
+    return r;
+#endif
+}
+
 // 16 bits -> 32 bits, bit s moves to bit 2s
 LLVQ_HD unsigned int spread16(unsigned int x) {
     x = (x | (x << 8)) & 0x00FF00FFu;
@@ -230,15 +242,19 @@ LLVQ_HD void even_fast(const FastTables& T, unsigned long long local, unsigned i
 #pragma unroll
     for (int pos = 0; pos < kDim; ++pos) {
         const bool bit = (cw >> pos) & 1u;
-        const unsigned int code = (bit ? on : off) & 3u;
-        const unsigned int byte = ((bit ? q2.z : q2.w) >> (8 * code)) & 0xffu;
+        const unsigned int t = bit ? on : off;
+        // |value| as a float without an integer->float conversion: the table byte is
+        // dropped into the mantissa of 2^23 (0x4B000000) and 2^23 is subtracted.
+        const unsigned int mag = byte_perm32(bit ? q2.z : q2.w, 0x4B000000u, (t & 3u) | 0x7440u);
+        float val = bits_to_float(mag) - 8388608.0f;
         if (bit) on >>= 2; else off >>= 2;
-        float val = (float)(int)(signed char)byte;
-        const bool nz = !bit && byte != 0;  // the zero run is recognised by its value
-        if (nz) {
-            val = bits_to_float(float_to_bits(val) ^ (sf << 31));
-            sf >>= 1;
-        }
+        // support slot: the sign travels in bit 1 of its code; off-support slot: the next
+        // free sign bit, consumed only by a non-zero value (the zero run is recognised by
+        // its value, never by its kind index)
+        const bool nz = !bit && mag != 0x4B000000u;
+        const unsigned int sbit = bit ? (t << 30) : (sf << 31);
+        val = bits_to_float(float_to_bits(val) ^ (sbit & 0x80000000u));
+        if (nz) sf >>= 1;
         emit(pos, val);
     }
 }

@@ -96,8 +96,35 @@ __device__ __forceinline__ unsigned long long slab_code48(const unsigned char* s
     return ((unsigned long long)hi << 32) | lo;
 }
 
+// xs[pos * kChunkPad + b] = x[b * 24 + pos] for the n = 24 * blocks activations of a chunk.
+// Eight consecutive activations (8 | 24, so they stay inside one block) per thread and step.
+template <typename XT>
+__device__ __forceinline__ void stage_x_chunk(float* xs, const XT* __restrict__ x, int n, int tid) {
+    for (int i = tid * 8; i < n; i += kThreads * 8) {
+        const int b = i / kDim, pos = i - b * kDim;
+        float v[8];
+        if constexpr (sizeof(XT) == 2) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(x + i);  // 16-byte aligned: i % 8 == 0
+            const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f2 = __half22float2(h[k]);
+                v[2 * k] = f2.x;
+                v[2 * k + 1] = f2.y;
+            }
+        } else {
+            const float4 lo = *reinterpret_cast<const float4*>(x + i);
+            const float4 hi = *reinterpret_cast<const float4*>(x + i + 4);
+            v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+            v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) xs[(pos + k) * kChunkPad + b] = v[k];
+    }
+}
+
 template <typename XT, typename YT>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restrict__ x, YT* __restrict__ y,
                    int* __restrict__ err_flag) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -116,6 +143,7 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
     }
     if (tid < 32) S.xs_tail[tid] = tid < mv.tail_w ? to_f32<XT>(x[nb * kDim + tid]) : 0.0f;
     if (tid == 0) S.error = 0;
+    __syncthreads();
 
     if (nb > 0) {
         // the slab start is 16-byte aligned because row0 is a multiple of 8 (48 * nb bytes per 8 rows)
@@ -131,13 +159,9 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
 
     for (int cb0 = 0; cb0 < nb; cb0 += kChunk) {
         const int cbn = min(kChunk, nb - cb0);
-        const int n_items = rows * cbn;
 
         // ---- stage the activation chunk (transposed) and reset the queue ----
-        for (int i = tid; i < cbn * kDim; i += kThreads) {
-            const int b = i / kDim, pos = i - b * kDim;
-            S.xs[pos * kChunkPad + b] = to_f32<XT>(x[(size_t)cb0 * kDim + i]);
-        }
+        stage_x_chunk<XT>(S.xs, x + (size_t)cb0 * kDim, cbn * kDim, tid);
         if (tid < 4) S.count[tid] = 0;
         if (tid == 0) S.ticket = 0;
         __syncthreads();
@@ -149,10 +173,8 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
         int slot[kItemsPerThread];
 #pragma unroll
         for (int k = 0; k < kItemsPerThread; ++k) {
-            const int f = tid + k * kThreads;
-            const bool active = f < n_items;
-            const int lr = active ? f / cbn : 0;
-            const int bl = active ? f - lr * cbn : 0;
+            const int lr = warp, bl = lane + 32 * k;  // one warp per row, a lane every 32 blocks
+            const bool active = lr < rows && bl < cbn;
             unsigned int path = 0, valid = 0;
             meta[k] = 0;
             loc[k] = 0;
@@ -171,18 +193,15 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
                     if (c.ci == -2) S.error = 1;
                 }
             }
-            // warp-aggregated slot allocation inside the family's queue
-            slot[k] = 0;
-#pragma unroll
-            for (unsigned int p = 0; p < 4; ++p) {
-                const unsigned int mask = __ballot_sync(0xffffffffu, valid && path == p);
-                if (mask) {
-                    int first = 0;
-                    if (lane == (__ffs(mask) - 1)) first = atomicAdd(&S.count[p], __popc(mask));
-                    first = __shfl_sync(0xffffffffu, first, __ffs(mask) - 1);
-                    if (valid && path == p) slot[k] = first + __popc(mask & ((1u << lane) - 1u));
-                }
-            }
+            // warp-aggregated slot allocation inside the family's queue: lanes of the same
+            // family find each other with match.any, the lowest one reserves the slots
+            const unsigned int grp = valid ? path : 4u;
+            const unsigned int peers = __match_any_sync(0xffffffffu, grp);
+            const int leader = __ffs(peers) - 1;
+            int first = 0;
+            if (valid && lane == leader) first = atomicAdd(&S.count[path], __popc(peers));
+            first = __shfl_sync(0xffffffffu, first, leader);
+            slot[k] = first + __popc(peers & ((1u << lane) - 1u));
         }
         __syncthreads();
         if (tid == 0) {
