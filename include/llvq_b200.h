@@ -157,6 +157,26 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x_dev, uint16_t* y_dev, int32_t 
 int llvq_gemv_f32_host(llvq_matrix* m, const float* x_host, float* y_host, llvq_stream_t stream);
 int llvq_gemv_h_host(llvq_matrix* m, const uint16_t* x_host, uint16_t* y_host, llvq_stream_t stream);
 
+/* No counterpart in the reference. Same contract as llvq_gemv_f32_host, for
+ * callers that must not cause a device allocation: code that runs while another
+ * part of the process is capturing a CUDA graph (cudaMalloc is illegal there), or a
+ * plugin hosted by a server whose device memory is handed out once at start-up and
+ * audited afterwards. The device staging of x and y is a fixed array inside the
+ * library image (LLVQ_STATIC_MAX_D_IN + LLVQ_STATIC_MAX_D_OUT floats, about 1.3 MB,
+ * held by every GPU that loads the library until the process exits), so the call
+ * performs no cudaMalloc/cudaFree, directly or through any library.
+ *   - matrices larger than the two limits are refused with LLVQ_ERR_INVALID;
+ *   - the first call on a device looks the array's address up; make that call
+ *     before any stream capture begins;
+ *   - all calls on one device share the array: two calls whose GPU work overlaps
+ *     (different streams or threads) race on it. The array keeps whatever the last
+ *     call left; nothing in it needs clearing because x is copied in whole and
+ *     every row of y is stored before it is copied out.
+ * Synchronises the stream, like llvq_gemv_f32_host. */
+#define LLVQ_STATIC_MAX_D_IN 65536
+#define LLVQ_STATIC_MAX_D_OUT 262144
+int llvq_gemv_f32_host_static(llvq_matrix* m, const float* x_host, float* y_host, llvq_stream_t stream);
+
 /* ---- decode probes --------------------------------------------------------- */
 
 /* Decode n packed 6-byte records on the GPU to their lattice points: 24 int8

@@ -471,6 +471,49 @@ int llvq_gemv_h_host(llvq_matrix* m, const uint16_t* x, uint16_t* y, llvq_stream
     return gemv_host<__half, __half>(m, (const __half*)x, (__half*)y, s);
 }
 
+// ---- host-buffer GEMV that never allocates ---------------------------------
+//
+// Device staging for llvq_gemv_f32_host_static. The array lives in the module
+// image, so every GPU that loads this library holds these bytes until the
+// process exits; nothing is ever cudaMalloc'd for it. Layout: the activation
+// first, then the result.
+static __device__ __align__(256) float g_static_stage[LLVQ_STATIC_MAX_D_IN + LLVQ_STATIC_MAX_D_OUT];
+
+namespace {
+// In host code `g_static_stage` is only a handle; the device address has to be
+// asked for, once per device, while that device is current.
+constexpr int kMaxDevices = 64;
+float* g_static_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+int llvq_gemv_f32_host_static(llvq_matrix* m, const float* x_host, float* y_host, llvq_stream_t stream) {
+    if (!m || !x_host || !y_host) return fail(LLVQ_ERR_INVALID, "gemv_f32_host_static: null argument");
+    if (m->d_in > LLVQ_STATIC_MAX_D_IN || m->d_out > LLVQ_STATIC_MAX_D_OUT)
+        return fail(LLVQ_ERR_INVALID,
+                    "gemv_f32_host_static: %d x %d exceeds the built-in staging area (d_out <= %d, d_in <= %d); use "
+                    "llvq_gemv_f32_host",
+                    m->d_out, m->d_in, LLVQ_STATIC_MAX_D_OUT, LLVQ_STATIC_MAX_D_IN);
+    const int dev = m->rt->device;
+    if (dev < 0 || dev >= kMaxDevices) return fail(LLVQ_ERR_INVALID, "gemv_f32_host_static: device %d", dev);
+    DeviceGuard g(dev);
+    if (!g_static_ptr[dev]) {  // first call on this device: resolve the symbol (do this before any stream capture)
+        void* p = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress(&p, g_static_stage));
+        g_static_ptr[dev] = static_cast<float*>(p);
+    }
+    float* xs = g_static_ptr[dev];
+    float* ys = xs + LLVQ_STATIC_MAX_D_IN;
+    cudaStream_t s = (cudaStream_t)stream;
+    // Nothing in the staging area has to start at zero: x is copied in full and the kernel
+    // stores every row of y. What the previous call left behind is simply overwritten.
+    CUDA_TRY(cudaMemcpyAsync(xs, x_host, (size_t)m->d_in * sizeof(float), cudaMemcpyHostToDevice, s));
+    int st = launch_gemv<float, float>(m, xs, ys, s);
+    if (st) return st;
+    CUDA_TRY(cudaMemcpyAsync(y_host, ys, (size_t)m->d_out * sizeof(float), cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaStreamSynchronize(s));
+    return LLVQ_OK;
+}
+
 int llvq_decode_blocks(llvq_runtime* rt, const uint8_t* codes, size_t n, int8_t* points, uint8_t* shell, uint8_t* gain,
                        llvq_stream_t stream) {
     if (!rt) return fail(LLVQ_ERR_INVALID, "decode_blocks: null runtime");
