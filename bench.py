@@ -159,6 +159,8 @@ def main():
     ap.add_argument("--layers", type=int, default=36, help="distinct layers per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-groups", action="store_true",
+                    help="launch q, k, v and gate, up separately instead of row-concatenated")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -182,13 +184,17 @@ def main():
     # the projections of different layers are independent units).
     t_gen = time.perf_counter()
     projs, xs_host, mats_meta = [], [], []
+    # q|k|v and gate|up read the same activation, so each group is one row-concatenated launch
+    # (llvq_matrix_upload_group); the seven projections are all computed either way.
+    groups = [[n] for n in PROJS] if args.no_groups else [["q", "k", "v"], ["o"], ["gate", "up"], ["down"]]
     for l in range(args.layers):
         layer = synth.make_layer(MODEL, CONFIG_ID, rank * 1000 + l)
-        for name in PROJS:
-            m = layer[name]
-            projs.append(rt.upload(m, tail_f16=True))
-            mats_meta.append((m.codes.size, m.tail.size, m.d_out, m.d_in))
-            xs_host.append(torch.from_numpy(synth.make_activation(m.d_in, 0x2000 + len(xs_host), np.float16)).pin_memory())
+        for names in groups:
+            ms = [layer[n] for n in names]
+            projs.append(rt.upload_group(ms, tail_f16=True) if len(ms) > 1 else rt.upload(ms[0], tail_f16=True))
+            mats_meta.append((sum(m.codes.size for m in ms), sum(m.tail.size for m in ms), sum(m.d_out for m in ms),
+                              ms[0].d_in))
+            xs_host.append(torch.from_numpy(synth.make_activation(ms[0].d_in, 0x2000 + len(xs_host), np.float16)).pin_memory())
     gen_s = time.perf_counter() - t_gen
     xs_dev = [x.cuda() for x in xs_host]
     ys_dev = [torch.empty(p.d_out, dtype=torch.float16, device="cuda") for p in projs]
@@ -261,7 +267,8 @@ def main():
         "metric": "dequant_gemv_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "qwen3-4b-layer-gemv", "layers_per_step": args.layers, "gemvs_per_step": len(projs),
+        "config": {"workload": "qwen3-4b-layer-gemv", "layers_per_step": args.layers, "projections_per_step": 7 * args.layers,
+                   "launches_per_step": len(projs), "grouping": "none" if args.no_groups else "q|k|v, o, gate|up, down",
                    "blocks_per_step": step_blocks, "algorithmic_bytes_per_step": step_bytes, "activations": "f16",
                    "l2": "every step streams %.0f MB of distinct codes (> 126 MB L2)" % (codes_bytes / 1e6),
                    "parallelism": f"replicas x{world}" if world > 1 else "single"},

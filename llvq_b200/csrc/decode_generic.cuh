@@ -130,6 +130,136 @@ LLVQ_HD int decode_generic(const DevTables& T, unsigned long long idx,
     return c.shell;
 }
 
+// ---------------------------------------------------------------------------
+// The same decoder restricted to the cap-12 ball, where every arrangement count
+// is below 2^31: the unranking runs in 32-bit arithmetic and M * c / n is the exact
+// division ((M * c) >> a) * o^-1 mod 2^32 for n = 2^a * o (the quotient is below
+// 2^31, so its low 32 bits are the quotient). This is what the GEMV runs for the
+// rare classes outside its table-driven families.
+// ---------------------------------------------------------------------------
+
+// o^-1 mod 2^32 | a << 32 for n = 2^a * o, n = 1..24 (index 0 unused)
+#if defined(__CUDACC__)
+static __device__ __constant__ unsigned long long kExactDiv[25] = {
+#else
+static const unsigned long long kExactDiv[25] = {
+#endif
+        0ull,
+        0x00000001ull | 0ull << 32,  // 1
+        0x00000001ull | 1ull << 32,  // 2
+        0xAAAAAAABull | 0ull << 32,  // 3
+        0x00000001ull | 2ull << 32,  // 4
+        0xCCCCCCCDull | 0ull << 32,  // 5
+        0xAAAAAAABull | 1ull << 32,  // 6
+        0xB6DB6DB7ull | 0ull << 32,  // 7
+        0x00000001ull | 3ull << 32,  // 8
+        0x38E38E39ull | 0ull << 32,  // 9
+        0xCCCCCCCDull | 1ull << 32,  // 10
+        0xBA2E8BA3ull | 0ull << 32,  // 11
+        0xAAAAAAABull | 2ull << 32,  // 12
+        0xC4EC4EC5ull | 0ull << 32,  // 13
+        0xB6DB6DB7ull | 1ull << 32,  // 14
+        0xEEEEEEEFull | 0ull << 32,  // 15
+        0x00000001ull | 4ull << 32,  // 16
+        0xF0F0F0F1ull | 0ull << 32,  // 17
+        0x38E38E39ull | 1ull << 32,  // 18
+        0x286BCA1Bull | 0ull << 32,  // 19
+        0xCCCCCCCDull | 2ull << 32,  // 20
+        0x3CF3CF3Dull | 0ull << 32,  // 21
+        0xBA2E8BA3ull | 1ull << 32,  // 22
+        0xE9BD37A7ull | 0ull << 32,  // 23
+        0xAAAAAAABull | 3ull << 32,  // 24
+};
+
+LLVQ_HD unsigned long long exact_div_params(int n) { return kExactDiv[n]; }
+
+template <typename CntT>
+LLVQ_HD int unrank_step32(unsigned int& rank, unsigned int& m, int& n, CntT& cnt, int k) {
+    const unsigned long long prm = exact_div_params(n);
+    const unsigned int inv = (unsigned int)prm, a = (unsigned int)(prm >> 32);
+    int chosen = k - 1;
+    for (int j = 0; j < k; ++j) {
+        const unsigned int c = (unsigned int)(cnt >> (8 * j)) & 0xffu;
+        if (c == 0) continue;
+        const unsigned int mj = (unsigned int)(((unsigned long long)m * c) >> a) * inv;
+        if (rank < mj || j == k - 1) {
+            m = mj;
+            chosen = j;
+            break;
+        }
+        rank -= mj;
+    }
+    cnt -= (CntT)1 << (8 * chosen);
+    n -= 1;
+    return chosen;
+}
+
+// Contract of decode_generic, for idx in the cap-12 ball (anything else is refused).
+template <class Emit>
+LLVQ_HD int decode_generic12(const DevTables& T, unsigned long long idx, Emit emit, float* scale) {
+    if (idx == 0 || idx > kN12) {
+#pragma unroll
+        for (int pos = 0; pos < kDim; ++pos) emit(pos, 0);
+        *scale = 0.0f;
+        return idx == 0 ? 0 : 255;
+    }
+    const unsigned long long i = idx - 1;
+    const int ci = find_class(T, i);
+    const DevClass c = T.cls[ci];
+    unsigned long long local = i - c.offset;
+    *scale = c.inv_norm;
+    unsigned int rank_a, m_a = (unsigned int)c.arr_a, rank_b = 0, m_b = (unsigned int)c.arr_b;
+    unsigned long long cnt_a = c.cnts_a;
+    unsigned int cnt_b = c.cnts_b;
+    int n_a, n_b = 0;
+    unsigned int cw, sw = 0, sf = 0;
+    if (c.odd) {
+        rank_a = (unsigned int)(local % m_a);
+        cw = T.golay[local / m_a];
+        n_a = kDim;
+    } else {
+        sf = (unsigned int)local & ((1u << c.free_n) - 1u);
+        local >>= c.free_n;
+        const int wb = c.w ? c.w - 1 : 0;
+        sw = (unsigned int)local & ((1u << wb) - 1u);
+        local >>= wb;
+        const unsigned int q = (unsigned int)local;  // gamma * a_on * a_off < 2^28
+        rank_b = q % m_b;
+        const unsigned int q2 = q / m_b;
+        rank_a = q2 % m_a;
+        cw = T.golay[c.golay_base + q2 / m_a];
+        if (c.w) sw |= (unsigned int)((popc32(sw) & 1) ^ c.p_req) << (c.w - 1);
+        n_a = c.w;
+        n_b = kDim - c.w;
+    }
+#pragma unroll 1
+    for (int pos = 0; pos < kDim; ++pos) {
+        const unsigned int bit = (cw >> pos) & 1u;
+        int val;
+        if (c.odd || bit) {
+            const int j = unrank_step32(rank_a, m_a, n_a, cnt_a, (int)c.n_a);
+            const int v = (int)((c.vals_a >> (4 * j)) & 15u);
+            if (c.odd) {
+                const int a = (v & 3) == 3 ? v : -v;
+                val = bit ? a : -a;
+            } else {
+                val = (sw & 1u) ? -v : v;
+                sw >>= 1;
+            }
+        } else {
+            const int j = unrank_step32(rank_b, m_b, n_b, cnt_b, (int)c.n_b);
+            const int v = (int)((c.vals_b >> (4 * j)) & 15u);
+            val = v;
+            if (v) {
+                val = (sf & 1u) ? -v : v;
+                sf >>= 1;
+            }
+        }
+        emit(pos, val);
+    }
+    return c.shell;
+}
+
 // Big-endian 48-bit record of block b: idx = v >> 1, gain = v & 1
 // (llvq-search/src/pack.rs:113-137, llvq-artifact/src/format.rs:362-368).
 LLVQ_HD unsigned long long load_code48(const unsigned char* codes, size_t b) {

@@ -6,9 +6,10 @@
 // tile is then processed in chunks of up to kChunk column blocks:
 //
 //   phase 1  every thread takes blocks of the chunk: 48-bit big-endian record ->
-//            (index, gain) -> class search -> local rank -> decode family. Blocks
-//            are counted per family with warp-aggregated shared-memory atomics.
-//   phase 1b items are written into one queue, grouped by family.
+//            (index, gain) -> class search -> local rank -> decode family. The
+//            block's item is stored at its own position; its position is appended
+//            to the list of its family (match.any + one shared-memory atomic per
+//            family and warp).
 //   phase 2  warps pull batches of 32 same-family items and run that family's
 //            branch-free decoder (decode_fast.cuh) with the dot product against
 //            the staged activation fused into its position loop; the block's
@@ -31,25 +32,32 @@
 
 namespace llvq {
 
-constexpr int kRows = 8;                             // rows per CTA
-constexpr int kChunk = 128;                          // column blocks per chunk
-constexpr int kChunkPad = kChunk + 1;                // xs row stride (odd: conflict-free transposition)
-constexpr int kThreads = 256;                        // 8 warps, one per row in phase 3
-constexpr int kItems = kRows * kChunk;               // 1024 blocks per chunk
-constexpr int kItemsPerThread = kItems / kThreads;   // 4
-constexpr unsigned int kSpinLimit = 1u << 22;        // bounded wait on the bulk copy
+constexpr int kChunk = 128;                    // column blocks per chunk
+constexpr int kChunkPad = kChunk + 1;          // xs row stride (odd: conflict-free transposition)
+constexpr int kThreads = 256;                  // 8 warps
+constexpr int kWarps = kThreads / 32;
+constexpr unsigned int kSpinLimit = 1u << 22;  // bounded wait on the bulk copy
 
-struct SortedSmem {
+// ROWS = rows per CTA (8 or 16; a multiple of 8 keeps the code slab 16-byte aligned).
+// More rows per CTA mean more batches per chunk and so a better balance between the
+// warps of phase 2; fewer rows mean more CTAs for matrices with few rows.
+template <int ROWS>
+struct alignas(16) SortedSmem {
+    static constexpr int kItems = ROWS * kChunk;
     unsigned long long mbar;
-    int count[4];   // items per family in this chunk
-    int base[4];    // first queue slot of each family
-    int ticket;     // next batch to hand out
+    int count[4];  // items per family in this chunk
+    int ticket;    // next batch to hand out
     int error;
-    float2 cent[kRows];
-    float rscale[kRows];
+    int pad[2];
+    float2 cent[ROWS];
+    float rscale[ROWS];
     float xs_tail[32];
     float part[kItems];
-    uint4 items[kItems];
+    uint2 items[kItems];  // local rank (47 bits) | class << 47 | gain << 56, at the block's own slot
+    // Slots (row << 7 | block) of each family's blocks. Two families share one array, one
+    // growing from the front and one from the back: even / odd-2 in list_a, odd-3 / generic in list_b.
+    unsigned short list_a[kItems];
+    unsigned short list_b[kItems];
     float xs[kDim * kChunkPad];
     // followed by the code slab (dynamic size)
 };
@@ -123,20 +131,32 @@ __device__ __forceinline__ void stage_x_chunk(float* xs, const XT* __restrict__ 
     }
 }
 
-template <typename XT, typename YT>
-__global__ void __launch_bounds__(kThreads, 3)
+// Position of entry i of a family's list inside its shared array.
+template <int ROWS>
+__device__ __forceinline__ unsigned short* list_slot(SortedSmem<ROWS>& S, unsigned int fam, int i) {
+    constexpr int kItems = SortedSmem<ROWS>::kItems;
+    unsigned short* base = (fam == kPathEven || fam == kPathOdd2) ? S.list_a : S.list_b;
+    const bool front = fam == kPathEven || fam == kPathOdd3;
+    return base + (front ? i : kItems - 1 - i);
+}
+
+template <typename XT, typename YT, int ROWS>
+__global__ void __launch_bounds__(kThreads, 4)
 gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restrict__ x, YT* __restrict__ y,
                    int* __restrict__ err_flag) {
+    using Smem = SortedSmem<ROWS>;
+    constexpr int kRowsPerWarp = ROWS / kWarps;
+    static_assert(ROWS % kWarps == 0 && sizeof(Smem) % 16 == 0, "rows split evenly; slab starts 16-byte aligned");
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    SortedSmem& S = *reinterpret_cast<SortedSmem*>(smem_raw);
-    unsigned char* slab = smem_raw + sizeof(SortedSmem);
+    Smem& S = *reinterpret_cast<Smem*>(smem_raw);
+    unsigned char* slab = smem_raw + sizeof(Smem);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nb = mv.nb;
-    const int row0 = blockIdx.x * kRows;
-    const int rows = min(kRows, mv.d_out - row0);
+    const int row0 = blockIdx.x * ROWS;
+    const int rows = min(ROWS, mv.d_out - row0);
 
-    if (tid < kRows) {
+    if (tid < ROWS) {
         const int r = min(row0 + tid, mv.d_out - 1);
         S.cent[tid] = mv.cent[r];
         S.rscale[tid] = mv.rscale[r];
@@ -155,74 +175,49 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
         }
     }
 
-    float row_acc = 0.0f;  // phase 3: lane-replicated sum of the row owned by this warp
+    float row_acc[kRowsPerWarp];  // phase 3: lane-replicated sums of the rows owned by this warp
+#pragma unroll
+    for (int q = 0; q < kRowsPerWarp; ++q) row_acc[q] = 0.0f;
 
     for (int cb0 = 0; cb0 < nb; cb0 += kChunk) {
         const int cbn = min(kChunk, nb - cb0);
 
-        // ---- stage the activation chunk (transposed) and reset the queue ----
+        // ---- stage the activation chunk (transposed) and reset the queues ----
         stage_x_chunk<XT>(S.xs, x + (size_t)cb0 * kDim, cbn * kDim, tid);
         if (tid < 4) S.count[tid] = 0;
         if (tid == 0) S.ticket = 0;
         __syncthreads();
 
-        // ---- phase 1: classify ----
-        unsigned long long loc[kItemsPerThread];
-        unsigned int meta[kItemsPerThread];  // ci | gain << 16 | path << 20 | valid << 24
-        unsigned int where[kItemsPerThread];  // lr << 16 | b_local
-        int slot[kItemsPerThread];
-#pragma unroll
-        for (int k = 0; k < kItemsPerThread; ++k) {
-            const int lr = warp, bl = lane + 32 * k;  // one warp per row, a lane every 32 blocks
-            const bool active = lr < rows && bl < cbn;
-            unsigned int path = 0, valid = 0;
-            meta[k] = 0;
-            loc[k] = 0;
-            where[k] = (unsigned int)lr << 16 | (unsigned int)bl;
-            if (active) {
+        // ---- phase 1: classify; a warp takes rows warp, warp + 8, ..., a lane every 32nd block ----
+#pragma unroll 1
+        for (int k = 0; k < kRowsPerWarp * (kChunk / 32); ++k) {
+            const int lr = warp + kWarps * (k / (kChunk / 32)), bl = lane + 32 * (k % (kChunk / 32));
+            const int f = lr * kChunk + bl;
+            unsigned int path = 4u;  // 4: nothing to decode
+            if (lr < rows && bl < cbn) {
                 const unsigned long long v = slab_code48(slab, lr * nb + cb0 + bl);
                 const Classified c = classify12(F, v >> 1);
                 if (c.ci >= 0) {
-                    valid = 1;
                     path = c.path;
-                    // the generic decoder wants the index itself
-                    loc[k] = path == kPathSlow ? (v >> 1) : c.local;
-                    meta[k] = (unsigned int)c.ci | (unsigned int)(v & 1ull) << 16 | path << 20 | 1u << 24;
+                    const unsigned long long loc = path == kPathSlow ? (v >> 1) : c.local;  // generic wants the index
+                    S.items[f] = make_uint2((unsigned int)loc, (unsigned int)(loc >> 32) | (unsigned int)c.ci << 15 |
+                                                                   (unsigned int)(v & 1ull) << 24);
                 } else {
-                    S.part[lr * kChunk + bl] = 0.0f;  // origin, or refused index: contributes nothing
+                    S.part[f] = 0.0f;  // origin, or refused index: contributes nothing
                     if (c.ci == -2) S.error = 1;
                 }
             }
-            // warp-aggregated slot allocation inside the family's queue: lanes of the same
-            // family find each other with match.any, the lowest one reserves the slots
-            const unsigned int grp = valid ? path : 4u;
-            const unsigned int peers = __match_any_sync(0xffffffffu, grp);
+            // lanes of the same family find each other; the lowest one reserves their list slots
+            const unsigned int peers = __match_any_sync(0xffffffffu, path);
             const int leader = __ffs(peers) - 1;
             int first = 0;
-            if (valid && lane == leader) first = atomicAdd(&S.count[path], __popc(peers));
+            if (path < 4u && lane == leader) first = atomicAdd(&S.count[path], __popc(peers));
             first = __shfl_sync(0xffffffffu, first, leader);
-            slot[k] = first + __popc(peers & ((1u << lane) - 1u));
-        }
-        __syncthreads();
-        if (tid == 0) {
-            // queue order = processing order: generic first (longest single items), then odd, then even
-            S.base[kPathSlow] = 0;
-            S.base[kPathOdd3] = S.count[kPathSlow];
-            S.base[kPathOdd2] = S.base[kPathOdd3] + S.count[kPathOdd3];
-            S.base[kPathEven] = S.base[kPathOdd2] + S.count[kPathOdd2];
-        }
-        __syncthreads();
-#pragma unroll
-        for (int k = 0; k < kItemsPerThread; ++k) {
-            if (meta[k] >> 24) {
-                const unsigned int p = (meta[k] >> 20) & 3u;
-                S.items[S.base[p] + slot[k]] =
-                    make_uint4((unsigned int)loc[k], (unsigned int)(loc[k] >> 32), meta[k], where[k]);
-            }
+            if (path < 4u) *list_slot<ROWS>(S, path, first + __popc(peers & ((1u << lane) - 1u))) = (unsigned short)f;
         }
         __syncthreads();
 
-        // ---- phase 2: decode + dot, one family per batch ----
+        // ---- phase 2: decode + dot, one family per batch; longest batches first ----
         const int n_slow = S.count[kPathSlow], n_o3 = S.count[kPathOdd3], n_o2 = S.count[kPathOdd2],
                   n_ev = S.count[kPathEven];
         const int b_slow = (n_slow + 31) >> 5, b_o3 = (n_o3 + 31) >> 5, b_o2 = (n_o2 + 31) >> 5, b_ev = (n_ev + 31) >> 5;
@@ -235,70 +230,79 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
             unsigned int fam;
             int first, count;
             if (t < b_slow) {
-                fam = kPathSlow; first = S.base[kPathSlow] + 32 * t; count = n_slow - 32 * t;
+                fam = kPathSlow; first = 32 * t; count = n_slow - first;
             } else if (t < b_slow + b_o3) {
-                const int u = t - b_slow;
-                fam = kPathOdd3; first = S.base[kPathOdd3] + 32 * u; count = n_o3 - 32 * u;
+                fam = kPathOdd3; first = 32 * (t - b_slow); count = n_o3 - first;
             } else if (t < b_slow + b_o3 + b_o2) {
-                const int u = t - b_slow - b_o3;
-                fam = kPathOdd2; first = S.base[kPathOdd2] + 32 * u; count = n_o2 - 32 * u;
+                fam = kPathOdd2; first = 32 * (t - b_slow - b_o3); count = n_o2 - first;
             } else {
-                const int u = t - b_slow - b_o3 - b_o2;
-                fam = kPathEven; first = S.base[kPathEven] + 32 * u; count = n_ev - 32 * u;
+                fam = kPathEven; first = 32 * (t - b_slow - b_o3 - b_o2); count = n_ev - first;
             }
             if (lane < count) {  // the last batch of a family may be ragged
-            const uint4 it = S.items[first + lane];
-            const unsigned long long local = (unsigned long long)it.y << 32 | it.x;
-            const int ci = (int)(it.z & 0xffffu);
-            const unsigned int gain = (it.z >> 16) & 1u;
-            const int lr = (int)(it.w >> 16), bl = (int)(it.w & 0xffffu);
-            const float* xb = S.xs + bl;
-            float acc = 0.0f, scale;
-            auto dot = [&](int pos, float v) { acc = fmaf(v, xb[pos * kChunkPad], acc); };
-            const FastClass* rec = F.cls + ci;
-            if (fam == kPathEven) {
-                const Quad q1 = load_quad(rec, 1), q2 = load_quad(rec, 2), q3 = load_quad(rec, 3);
-                const Quad q0 = load_quad(rec, 0);
-                scale = bits_to_float(q3.x);
-                even_fast(F, local, q0.z, q1, q2, dot);
-            } else if (fam == kPathSlow) {
-                decode_generic(G, local, kN12, [&](int pos, int v) { acc = fmaf((float)v, xb[pos * kChunkPad], acc); },
-                               &scale);
-            } else {
-                const Quad q0 = load_quad(rec, 0), q1 = load_quad(rec, 1);
-                unsigned int g, r;
-                divmod_odd(local, q0.z, bits_to_float(q1.w), &g, &r);
-                const unsigned int cw = __ldg(F.golay + g);
-                scale = bits_to_float(q1.z);
-                if (fam == kPathOdd2)
-                    odd_fast<2>(r, q0.z, q1.x, q1.y, cw, dot);
-                else
-                    odd_fast<3>(r, q0.z, q1.x, q1.y, cw, dot);
-            }
-            const float2 cg = S.cent[lr];
-            S.part[lr * kChunk + bl] = acc * (scale * (gain ? cg.y : cg.x));
+                const int f = *list_slot<ROWS>(S, fam, first + lane);
+                const uint2 it = S.items[f];
+                const unsigned long long local = (unsigned long long)(it.y & 0x7fffu) << 32 | it.x;
+                const int ci = (int)((it.y >> 15) & 0x1ffu);
+                const unsigned int gain = (it.y >> 24) & 1u;
+                const int lr = f >> 7, bl = f & (kChunk - 1);
+                const float* xb = S.xs + bl;
+                float acc = 0.0f, scale;
+                auto dot = [&](int pos, float v) { acc = fmaf(v, xb[pos * kChunkPad], acc); };
+                const FastClass* rec = F.cls + ci;
+                if (fam == kPathEven) {
+                    const Quad q0 = load_quad(rec, 0), q1 = load_quad(rec, 1), q2 = load_quad(rec, 2),
+                               q3 = load_quad(rec, 3);
+                    scale = bits_to_float(q3.x);
+                    even_fast(F, local, q0.z, q1, q2, dot);
+                } else if (fam == kPathSlow) {
+                    decode_generic12(G, local, [&](int pos, int v) { acc = fmaf((float)v, xb[pos * kChunkPad], acc); },
+                                     &scale);
+                } else {
+                    const Quad q0 = load_quad(rec, 0), q1 = load_quad(rec, 1);
+                    unsigned int g, r;
+                    divmod_odd(local, q0.z, bits_to_float(q1.w), &g, &r);
+                    const unsigned int cw = __ldg(F.golay + g);
+                    scale = bits_to_float(q1.z);
+                    if (fam == kPathOdd2)
+                        odd_fast<2>(r, q0.z, q1.x, q1.y, cw, dot);
+                    else
+                        odd_fast<3>(r, q0.z, q1.x, q1.y, cw, dot);
+                }
+                const float2 cg = S.cent[lr];
+                S.part[f] = acc * (scale * (gain ? cg.y : cg.x));
             }
         }
         __syncthreads();
 
         // ---- phase 3: fixed-order row sums ----
-        if (warp < rows) {
-            float s = 0.0f;
-            for (int b = lane; b < cbn; b += 32) s += S.part[warp * kChunk + b];
-            row_acc += warp_sum(s);
+#pragma unroll
+        for (int q = 0; q < kRowsPerWarp; ++q) {
+            const int lr = warp + kWarps * q;
+            if (lr < rows) {
+                float s = 0.0f;
+                for (int b = lane; b < cbn; b += 32) s += S.part[lr * kChunk + b];
+                row_acc[q] += warp_sum(s);
+            }
         }
         // the next chunk's staging overwrites xs/items only; part is rewritten after two barriers
     }
 
-    if (warp < rows) {
-        const int r = row0 + warp;
-        const float t = tail_dot(mv, r, S.xs_tail, lane);
-        if (lane == 0) store_y<YT>(y, r, fmaf(row_acc, S.rscale[warp], t));
+#pragma unroll
+    for (int q = 0; q < kRowsPerWarp; ++q) {
+        const int lr = warp + kWarps * q;
+        if (lr < rows) {
+            const int r = row0 + lr;
+            const float t = tail_dot(mv, r, S.xs_tail, lane);
+            if (lane == 0) store_y<YT>(y, r, fmaf(row_acc[q], S.rscale[lr], t));
+        }
     }
     __syncthreads();
     if (tid == 0 && S.error) atomicOr(err_flag, 1);
 }
 
-inline size_t sorted_smem_bytes(int nb) { return sizeof(SortedSmem) + (((size_t)kRows * nb * 6 + 15) & ~(size_t)15) + 16; }
+template <int ROWS>
+inline size_t sorted_smem_bytes(int nb) {
+    return sizeof(SortedSmem<ROWS>) + (((size_t)ROWS * nb * 6 + 15) & ~(size_t)15) + 16;
+}
 
 }  // namespace llvq
