@@ -34,6 +34,9 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# DRAM bytes (read + write) the GEMV kernel moved for the four grouped launches of one layer in the
+# ncu capture summarised in profiles/gemv_sorted_kernel_qwen3_4b_layer.md (5.16 + 3.62 + 14.31 + 7.34 MB).
+NCU_DRAM_BYTES_PER_LAYER = 30.43e6
 MODEL = "qwen3-4b"
 PROJS = ["q", "k", "v", "o", "gate", "up", "down"]
 CONFIG_ID = 1
@@ -275,7 +278,8 @@ def main():
         "token_equiv_per_s": world * (args.layers / 36.0) / (ms_step * 1e-3),
         "gblocks_per_s": world * step_blocks / (ms_step * 1e-3) / 1e9,
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
-                     "traffic": None, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBps": per_gpu_gbs / 8000.0,
+                     "traffic": (NCU_DRAM_BYTES_PER_LAYER * args.layers / len(projs)) if not args.no_groups else None,
+                     "algorithmic_bytes_per_launch": step_bytes / len(projs), "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBps": per_gpu_gbs / 8000.0,
                      "kernel": "gemv", "launches": launches, "avg_launch_us": ms_total * 1e3 / max(launches, 1),
                      "two_term": {"t_bytes_ms": t_bytes * 1e3, "t_alu_ms": t_alu * 1e3,
                                   "frac": max(t_bytes, t_alu) * 1e3 / ms_step, "ops_per_block": 184}},

@@ -14,6 +14,7 @@
 
 #include "../../include/llvq_b200.h"
 #include "codebook.h"
+#include "gemm_tc.cuh"
 #include "gemv_sorted.cuh"
 #include "kernels_generic.cuh"
 
@@ -75,6 +76,9 @@ struct llvq_runtime {
     uint64_t fingerprint = 0;
     int max_smem_optin = 0;
     int sm_count = 0;
+    // split-K partials of the batched GEMM; grown on demand, shared by all matrices of the runtime
+    float* gemm_ws = nullptr;
+    size_t gemm_ws_bytes = 0;
 };
 
 struct llvq_matrix {
@@ -280,6 +284,7 @@ void llvq_runtime_destroy(llvq_runtime* rt) {
     cudaFree(rt->d_lut);
     cudaFree(rt->d_golay);
     cudaFree(rt->d_err);
+    cudaFree(rt->gemm_ws);
     cudaFree(rt->d_fcls);
     cudaFree(rt->d_lut_on);
     cudaFree(rt->d_lut_off);
@@ -464,13 +469,62 @@ int llvq_gemv_f32x_h(llvq_matrix* m, const float* x, uint16_t* y, llvq_stream_t 
     return gemv_entry<float, __half>(m, x, (__half*)y, s);
 }
 
-int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, llvq_stream_t s) {
+int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, llvq_stream_t stream) {
     if (!m || !x || !y || batch <= 0) return fail(LLVQ_ERR_INVALID, "gemm_h: bad argument");
-    // Until the batched kernel lands the batch is served row by row, exactly as the
-    // reference's drive_rows does.
-    for (int b = 0; b < batch; ++b) {
-        int st = gemv_entry<__half, __half>(m, (const __half*)x + (size_t)b * m->d_in, (__half*)y + (size_t)b * m->d_out, s);
-        if (st) return st;
+    if (((uintptr_t)x & 1u) || ((uintptr_t)y & 1u)) return fail(LLVQ_ERR_INVALID, "gemm_h: misaligned buffer");
+    llvq_runtime* rt = m->rt;
+    DeviceGuard g(rt->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (batch < 16) {
+        // below 16 rows the contraction is too thin for the tensor cores: one fused GEMV per row,
+        // as the reference's drive_rows does (llvq-llm/src/model.rs:497-536)
+        for (int b = 0; b < batch; ++b) {
+            int st = launch_gemv<__half, __half>(m, (const __half*)x + (size_t)b * m->d_in,
+                                                 (__half*)y + (size_t)b * m->d_out, s);
+            if (st) return st;
+        }
+        return LLVQ_OK;
+    }
+    const int tiles = (m->d_out + kGM - 1) / kGM;
+    const int chunks = (m->nb + kGKB - 1) / kGKB;
+    // enough CTAs for two per SM: split the column chunks when the row tiles alone are too few
+    int splits = chunks > 0 ? (2 * rt->sm_count + tiles - 1) / tiles : 0;
+    if (splits > chunks) splits = chunks;
+    const int cps = splits > 0 ? (chunks + splits - 1) / splits : 1;
+    splits = chunks > 0 ? (chunks + cps - 1) / cps : 0;
+    const size_t need = (size_t)(splits > 0 ? splits : 1) * kGMaxN * m->d_out * sizeof(float);
+    if (need > rt->gemm_ws_bytes) {  // first use or a larger matrix: (re)allocate the workspace
+        CUDA_TRY(cudaStreamSynchronize(s));
+        CUDA_TRY(cudaFree(rt->gemm_ws));
+        rt->gemm_ws = nullptr;
+        rt->gemm_ws_bytes = 0;
+        CUDA_TRY(cudaMalloc((void**)&rt->gemm_ws, need));
+        rt->gemm_ws_bytes = need;
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes()));
+        attr_set = true;
+    }
+    const MatrixView mv = m->view();
+    for (int b0 = 0; b0 < batch; b0 += kGMaxN) {
+        const int nb_rows = batch - b0 < kGMaxN ? batch - b0 : kGMaxN;
+        GemmArgs ga;
+        ga.x = (const __half*)x + (size_t)b0 * m->d_in;
+        ga.ws = rt->gemm_ws;
+        ga.batch = nb_rows;
+        ga.n_pad = (nb_rows + 15) & ~15;
+        ga.chunks_per_split = cps;
+        ga.x_vec_ok = ((m->d_in & 7) == 0 && ((uintptr_t)ga.x & 15u) == 0) ? 1 : 0;
+        if (splits > 0) {
+            gemm_tc_kernel<<<dim3(tiles, splits), kGThreads, gemm_smem_bytes(), s>>>(rt->F, rt->T, mv, ga, rt->d_err);
+            g_launches++;
+            CUDA_TRY(cudaGetLastError());
+        }
+        gemm_reduce_kernel<<<dim3((m->d_out + 127) / 128, nb_rows), 128, 0, s>>>(
+            mv, ga.x, rt->gemm_ws, (__half*)y + (size_t)b0 * m->d_out, nb_rows, ga.n_pad, splits);
+        g_launches++;
+        CUDA_TRY(cudaGetLastError());
     }
     return LLVQ_OK;
 }

@@ -139,39 +139,44 @@ LLVQ_HD int decode_generic(const DevTables& T, unsigned long long idx,
 // ---------------------------------------------------------------------------
 
 // o^-1 mod 2^32 | a << 32 for n = 2^a * o, n = 1..24 (index 0 unused)
+#define LLVQ_EXACT_DIV_TABLE \
+    { 0ull, \
+      0x00000001ull | 0ull << 32, \
+      0x00000001ull | 1ull << 32, \
+      0xAAAAAAABull | 0ull << 32, \
+      0x00000001ull | 2ull << 32, \
+      0xCCCCCCCDull | 0ull << 32, \
+      0xAAAAAAABull | 1ull << 32, \
+      0xB6DB6DB7ull | 0ull << 32, \
+      0x00000001ull | 3ull << 32, \
+      0x38E38E39ull | 0ull << 32, \
+      0xCCCCCCCDull | 1ull << 32, \
+      0xBA2E8BA3ull | 0ull << 32, \
+      0xAAAAAAABull | 2ull << 32, \
+      0xC4EC4EC5ull | 0ull << 32, \
+      0xB6DB6DB7ull | 1ull << 32, \
+      0xEEEEEEEFull | 0ull << 32, \
+      0x00000001ull | 4ull << 32, \
+      0xF0F0F0F1ull | 0ull << 32, \
+      0x38E38E39ull | 1ull << 32, \
+      0x286BCA1Bull | 0ull << 32, \
+      0xCCCCCCCDull | 2ull << 32, \
+      0x3CF3CF3Dull | 0ull << 32, \
+      0xBA2E8BA3ull | 1ull << 32, \
+      0xE9BD37A7ull | 0ull << 32, \
+      0xAAAAAAABull | 3ull << 32, }
+static const unsigned long long kExactDivHost[25] = LLVQ_EXACT_DIV_TABLE;
 #if defined(__CUDACC__)
-static __device__ __constant__ unsigned long long kExactDiv[25] = {
-#else
-static const unsigned long long kExactDiv[25] = {
+static __device__ __constant__ unsigned long long kExactDivDev[25] = LLVQ_EXACT_DIV_TABLE;
 #endif
-        0ull,
-        0x00000001ull | 0ull << 32,  // 1
-        0x00000001ull | 1ull << 32,  // 2
-        0xAAAAAAABull | 0ull << 32,  // 3
-        0x00000001ull | 2ull << 32,  // 4
-        0xCCCCCCCDull | 0ull << 32,  // 5
-        0xAAAAAAABull | 1ull << 32,  // 6
-        0xB6DB6DB7ull | 0ull << 32,  // 7
-        0x00000001ull | 3ull << 32,  // 8
-        0x38E38E39ull | 0ull << 32,  // 9
-        0xCCCCCCCDull | 1ull << 32,  // 10
-        0xBA2E8BA3ull | 0ull << 32,  // 11
-        0xAAAAAAABull | 2ull << 32,  // 12
-        0xC4EC4EC5ull | 0ull << 32,  // 13
-        0xB6DB6DB7ull | 1ull << 32,  // 14
-        0xEEEEEEEFull | 0ull << 32,  // 15
-        0x00000001ull | 4ull << 32,  // 16
-        0xF0F0F0F1ull | 0ull << 32,  // 17
-        0x38E38E39ull | 1ull << 32,  // 18
-        0x286BCA1Bull | 0ull << 32,  // 19
-        0xCCCCCCCDull | 2ull << 32,  // 20
-        0x3CF3CF3Dull | 0ull << 32,  // 21
-        0xBA2E8BA3ull | 1ull << 32,  // 22
-        0xE9BD37A7ull | 0ull << 32,  // 23
-        0xAAAAAAABull | 3ull << 32,  // 24
-};
 
-LLVQ_HD unsigned long long exact_div_params(int n) { return kExactDiv[n]; }
+LLVQ_HD unsigned long long exact_div_params(int n) {
+#if defined(__CUDA_ARCH__)
+    return kExactDivDev[n];
+#else
+    return kExactDivHost[n];
+#endif
+}
 
 template <typename CntT>
 LLVQ_HD int unrank_step32(unsigned int& rank, unsigned int& m, int& n, CntT& cnt, int k) {

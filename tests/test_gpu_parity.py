@@ -244,3 +244,51 @@ def test_batch_forward_matches_row_by_row(rt, oracle):
         tail16 = m.tail.astype(np.float16).astype(np.float32)
         ref = oracle.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales, tail16, x.astype(np.float64))
         assert y.shape == (batch, 256) and rel_l2(y, ref) <= TOL_F16
+
+
+@pytest.mark.parametrize("d_out,d_in,batch", [(128, 192, 16), (200, 24 * 11 + 5, 17), (384, 24 * 19, 32), (136, 24 * 8 + 12, 100),
+                                              (72, 30, 16)])
+def test_batched_gemm_ragged_shapes(rt, oracle, d_out, d_in, batch):
+    """tcgen05 path: row tiles, column chunks, batch padding and the unaligned-x route all have ragged cases."""
+    torch = _torch()
+    from llvq_b200 import synth
+    m = synth.make_matrix(d_out, d_in, 0x6E44 + d_out + d_in)
+    proj = rt.upload(m, tail_f16=True)
+    x = synth.make_activation(d_in, 0x77 + batch, np.float16, batch=batch)
+    y = rt.forward_batch(proj, torch.from_numpy(x).cuda()).cpu().numpy()
+    tail16 = m.tail.astype(np.float16).astype(np.float32)
+    ref = oracle.gemv_f64(m.codes, d_out, d_in, m.centroids, m.row_scales, tail16, x.astype(np.float64))
+    assert y.shape == (batch, d_out) and np.isfinite(y).all()
+    assert rel_l2(y, ref) <= TOL_F16
+    for n in (0, batch - 1):  # every batch row on its own, not just the aggregate
+        assert rel_l2(y[n], ref[n]) <= 2 * TOL_F16
+    assert not rt.poll_range_error()
+
+
+def test_batched_gemm_config3_qwen3_8b_shapes(rt, oracle):
+    """BASELINE config 3: tree-verify batches of 16 and 64 on Qwen3-8B shapes (k_proj and a slice of gate_proj)."""
+    torch = _torch()
+    from llvq_b200 import synth
+    for d_out, d_in in ((1024, 4096), (1536, 4096), (512, 12288)):
+        m = synth.make_matrix(d_out, d_in, synth.matrix_seed(3, 0, d_out % 7))
+        proj = rt.upload(m, tail_f16=True)
+        tail16 = m.tail.astype(np.float16).astype(np.float32)
+        for batch in (16, 64):
+            x = synth.make_activation(d_in, 0x300 + batch, np.float16, batch=batch)
+            y = rt.forward_batch(proj, torch.from_numpy(x).cuda()).cpu().numpy()
+            ref = oracle.gemv_f64(m.codes, d_out, d_in, m.centroids, m.row_scales, tail16, x.astype(np.float64))
+            assert rel_l2(y, ref) <= TOL_F16, (d_out, d_in, batch)
+        proj.free()
+
+
+def test_batched_gemm_equals_gemv_semantics(rt):
+    """The same activation in every batch row gives the same output row, close to the batch-1 kernel's."""
+    torch = _torch()
+    from llvq_b200 import synth
+    m = synth.make_matrix(256, 24 * 64, 4711)
+    proj = rt.upload(m, tail_f16=True)
+    x1 = torch.from_numpy(synth.make_activation(m.d_in, 5, np.float16)).cuda()
+    yb = rt.forward_batch(proj, x1.repeat(16, 1).contiguous())
+    assert torch.equal(yb[0], yb[15])
+    y1 = rt.forward(proj, x1).float()
+    assert ((yb[0].float() - y1).norm() / y1.norm()).item() < 2e-3
