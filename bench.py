@@ -125,6 +125,40 @@ def cpu_baseline(layers_sample=1, min_seconds=6.0, max_seconds=30.0):
             "ns_per_block_per_core": t * threads / blocks * 1e9, "ms_per_pass": t * 1e3}, nbytes
 
 
+def gemm_section(rt, torch, synth, layers=3, iters=4):
+    """BASELINE config 3: batched dequant-GEMM (tcgen05) on Qwen3-8B projection shapes, B = 16 and 64.
+    `layers` distinct layers per pass (152 MB of codes) so no matrix is re-read warm."""
+    shapes = synth.layer_shapes("qwen3-8b")
+    projs = []
+    for l in range(layers):
+        for name, (do, di) in shapes.items():
+            projs.append(rt.upload(synth.make_matrix(do, di, synth.matrix_seed(3, l, synth.PROJ_IDS[name])), tail_f16=True))
+    blocks = sum(p.n_blocks for p in projs)
+    out = {"workload": "qwen3-8b-layer-gemm", "layers_per_pass": layers, "blocks_per_pass": blocks}
+    for batch in (16, 64):
+        xs = {di: torch.from_numpy(synth.make_activation(di, 0x3000 + batch, np.float16, batch=batch)).cuda()
+              for di in {p.d_in for p in projs}}
+        ys = [torch.empty(batch, p.d_out, dtype=torch.float16, device="cuda") for p in projs]
+        for _ in range(2):
+            for p, y in zip(projs, ys):
+                rt.forward_batch(p, xs[p.d_in], out=y)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(iters):
+            for p, y in zip(projs, ys):
+                rt.forward_batch(p, xs[p.d_in], out=y)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        flops = sum(2.0 * batch * p.d_out * p.d_in for p in projs)
+        out[f"batch{batch}"] = {"ms_per_layer": ms / layers, "gblocks_per_s": blocks / ms / 1e6,
+                                "tflops": flops / ms / 1e9, "tokens_x_layers_per_s": batch * layers / (ms * 1e-3)}
+    for p in projs:
+        p.free()
+    return out
+
+
 def run_reference(args):
     """Reference arm: the reference's CPU path (oracle port) on the host cores; rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
@@ -162,6 +196,7 @@ def main():
     ap.add_argument("--layers", type=int, default=36, help="distinct layers per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gemm", action="store_true", help="skip the batched-GEMM (config 3) side measurement")
     ap.add_argument("--no-groups", action="store_true",
                     help="launch q, k, v and gate, up separately instead of row-concatenated")
     args = ap.parse_args()
@@ -288,6 +323,10 @@ def main():
                 "d2h_bytes_per_step": sum(do * 2 for _, _, do, _ in mats_meta), "ms_per_step": ms_e2e / e2e_steps},
         "gpu_launches": int(launches), "clocks": clocks, "setup_s": gen_s,
     }
+    if not args.no_gemm:
+        for p in projs:
+            p.free()
+        out["gemm"] = gemm_section(rt, torch, synth)
     if not args.no_cpu_baseline:
         cb, _ = cpu_baseline()
         out["cpu_baseline"] = cb

@@ -89,6 +89,11 @@ struct llvq_matrix {
     float* rscale = nullptr;
     void* tail = nullptr;
     size_t codes_bytes = 0;
+    // column split of the GEMV (matrices whose rows are longer than one 128-block chunk): every
+    // split owns split_range column blocks; partial row sums and one arrival counter per row tile
+    int splits = 1, split_range = 0;
+    float* split_ws = nullptr;
+    int* split_counter = nullptr;
     // staging for the host-buffer entry points
     void* x_stage = nullptr;
     void* y_stage = nullptr;
@@ -135,8 +140,9 @@ int launch_sorted(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s, size_t sme
     llvq_runtime* rt = m->rt;
     auto kern = gemv_sorted_kernel<XT, YT, ROWS>;
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int grid = (m->d_out + ROWS - 1) / ROWS;
-    kern<<<grid, kThreads, smem, s>>>(rt->F, rt->T, m->view(), x, y, rt->d_err);
+    const dim3 grid((m->d_out + ROWS - 1) / ROWS, m->splits);
+    kern<<<grid, kThreads, smem, s>>>(rt->F, rt->T, m->view(), x, y, rt->d_err, m->split_range, m->split_ws,
+                                      m->split_counter);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
@@ -148,7 +154,7 @@ int launch_gemv(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
     // the sorted kernel reads the activation with 16-byte loads
     if ((uintptr_t)x & 15u) return launch_gemv_generic<XT, YT>(m, x, y, s);
     // 8 rows per CTA: measured against 16, the larger grid wins on every Qwen3 shape.
-    const size_t smem8 = sorted_smem_bytes<8>(m->nb);
+    const size_t smem8 = sorted_smem_bytes<8>(m->splits > 1 ? 0 : m->nb);  // no code slab when the columns are split
     if (smem8 <= (size_t)rt->max_smem_optin) return launch_sorted<XT, YT, 8>(m, x, y, s, smem8);
     return launch_gemv_generic<XT, YT>(m, x, y, s);
 }
@@ -179,6 +185,8 @@ void free_matrix_buffers(llvq_matrix* m) {
     cudaFree(m->tail);
     cudaFree(m->x_stage);
     cudaFree(m->y_stage);
+    cudaFree(m->split_ws);
+    cudaFree(m->split_counter);
 }
 
 int upload_impl(llvq_runtime* rt, const llvq_matrix_desc* descs, int n, llvq_matrix** out) {
@@ -247,6 +255,15 @@ int upload_impl(llvq_runtime* rt, const llvq_matrix_desc* descs, int n, llvq_mat
         }
     } else {
         UP_TRY(cudaMalloc(&m->tail, 16));  // never read; keeps the pointer valid
+    }
+    // one chunk of at most 128 column blocks per CTA, the row cut into equal parts
+    m->splits = m->nb > kChunk ? (m->nb + kChunk - 1) / kChunk : 1;
+    m->split_range = m->nb > 0 ? (m->nb + m->splits - 1) / m->splits : 1;
+    if (m->splits > 1) {
+        const size_t tiles = ((size_t)m->d_out + 7) / 8;
+        UP_TRY(cudaMalloc((void**)&m->split_ws, (size_t)m->splits * m->d_out * sizeof(float)));
+        UP_TRY(cudaMalloc((void**)&m->split_counter, tiles * sizeof(int)));
+        UP_TRY(cudaMemset(m->split_counter, 0, tiles * sizeof(int)));
     }
     UP_TRY(cudaMalloc(&m->x_stage, (size_t)m->d_in * sizeof(float) + 16));
     UP_TRY(cudaMalloc(&m->y_stage, (size_t)m->d_out * sizeof(float) + 16));

@@ -143,7 +143,8 @@ __device__ __forceinline__ unsigned short* list_slot(SortedSmem<ROWS>& S, unsign
 template <typename XT, typename YT, int ROWS>
 __global__ void __launch_bounds__(kThreads, 4)
 gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restrict__ x, YT* __restrict__ y,
-                   int* __restrict__ err_flag) {
+                   int* __restrict__ err_flag, int split_range, float* __restrict__ split_ws,
+                   int* __restrict__ split_counter) {
     using Smem = SortedSmem<ROWS>;
     constexpr int kRowsPerWarp = ROWS / kWarps;
     static_assert(ROWS % kWarps == 0 && sizeof(Smem) % 16 == 0, "rows split evenly; slab starts 16-byte aligned");
@@ -165,22 +166,28 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
     if (tid == 0) S.error = 0;
     __syncthreads();
 
-    if (nb > 0) {
+    // Column split: blockIdx.y owns the column blocks [cs0, cs1). A CTA that owns whole rows stages
+    // their codes with one bulk copy; a CTA that owns a column range reads its codes from global
+    // memory (its part of each row is neither contiguous with the next row's nor 16-byte aligned).
+    const int cs0 = blockIdx.y * split_range, cs1 = min(nb, cs0 + split_range);
+    const unsigned char* codes = mv.codes + (size_t)row0 * nb * 6;
+    if (gridDim.y == 1 && nb > 0) {
         // the slab start is 16-byte aligned because row0 is a multiple of 8 (48 * nb bytes per 8 rows)
         const unsigned int bytes = ((unsigned int)rows * nb * 6 + 15u) & ~15u;
-        const bool landed = bulk_load_codes(slab, mv.codes + (size_t)row0 * nb * 6, bytes, &S.mbar, tid);
+        const bool landed = bulk_load_codes(slab, codes, bytes, &S.mbar, tid);
         if (!__syncthreads_and(landed)) {
             if (tid == 0) atomicOr(err_flag, 2);
             return;  // the copy never landed: report, do not touch the slab
         }
+        codes = slab;
     }
 
     float row_acc[kRowsPerWarp];  // phase 3: lane-replicated sums of the rows owned by this warp
 #pragma unroll
     for (int q = 0; q < kRowsPerWarp; ++q) row_acc[q] = 0.0f;
 
-    for (int cb0 = 0; cb0 < nb; cb0 += kChunk) {
-        const int cbn = min(kChunk, nb - cb0);
+    for (int cb0 = cs0; cb0 < cs1; cb0 += kChunk) {
+        const int cbn = min(kChunk, cs1 - cb0);
 
         // ---- stage the activation chunk (transposed) and reset the queues ----
         stage_x_chunk<XT>(S.xs, x + (size_t)cb0 * kDim, cbn * kDim, tid);
@@ -195,7 +202,7 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
             const int f = lr * kChunk + bl;
             unsigned int path = 4u;  // 4: nothing to decode
             if (lr < rows && bl < cbn) {
-                const unsigned long long v = slab_code48(slab, lr * nb + cb0 + bl);
+                const unsigned long long v = slab_code48(codes, lr * nb + cb0 + bl);
                 const Classified c = classify12(F, v >> 1);
                 if (c.ci >= 0) {
                     path = c.path;
@@ -287,13 +294,43 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
         // the next chunk's staging overwrites xs/items only; part is rewritten after two barriers
     }
 
+    if (gridDim.y == 1) {
 #pragma unroll
-    for (int q = 0; q < kRowsPerWarp; ++q) {
-        const int lr = warp + kWarps * q;
-        if (lr < rows) {
-            const int r = row0 + lr;
-            const float t = tail_dot(mv, r, S.xs_tail, lane);
-            if (lane == 0) store_y<YT>(y, r, fmaf(row_acc[q], S.rscale[lr], t));
+        for (int q = 0; q < kRowsPerWarp; ++q) {
+            const int lr = warp + kWarps * q;
+            if (lr < rows) {
+                const int r = row0 + lr;
+                const float t = tail_dot(mv, r, S.xs_tail, lane);
+                if (lane == 0) store_y<YT>(y, r, fmaf(row_acc[q], S.rscale[lr], t));
+            }
+        }
+    } else {
+        // column split: publish this CTA's partial row sums; the CTA that arrives last at the row
+        // tile's counter adds the partials in split order (so the result does not depend on which
+        // CTA that is), finishes the rows and re-arms the counter for the next launch.
+#pragma unroll
+        for (int q = 0; q < kRowsPerWarp; ++q) {
+            const int lr = warp + kWarps * q;
+            if (lr < rows && lane == 0) split_ws[(size_t)blockIdx.y * mv.d_out + row0 + lr] = row_acc[q];
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) S.ticket = atomicAdd(&split_counter[blockIdx.x], 1) == (int)gridDim.y - 1;
+        __syncthreads();
+        if (S.ticket) {
+            __threadfence();
+#pragma unroll
+            for (int q = 0; q < kRowsPerWarp; ++q) {
+                const int lr = warp + kWarps * q;
+                if (lr < rows) {
+                    const int r = row0 + lr;
+                    float s = 0.0f;
+                    for (unsigned int k = 0; k < gridDim.y; ++k) s += __ldcg(split_ws + (size_t)k * mv.d_out + r);
+                    const float t = tail_dot(mv, r, S.xs_tail, lane);
+                    if (lane == 0) store_y<YT>(y, r, fmaf(s, S.rscale[lr], t));
+                }
+            }
+            if (tid == 0) split_counter[blockIdx.x] = 0;
         }
     }
     __syncthreads();
