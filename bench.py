@@ -188,8 +188,90 @@ def run_reference(args):
     }))
 
 
+def run_tp(args):
+    """BASELINE config 4 (GEMV part): Qwen3-14B projections row-sharded over the ranks, f16 activations,
+    NCCL all-gather of every output the next projection needs whole (4 per layer). Strong scaling:
+    the job is the same 40-layer pass at every N; `value` = whole-job algorithmic GB/s."""
+    import torch
+    import torch.distributed as dist
+    from llvq_b200 import FusedRuntime, synth
+    from llvq_b200.parallel import shard_rows
+    rank, local_rank = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    rt = FusedRuntime(local_rank)
+    shapes = synth.layer_shapes("qwen3-14b")
+    layers = args.layers if args.layers != 36 else 40
+    order = [["q", "k", "v"], ["o"], ["gate", "up"], ["down"]]
+    per_layer, job_bytes, job_blocks = [], 0, 0
+    for l in range(layers):
+        row = []
+        for names in order:
+            ms = []
+            for n in names:
+                do, di = shapes[n]
+                lo, hi = shard_rows(do, world, rank)
+                ms.append(synth.make_matrix(hi - lo, di, synth.matrix_seed(4, l, synth.PROJ_IDS[n]) ^ (rank << 40), n))
+                job_bytes += do * (di // 24) * 6 + do * (di % 24) * 4 + do * 8 + do * 2
+                job_blocks += do * (di // 24)
+            job_bytes += shapes[names[0]][1] * 2
+            proj = rt.upload_group(ms, tail_f16=True) if len(ms) > 1 else rt.upload(ms[0], tail_f16=True)
+            full = sum(shapes[n][0] for n in names)
+            row.append((proj, torch.empty(proj.d_out, dtype=torch.float16, device="cuda"),
+                        torch.empty(proj.d_out * world, dtype=torch.float16, device="cuda"), full))
+        per_layer.append(row)
+    x_h = torch.from_numpy(synth.make_activation(5120, 0x4000, np.float16)).cuda()
+    x_i = torch.from_numpy(synth.make_activation(17408, 0x4001, np.float16)).cuda()
+
+    def step():
+        for row in per_layer:
+            for gi, (proj, y_loc, y_all, _full) in enumerate(row):
+                rt.forward(proj, x_i if gi == 3 else x_h, out=y_loc)
+                if world > 1:  # q|k|v -> context, o, gate|up -> SwiGLU product, down: all needed whole next
+                    dist.all_gather_into_tensor(y_all, y_loc)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    if rank == 0:
+        peak, peak_kind, _ = measured_peaks()
+        gbs = job_bytes / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "dequant_gemv_algorithmic_GBps", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "qwen3-14b-tp-layer-gemv", "layers_per_step": layers, "parallelism": f"tp{world}",
+                       "collective": "nccl all_gather_into_tensor x4 per layer" if world > 1 else "none",
+                       "blocks_per_step": job_blocks, "algorithmic_bytes_per_step": job_bytes},
+            "token_equiv_per_s": (layers / 40.0) / (ms * 1e-3), "gblocks_per_s": job_blocks / (ms * 1e-3) / 1e9,
+            "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
+                         "traffic": None, "peak_kind": f"of {peak_kind}"}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--tp", action="store_true",
+                    help="tensor-parallel mode: Qwen3-14B projections row-sharded over the ranks with all-gathers")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -202,6 +284,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.tp:
+        return run_tp(args)
 
     import torch
     import torch.distributed as dist
