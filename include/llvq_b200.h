@@ -157,6 +157,18 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x_dev, uint16_t* y_dev, int32_t 
 int llvq_gemv_f32_host(llvq_matrix* m, const float* x_host, float* y_host, llvq_stream_t stream);
 int llvq_gemv_h_host(llvq_matrix* m, const uint16_t* x_host, uint16_t* y_host, llvq_stream_t stream);
 
+/* A whole list of host-buffer GEMVs (f16 in, f16 out) enqueued back to back with ONE
+ * synchronisation at the end: what a layer or a token is for a plugin that holds host
+ * tensors. The reference's loop also issues every launch of a token and synchronises once,
+ * at the argmax read-back (llvq-llm/src/model.rs:1058-1072). Pinned host buffers let the
+ * copies overlap the kernels of the neighbouring calls. */
+typedef struct llvq_host_call {
+    llvq_matrix* m;
+    const uint16_t* x_host; /* d_in halves */
+    uint16_t* y_host;       /* d_out halves */
+} llvq_host_call;
+int llvq_gemv_h_host_many(const llvq_host_call* calls, int32_t n, llvq_stream_t stream);
+
 /* No counterpart in the reference. Same contract as llvq_gemv_f32_host, for
  * callers that must not cause a device allocation: code that runs while another
  * part of the process is capturing a CUDA graph (cudaMalloc is illegal there), or a

@@ -20,6 +20,11 @@ class MatrixDesc(C.Structure):
     ]
 
 
+class HostCall(C.Structure):
+    """llvq_host_call of include/llvq_b200.h."""
+    _fields_ = [("m", C.c_void_p), ("x_host", C.c_void_p), ("y_host", C.c_void_p)]
+
+
 class LlvqError(RuntimeError):
     def __init__(self, status: int, message: str):
         super().__init__(f"llvq status {status}: {message}")
@@ -49,6 +54,7 @@ _SIGNATURES = {
     "llvq_gemm_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "llvq_gemv_f32_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "llvq_gemv_h_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llvq_gemv_h_host_many": (C.c_int, [C.POINTER(HostCall), C.c_int32, C.c_void_p]),
     "llvq_gemv_f32_host_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "llvq_decode_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "llvq_decode_indices": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -139,7 +139,11 @@ template <typename XT, typename YT, int ROWS>
 int launch_sorted(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s, size_t smem) {
     llvq_runtime* rt = m->rt;
     auto kern = gemv_sorted_kernel<XT, YT, ROWS>;
-    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static size_t configured = 0;  // raise the kernel's shared-memory limit only when a larger tile shows up
+    if (smem > configured) {
+        CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
     const dim3 grid((m->d_out + ROWS - 1) / ROWS, m->splits);
     kern<<<grid, kThreads, smem, s>>>(rt->F, rt->T, m->view(), x, y, rt->d_err, m->split_range, m->split_ws,
                                       m->split_counter);
@@ -549,6 +553,25 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
 int llvq_gemv_f32_host(llvq_matrix* m, const float* x, float* y, llvq_stream_t s) { return gemv_host<float, float>(m, x, y, s); }
 int llvq_gemv_h_host(llvq_matrix* m, const uint16_t* x, uint16_t* y, llvq_stream_t s) {
     return gemv_host<__half, __half>(m, (const __half*)x, (__half*)y, s);
+}
+
+int llvq_gemv_h_host_many(const llvq_host_call* calls, int32_t n, llvq_stream_t stream) {
+    if (!calls || n < 0) return fail(LLVQ_ERR_INVALID, "gemv_h_host_many: bad argument");
+    if (n == 0) return LLVQ_OK;
+    for (int i = 0; i < n; ++i)
+        if (!calls[i].m || !calls[i].x_host || !calls[i].y_host || calls[i].m->rt != calls[0].m->rt)
+            return fail(LLVQ_ERR_INVALID, "gemv_h_host_many: call %d has a null field or another runtime", i);
+    DeviceGuard g(calls[0].m->rt->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    for (int i = 0; i < n; ++i) {
+        llvq_matrix* m = calls[i].m;
+        CUDA_TRY(cudaMemcpyAsync(m->x_stage, calls[i].x_host, (size_t)m->d_in * sizeof(__half), cudaMemcpyHostToDevice, s));
+        int st = launch_gemv<__half, __half>(m, (const __half*)m->x_stage, (__half*)m->y_stage, s);
+        if (st) return st;
+        CUDA_TRY(cudaMemcpyAsync(calls[i].y_host, m->y_stage, (size_t)m->d_out * sizeof(__half), cudaMemcpyDeviceToHost, s));
+    }
+    CUDA_TRY(cudaStreamSynchronize(s));
+    return LLVQ_OK;
 }
 
 // ---- host-buffer GEMV that never allocates ---------------------------------

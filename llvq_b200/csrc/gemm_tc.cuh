@@ -66,21 +66,6 @@ __device__ __forceinline__ unsigned int swz_offset(int r, int gc, int panel_byte
     return (unsigned int)((gc >> 3) * panel_bytes + r * 128 + (((gc & 7) ^ (r & 7)) << 4));
 }
 
-__device__ __forceinline__ bool mbar_wait(unsigned long long* mbar, unsigned int parity) {
-    const unsigned int bar = smem_addr(mbar);
-    unsigned int done = 0;
-    for (unsigned int spin = 0; spin < kSpinLimit && !done; ++spin) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-    }
-    return done != 0;
-}
-
 // Collects the 24 values of one block and writes them as three 16-byte chunks of f16.
 struct TileWriter {
     unsigned int h[12];
@@ -185,7 +170,7 @@ gemm_tc_kernel(FastTables F, DevTables G, MatrixView mv, GemmArgs ga, int* __res
         }
 
         // ---- the tiles are free once the previous chunk's MMAs have completed ----
-        if (c > c_begin) ok = mbar_wait(&S.mbar, (unsigned int)((c - c_begin - 1) & 1));
+        if (c > c_begin && tid == 0) ok = mbar_wait(&S.mbar, (unsigned int)((c - c_begin - 1) & 1));  // one poller
         ok = __syncthreads_and(ok);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -315,7 +300,7 @@ gemm_tc_kernel(FastTables F, DevTables G, MatrixView mv, GemmArgs ga, int* __res
     }
 
     // ---- epilogue: wait for the last MMAs, read the accumulators, store the split-K partials ----
-    if (ok && c_end > c_begin) ok = mbar_wait(&S.mbar, (unsigned int)((c_end - c_begin - 1) & 1));
+    if (ok && c_end > c_begin && tid == 0) ok = mbar_wait(&S.mbar, (unsigned int)((c_end - c_begin - 1) & 1));
     ok = __syncthreads_and(ok);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok && warp < 4 && c_end > c_begin) {

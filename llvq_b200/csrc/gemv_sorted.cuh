@@ -66,30 +66,31 @@ __device__ __forceinline__ unsigned int smem_addr(const void* p) {
     return (unsigned int)__cvta_generic_to_shared(p);
 }
 
-// Returns false when the copy did not complete within the spin limit.
-__device__ __forceinline__ bool bulk_load_codes(unsigned char* dst, const unsigned char* src, unsigned int bytes,
-                                                unsigned long long* mbar, int tid) {
+// Starts the bulk copy of `bytes` (a multiple of 16) from 16-byte aligned global memory into shared
+// memory; completion is signalled on `mbar`. Call from one thread, after the barrier has been
+// initialised and that initialisation made visible by a __syncthreads().
+__device__ __forceinline__ void bulk_load_issue(unsigned char* dst, const unsigned char* src, unsigned int bytes,
+                                                unsigned long long* mbar) {
     const unsigned int bar = smem_addr(mbar);
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    if (tid == 0) {
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-        asm volatile(
-            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
-            "l"(src), "r"(bytes), "r"(bar)
-            : "memory");
-    }
-    unsigned int done = 0;  // every thread polls; the verdict is made uniform by the caller
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+// Bounded wait for phase `parity` of an mbarrier; false when the spin limit ran out. Meant for ONE
+// polling thread: the rest of the CTA waits at the __syncthreads_and() that spreads the verdict.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* mbar, unsigned int parity) {
+    const unsigned int bar = smem_addr(mbar);
+    unsigned int done = 0;
     for (unsigned int spin = 0; spin < kSpinLimit && !done; ++spin) {
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done)
-            : "r"(bar)
+            : "r"(bar), "r"(parity)
             : "memory");
     }
     return done != 0;
@@ -163,7 +164,11 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
         S.rscale[tid] = mv.rscale[r];
     }
     if (tid < 32) S.xs_tail[tid] = tid < mv.tail_w ? to_f32<XT>(x[nb * kDim + tid]) : 0.0f;
-    if (tid == 0) S.error = 0;
+    if (tid == 0) {
+        S.error = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&S.mbar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     __syncthreads();
 
     // Column split: blockIdx.y owns the column blocks [cs0, cs1). A CTA that owns whole rows stages
@@ -171,14 +176,11 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
     // memory (its part of each row is neither contiguous with the next row's nor 16-byte aligned).
     const int cs0 = blockIdx.y * split_range, cs1 = min(nb, cs0 + split_range);
     const unsigned char* codes = mv.codes + (size_t)row0 * nb * 6;
-    if (gridDim.y == 1 && nb > 0) {
-        // the slab start is 16-byte aligned because row0 is a multiple of 8 (48 * nb bytes per 8 rows)
-        const unsigned int bytes = ((unsigned int)rows * nb * 6 + 15u) & ~15u;
-        const bool landed = bulk_load_codes(slab, codes, bytes, &S.mbar, tid);
-        if (!__syncthreads_and(landed)) {
-            if (tid == 0) atomicOr(err_flag, 2);
-            return;  // the copy never landed: report, do not touch the slab
-        }
+    const bool use_slab = gridDim.y == 1 && nb > 0;
+    if (use_slab) {
+        // the slab start is 16-byte aligned because row0 is a multiple of 8 (48 * nb bytes per 8 rows);
+        // the copy runs while the first activation chunk is being staged
+        if (tid == 0) bulk_load_issue(slab, codes, ((unsigned int)rows * nb * 6 + 15u) & ~15u, &S.mbar);
         codes = slab;
     }
 
@@ -193,7 +195,16 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
         stage_x_chunk<XT>(S.xs, x + (size_t)cb0 * kDim, cbn * kDim, tid);
         if (tid < 4) S.count[tid] = 0;
         if (tid == 0) S.ticket = 0;
-        __syncthreads();
+        if (use_slab && cb0 == cs0) {
+            // one thread waits (bounded) for the code slab; the barrier spreads its verdict
+            const bool landed = tid != 0 || mbar_wait(&S.mbar, 0);
+            if (!__syncthreads_and(landed)) {
+                if (tid == 0) atomicOr(err_flag, 2);
+                return;  // the copy never landed: report, do not touch the slab
+            }
+        } else {
+            __syncthreads();
+        }
 
         // ---- phase 1: classify; a warp takes rows warp, warp + 8, ..., a lane every 32nd block ----
 #pragma unroll 1

@@ -154,6 +154,17 @@ class FusedRuntime:
         check(fn(proj._h, x_host.ctypes.data, y_host.ctypes.data, self._stream()))
         return y_host
 
+    def forward_host_many(self, projs, xs_host, ys_host) -> None:
+        """f16 host buffers for a list of projections: everything is enqueued, one synchronisation at the end."""
+        from ._lib import HostCall
+        n = len(projs)
+        arr = (HostCall * n)()
+        for i, (p, x, y) in enumerate(zip(projs, xs_host, ys_host)):
+            if x.dtype != np.float16 or y.dtype != np.float16 or x.size != p.d_in or y.size != p.d_out:
+                raise ValueError("forward_host_many: f16 buffers of d_in / d_out elements")
+            arr[i].m, arr[i].x_host, arr[i].y_host = p._h, x.ctypes.data, y.ctypes.data
+        check(self.lib.llvq_gemv_h_host_many(arr, n, self._stream()))
+
     @staticmethod
     def _check_x(proj: FusedProj, x, dtype) -> None:
         # the reference's own preconditions: contiguous, len == d_in (fused_cuda.rs:768-787)

@@ -193,6 +193,20 @@ def test_host_buffer_entry_point(rt, oracle):
         assert rel_l2(y, ref) <= tol
 
 
+def test_host_buffer_list_entry_point(rt, oracle):
+    from llvq_b200 import synth
+    ms = [synth.make_matrix(d, 24 * 12 + 3, 600 + d) for d in (64, 8, 40)]
+    projs = [rt.upload(m, tail_f16=True) for m in ms]
+    xs = [synth.make_activation(m.d_in, 70 + i, np.float16) for i, m in enumerate(ms)]
+    ys = [np.full(m.d_out, np.nan, np.float16) for m in ms]
+    rt.forward_host_many(projs, xs, ys)
+    for m, p, x, y in zip(ms, projs, xs, ys):
+        single = np.empty(m.d_out, np.float16)
+        rt.forward_host(p, x, single)
+        assert np.array_equal(y, single)
+    rt.forward_host_many([], [], [])
+
+
 def test_index_outside_the_ball_raises_the_range_flag(rt, oracle):
     torch = _torch()
     from llvq_b200 import synth
