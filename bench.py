@@ -180,8 +180,7 @@ def decode_section(rt, torch, prompt_len=128, new_tokens=256):
         nxt = model.logits_last(x).argmax()
         torch.cuda.synchronize()
         t1 = time.perf_counter()
-        model._tok = nxt.reshape(1).clone()
-        model._pos = torch.tensor([prompt_len], device=model.device, dtype=torch.long)
+        model.start_decode(nxt, prompt_len)
         out = [int(nxt)]
         while len(out) < new_tokens:
             model._graph_step()

@@ -112,6 +112,9 @@ class FusedQwen3:
             self.caches = [[torch.zeros(capacity, cfg.n_kv, cfg.head_dim, dtype=torch.float16, device=dev) for _ in range(2)]
                            for _ in blocks]
         self._graph = None
+        # the token and its position live in fixed device tensors: a captured graph keeps their addresses
+        self._tok = torch.zeros(1, dtype=torch.long, device=dev)
+        self._pos = torch.zeros(1, dtype=torch.long, device=dev)
 
     # ---- pieces ------------------------------------------------------------------
     def _rms(self, x, w):
@@ -186,13 +189,17 @@ class FusedQwen3:
         x = self.hidden(toks, self.positions[:n])
         nxt = self.logits_last(x).argmax()
         out = [int(nxt)]
-        self._tok = nxt.reshape(1).clone()
-        self._pos = torch.tensor([n], device=self.device, dtype=torch.long)
+        self.start_decode(nxt, n)
         step = self._graph_step if use_graph else self._eager_step
         while len(out) < max_new:
             step()
             out.append(int(self._tok))  # one scalar read-back per token, as model.rs:1064
         return out
+
+    def start_decode(self, first_token, position: int) -> None:
+        """Point the token step at `first_token` (device scalar) sitting at `position` (in place: graph-safe)."""
+        self._tok.copy_(first_token.reshape(1))
+        self._pos.fill_(position)
 
     def _eager_step(self):
         x = self.hidden(self._tok, self._pos)

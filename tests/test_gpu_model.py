@@ -64,6 +64,7 @@ def test_graph_replay_gives_the_eager_tokens(rt):
     b, _ = synthetic_model(rt, cfg, config_id=2, capacity=64)
     graphed = b.generate(prompt, 16, use_graph=True)
     assert eager == graphed
+    assert b.generate(prompt, 16, use_graph=True) == eager  # a second generation replays the same graph
     assert a.generate(prompt, 0) == []
 
 
