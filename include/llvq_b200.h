@@ -189,6 +189,35 @@ int llvq_gemv_h_host_many(const llvq_host_call* calls, int32_t n, llvq_stream_t 
 #define LLVQ_STATIC_MAX_D_OUT 262144
 int llvq_gemv_f32_host_static(llvq_matrix* m, const float* x_host, float* y_host, llvq_stream_t stream);
 
+/* ---- the rest of a batch-1 decode step ------------------------------------- */
+
+/* The non-projection steps of one Qwen3 block at batch 1, fused into four kernels; all tensors are
+ * device memory, f16 passed as uint16_t, arithmetic in f32. The reference runs these steps as stock
+ * candle ops (Block::forward_cached, llvq-llm/src/model.rs:778-834) and only simulates the int8 KV
+ * cache (quantize_dequantize, llvq-llm/src/kvq.rs:110-165); here the cache stores the u8 codes with
+ * an f16 scale and bias per group of 64 along head_dim ([capacity, n_kv, head_dim] codes,
+ * [capacity, n_kv, head_dim / 64] scales and biases). `pos_dev` points at the int64 position of the
+ * token in device memory, so a captured CUDA graph can be replayed for every token.
+ * head_dim must be 64 or 128. */
+
+/* x += delta (skipped when delta is NULL); y = x / rms(x) * w   (ln1 / ln2 / final norm + residual add) */
+int llvq_op_add_rmsnorm_h(uint16_t* x_dev, const uint16_t* delta_dev, const uint16_t* w_dev, uint16_t* y_dev, int32_t n,
+                          float eps, llvq_stream_t stream);
+/* qkv = [q | k | v] of one token: per-head RMSNorm of q and k, RoPE (rotate-half; cos/sin tables
+ * f32 [capacity, head_dim / 2]) at *pos_dev, q out; k and v quantised into the cache at *pos_dev. */
+int llvq_op_qkv_rope_cache_h(const uint16_t* qkv_dev, const uint16_t* q_norm_dev, const uint16_t* k_norm_dev,
+                             const float* cos_dev, const float* sin_dev, const int64_t* pos_dev, uint16_t* q_out_dev,
+                             uint8_t* kq_dev, uint16_t* ks_dev, uint16_t* kb_dev, uint8_t* vq_dev, uint16_t* vs_dev,
+                             uint16_t* vb_dev, int32_t n_heads, int32_t n_kv, int32_t head_dim, float eps,
+                             llvq_stream_t stream);
+/* softmax(q k^T / sqrt(head_dim)) v over positions 0..*pos_dev of the int8 cache, grouped-query heads. */
+int llvq_op_attn_decode_int8_h(const uint16_t* q_dev, const uint8_t* kq_dev, const uint16_t* ks_dev, const uint16_t* kb_dev,
+                               const uint8_t* vq_dev, const uint16_t* vs_dev, const uint16_t* vb_dev,
+                               const int64_t* pos_dev, uint16_t* out_dev, int32_t n_heads, int32_t n_kv, int32_t head_dim,
+                               llvq_stream_t stream);
+/* y[i] = silu(gate_up[i]) * gate_up[inter + i] */
+int llvq_op_silu_mul_h(const uint16_t* gate_up_dev, uint16_t* y_dev, int32_t inter, llvq_stream_t stream);
+
 /* ---- decode probes --------------------------------------------------------- */
 
 /* Decode n packed 6-byte records on the GPU to their lattice points: 24 int8

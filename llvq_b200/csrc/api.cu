@@ -14,6 +14,7 @@
 
 #include "../../include/llvq_b200.h"
 #include "codebook.h"
+#include "decode_ops.cuh"
 #include "gemm_tc.cuh"
 #include "gemv_sorted.cuh"
 #include "kernels_generic.cuh"
@@ -553,6 +554,65 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
 int llvq_gemv_f32_host(llvq_matrix* m, const float* x, float* y, llvq_stream_t s) { return gemv_host<float, float>(m, x, y, s); }
 int llvq_gemv_h_host(llvq_matrix* m, const uint16_t* x, uint16_t* y, llvq_stream_t s) {
     return gemv_host<__half, __half>(m, (const __half*)x, (__half*)y, s);
+}
+
+int llvq_op_add_rmsnorm_h(uint16_t* x, const uint16_t* delta, const uint16_t* w, uint16_t* y, int32_t n, float eps,
+                          llvq_stream_t stream) {
+    if (!x || !w || !y || n <= 0 || (n & 1) || n > 16384) return fail(LLVQ_ERR_INVALID, "op_add_rmsnorm: bad argument (n even, <= 16384)");
+    add_rmsnorm_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>((__half*)x, (const __half*)delta, (const __half*)w, (__half*)y, n,
+                                                            eps);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+int llvq_op_qkv_rope_cache_h(const uint16_t* qkv, const uint16_t* q_norm, const uint16_t* k_norm, const float* cos_t,
+                             const float* sin_t, const int64_t* pos, uint16_t* q_out, uint8_t* kq, uint16_t* ks,
+                             uint16_t* kb, uint8_t* vq, uint16_t* vs, uint16_t* vb, int32_t n_heads, int32_t n_kv,
+                             int32_t head_dim, float eps, llvq_stream_t stream) {
+    if (!qkv || !q_norm || !k_norm || !cos_t || !sin_t || !pos || !q_out || !kq || !ks || !kb || !vq || !vs || !vb)
+        return fail(LLVQ_ERR_INVALID, "op_qkv_rope_cache: null argument");
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv) return fail(LLVQ_ERR_INVALID, "op_qkv_rope_cache: %d heads over %d", n_heads, n_kv);
+    const KvCacheView kc{kq, (__half*)ks, (__half*)kb}, vc{vq, (__half*)vs, (__half*)vb};
+    const int grid = n_heads + 2 * n_kv;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (head_dim == 128)
+        qkv_rope_cache_kernel<128><<<grid, 32, 0, s>>>((const __half*)qkv, (const __half*)q_norm, (const __half*)k_norm, cos_t,
+                                                       sin_t, (const long long*)pos, (__half*)q_out, kc, vc, n_heads, n_kv, eps);
+    else if (head_dim == 64)
+        qkv_rope_cache_kernel<64><<<grid, 32, 0, s>>>((const __half*)qkv, (const __half*)q_norm, (const __half*)k_norm, cos_t,
+                                                      sin_t, (const long long*)pos, (__half*)q_out, kc, vc, n_heads, n_kv, eps);
+    else
+        return fail(LLVQ_ERR_UNSUPPORTED, "op_qkv_rope_cache: head_dim %d (64 or 128)", head_dim);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+int llvq_op_attn_decode_int8_h(const uint16_t* q, const uint8_t* kq, const uint16_t* ks, const uint16_t* kb,
+                               const uint8_t* vq, const uint16_t* vs, const uint16_t* vb, const int64_t* pos, uint16_t* out,
+                               int32_t n_heads, int32_t n_kv, int32_t head_dim, llvq_stream_t stream) {
+    if (!q || !kq || !ks || !kb || !vq || !vs || !vb || !pos || !out) return fail(LLVQ_ERR_INVALID, "op_attn_decode: null argument");
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv) return fail(LLVQ_ERR_INVALID, "op_attn_decode: %d heads over %d", n_heads, n_kv);
+    const KvCacheView kc{(unsigned char*)kq, (__half*)ks, (__half*)kb}, vc{(unsigned char*)vq, (__half*)vs, (__half*)vb};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (head_dim == 128)
+        attn_decode_kernel<128><<<n_heads, 128, 0, s>>>((const __half*)q, kc, vc, (const long long*)pos, (__half*)out, n_heads, n_kv);
+    else if (head_dim == 64)
+        attn_decode_kernel<64><<<n_heads, 128, 0, s>>>((const __half*)q, kc, vc, (const long long*)pos, (__half*)out, n_heads, n_kv);
+    else
+        return fail(LLVQ_ERR_UNSUPPORTED, "op_attn_decode: head_dim %d (64 or 128)", head_dim);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+int llvq_op_silu_mul_h(const uint16_t* gu, uint16_t* y, int32_t inter, llvq_stream_t stream) {
+    if (!gu || !y || inter <= 0) return fail(LLVQ_ERR_INVALID, "op_silu_mul: bad argument");
+    silu_mul_kernel<<<(inter + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const __half*)gu, (__half*)y, inter);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
 }
 
 int llvq_gemv_h_host_many(const llvq_host_call* calls, int32_t n, llvq_stream_t stream) {

@@ -94,7 +94,7 @@ class FusedQwen3:
     """`proj(name_group, x)` hooks let the same loop run on fused projections or on a dense stand-in."""
 
     def __init__(self, cfg: Qwen3Config, blocks: Sequence[dict], embed, final_norm, capacity: int,
-                 gemv: Callable, gemm: Callable, kv_int8: bool = True):
+                 gemv: Callable, gemm: Callable, kv_int8: bool = True, ops=None):
         """blocks[i]: {"qkv", "o", "gate_up", "down": projection handles, "ln1", "ln2", "q_norm", "k_norm": f16 tensors}.
         gemv(handle, x[d_in]) -> y[d_out]; gemm(handle, X[L, d_in]) -> Y[L, d_out] (both f16 on the GPU)."""
         import torch
@@ -112,6 +112,16 @@ class FusedQwen3:
             self.caches = [[torch.zeros(capacity, cfg.n_kv, cfg.head_dim, dtype=torch.float16, device=dev) for _ in range(2)]
                            for _ in blocks]
         self._graph = None
+        # `ops`: the C library (llvq_op_* kernels). With it and an int8 cache the token step runs the fused
+        # decode kernels; without it every non-projection step is a torch op (the prefill always is).
+        self.ops = ops if kv_int8 else None
+        if self.ops is not None:
+            f16 = dict(dtype=torch.float16, device=dev)
+            self._x, self._h = torch.zeros(cfg.hidden, **f16), torch.zeros(cfg.hidden, **f16)
+            self._qkv = torch.zeros((cfg.n_heads + 2 * cfg.n_kv) * cfg.head_dim, **f16)
+            self._q, self._ctx = (torch.zeros(cfg.n_heads * cfg.head_dim, **f16) for _ in range(2))
+            self._o, self._down = torch.zeros(cfg.hidden, **f16), torch.zeros(cfg.hidden, **f16)
+            self._gu, self._act = torch.zeros(2 * cfg.inter, **f16), torch.zeros(cfg.inter, **f16)
         # the token and its position live in fixed device tensors: a captured graph keeps their addresses
         self._tok = torch.zeros(1, dtype=torch.long, device=dev)
         self._pos = torch.zeros(1, dtype=torch.long, device=dev)
@@ -202,8 +212,41 @@ class FusedQwen3:
         self._pos.fill_(position)
 
     def _eager_step(self):
+        if self.ops is not None:
+            return self._fused_step()
         x = self.hidden(self._tok, self._pos)
         self._tok.copy_(self.logits_last(x).argmax().reshape(1))
+        self._pos += 1
+
+    def _fused_step(self):
+        """One token: 4 fused GEMV launches and 4 small fused kernels per block, nothing else."""
+        import ctypes as C
+        import torch
+        from ._lib import check
+        L, cfg = self.ops, self.cfg
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        p = lambda t: C.c_void_p(t.data_ptr())
+        self._x.copy_(self.embed.index_select(0, self._tok)[0])
+        delta = None
+        for blk, cache in zip(self.blocks, self.caches):
+            check(L.llvq_op_add_rmsnorm_h(p(self._x), p(delta) if delta is not None else None, p(blk["ln1"]), p(self._h),
+                                          cfg.hidden, cfg.eps, st))
+            self.gemv(blk["qkv"], self._h, out=self._qkv)
+            check(L.llvq_op_qkv_rope_cache_h(p(self._qkv), p(blk["q_norm"]), p(blk["k_norm"]), p(self.cos), p(self.sin),
+                                             p(self._pos), p(self._q), p(cache.q[0]), p(cache.s[0]), p(cache.b[0]),
+                                             p(cache.q[1]), p(cache.s[1]), p(cache.b[1]), cfg.n_heads, cfg.n_kv,
+                                             cfg.head_dim, cfg.eps, st))
+            check(L.llvq_op_attn_decode_int8_h(p(self._q), p(cache.q[0]), p(cache.s[0]), p(cache.b[0]), p(cache.q[1]),
+                                               p(cache.s[1]), p(cache.b[1]), p(self._pos), p(self._ctx), cfg.n_heads,
+                                               cfg.n_kv, cfg.head_dim, st))
+            self.gemv(blk["o"], self._ctx, out=self._o)
+            check(L.llvq_op_add_rmsnorm_h(p(self._x), p(self._o), p(blk["ln2"]), p(self._h), cfg.hidden, cfg.eps, st))
+            self.gemv(blk["gate_up"], self._h, out=self._gu)
+            check(L.llvq_op_silu_mul_h(p(self._gu), p(self._act), cfg.inter, st))
+            self.gemv(blk["down"], self._act, out=self._down)
+            delta = self._down
+        check(L.llvq_op_add_rmsnorm_h(p(self._x), p(delta), p(self.final_norm), p(self._h), cfg.hidden, cfg.eps, st))
+        self._tok.copy_((self._h[None, :] @ self.embed.t()).float()[0].argmax().reshape(1))
         self._pos += 1
 
     def _graph_step(self):
@@ -226,7 +269,7 @@ class FusedQwen3:
 
 
 def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: int = 0x51, layers: Optional[int] = None,
-                    kv_int8: bool = True):
+                    kv_int8: bool = True, fused_ops: bool = True):
     """Random-weight model of BASELINE config 2/4: LLVQ codes for every projection, f16 N(0, 0.02)
     norms and tied embedding (norm weights are 1 + N(0, 0.02) so that activations keep their scale)."""
     import torch
@@ -253,5 +296,6 @@ def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: i
                        "q_norm": f16(cfg.head_dim, 1.0), "k_norm": f16(cfg.head_dim, 1.0)})
     embed = f16(cfg.vocab * cfg.hidden).reshape(cfg.vocab, cfg.hidden)
     final_norm = f16(cfg.hidden, 1.0)
-    model = FusedQwen3(cfg, blocks, embed, final_norm, capacity, gemv=rt.forward, gemm=rt.forward_batch, kv_int8=kv_int8)
+    model = FusedQwen3(cfg, blocks, embed, final_norm, capacity, gemv=rt.forward, gemm=rt.forward_batch, kv_int8=kv_int8,
+                       ops=rt.lib if fused_ops else None)
     return model, mats

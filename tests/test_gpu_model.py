@@ -55,6 +55,27 @@ def test_greedy_tokens_match_the_dense_decoded_run(rt, oracle, kv_int8):
     assert not rt.poll_range_error()
 
 
+def test_fused_decode_kernels_agree_with_the_tensor_op_step(rt):
+    """Same model, token step once as four fused kernels per block and once as torch ops."""
+    import torch
+    from llvq_b200.model import Qwen3Config, synthetic_model
+    for hd, heads, kv in ((64, 4, 2), (128, 4, 1)):
+        cfg = Qwen3Config(hidden=24 * 10 + 16, inter=24 * 20 + 8, n_heads=heads, n_kv=kv, head_dim=hd, layers=2, vocab=512)
+        prompt = list(range(40, 60))
+        a, _ = synthetic_model(rt, cfg, config_id=2, capacity=64, fused_ops=True)
+        b, _ = synthetic_model(rt, cfg, config_id=2, capacity=64, fused_ops=False)
+        assert a.ops is not None and b.ops is None
+        assert a.generate(prompt, 20) == b.generate(prompt, 20)
+        # the hidden state after the step, not only the argmax
+        a.start_decode(torch.tensor(7, device=a.device), 30)
+        b.start_decode(torch.tensor(7, device=b.device), 30)
+        a._fused_step()
+        xb = b.hidden(torch.tensor([7], device=b.device), torch.tensor([30], device=b.device))
+        ha = a._h.float()
+        hb = b._rms(xb[-1:], b.final_norm)[0].float()
+        assert ((ha - hb).norm() / hb.norm()).item() < 5e-3
+
+
 def test_graph_replay_gives_the_eager_tokens(rt):
     from llvq_b200.model import Qwen3Config, synthetic_model
     cfg = Qwen3Config(hidden=24 * 10 + 16, inter=24 * 20 + 8, n_heads=4, n_kv=2, head_dim=64, layers=2, vocab=512)
