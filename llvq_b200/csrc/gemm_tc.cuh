@@ -30,7 +30,7 @@ namespace llvq {
 constexpr int kGM = 128;                  // rows of W per CTA = MMA M
 constexpr int kGKB = 8;                   // blocks per row and chunk: 8 * 24 = 192 = 3 * 64 columns
 constexpr int kGItems = kGM * kGKB;       // 1024 blocks per chunk
-constexpr int kGThreads = 256;
+constexpr int kGThreads = 512;
 constexpr int kGMaxN = 64;                // padded batch per launch = MMA N
 constexpr int kGPanelA = kGM * 128;       // bytes of one 64-column A panel
 constexpr int kGPanelB = kGMaxN * 128;    // bytes of one 64-column B panel
