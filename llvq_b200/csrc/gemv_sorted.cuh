@@ -142,7 +142,7 @@ __device__ __forceinline__ unsigned short* list_slot(SortedSmem<ROWS>& S, unsign
 }
 
 template <typename XT, typename YT, int ROWS>
-__global__ void __launch_bounds__(kThreads, 4)
+__global__ void __launch_bounds__(kThreads, 5)
 gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restrict__ x, YT* __restrict__ y,
                    int* __restrict__ err_flag, int split_range, float* __restrict__ split_ws,
                    int* __restrict__ split_counter) {
