@@ -175,9 +175,7 @@ def decode_section(rt, torch, prompt_len=128, new_tokens=256):
     for _ in range(2):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        toks = torch.tensor(prompt, device=model.device)
-        x = model.hidden(toks, model.positions[:prompt_len])
-        nxt = model.logits_last(x).argmax()
+        nxt = model.pick(model._rms(model.prefill(prompt), model.final_norm)[0])
         torch.cuda.synchronize()
         t1 = time.perf_counter()
         model.start_decode(nxt, prompt_len)
@@ -221,6 +219,92 @@ def run_reference(args):
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
+
+
+def run_tp_decode(args):
+    """BASELINE config 4: Qwen3-14B-architecture greedy decode, tensor-parallel over the ranks (q/k/v by heads, the
+    other projections and the tied head by rows, NCCL all-gathers of the row shards), int8 split-KV attention over a
+    long random prompt, then `new_tokens` greedy tokens at batch 1 replayed from a CUDA graph. `value` = generated
+    tokens per second over the decode phase (device-timed, max over ranks); the prefill is reported apart."""
+    import torch
+    import torch.distributed as dist
+    from llvq_b200 import FusedRuntime
+    from llvq_b200.model import Qwen3Config, TpGroup, synthetic_model
+    rank, local_rank = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    rt = FusedRuntime(local_rank)
+    cfg = Qwen3Config.named("qwen3-14b")
+    layers = args.layers if args.layers != 36 else cfg.layers
+    prompt_len, new_tokens = args.prompt, args.new_tokens
+    t0 = time.perf_counter()
+    model, _ = synthetic_model(rt, cfg, config_id=4, capacity=prompt_len + new_tokens, layers=layers,
+                               tp=TpGroup() if world > 1 else None, keep_host=False, device_codes=True)
+    torch.cuda.synchronize()
+    setup = time.perf_counter() - t0
+    rng = np.random.default_rng(0x4C0DE)
+    prompt = [int(t) for t in rng.integers(0, cfg.vocab, prompt_len)]
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e[0].record()
+    nxt = model.pick(model._rms(model.prefill(prompt), model.final_norm)[0])
+    e[1].record()
+    torch.cuda.synchronize()
+    model.start_decode(nxt, prompt_len)
+    for _ in range(max(args.warmup, 3)):  # the first call captures the graph; the position moves on, as in a real run
+        model._graph_step()
+    model.start_decode(nxt, prompt_len)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    if sampler:
+        sampler.start()
+    out = [int(nxt)]
+    e[2].record()
+    t1 = time.perf_counter()
+    while len(out) < new_tokens:
+        model._graph_step()
+        out.append(int(model._tok))  # the per-token read-back of the reference's loop
+    e[3].record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t1
+    clocks = sampler.stop() if sampler else None
+    t = torch.tensor([e[2].elapsed_time(e[3]), wall * 1e3, e[0].elapsed_time(e[1])], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        toks = torch.tensor(out, device="cuda")
+        ref = toks.clone()
+        dist.broadcast(ref, 0)
+        same = torch.tensor([int(torch.equal(ref, toks))], device="cuda")
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        ranks_agree = bool(same.item())
+    else:
+        ranks_agree = True
+    decode_ms, wall_ms, prefill_ms = t[0].item(), t[1].item(), t[2].item()
+    if rank == 0:
+        gen = new_tokens - 1
+        kv_bytes = 2 * layers * (prompt_len + new_tokens // 2) * cfg.n_kv * (cfg.head_dim + 2 * 2 * cfg.head_dim // 64)
+        print(json.dumps({
+            "metric": "decode_tok_per_s", "value": gen / (decode_ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": gen, "warmup": max(args.warmup, 3), "ms_per_step": decode_ms / gen, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "qwen3-14b-tp-greedy-decode", "layers": layers, "prompt_tokens": prompt_len,
+                       "new_tokens": new_tokens, "parallelism": f"tp{world}", "kv_cache": "int8 g64, split-KV attention",
+                       "attn_splits": model.attn_splits, "graph": True,
+                       "collective": "nccl all_gather_into_tensor x4 per layer + 1 per token" if world > 1 else "none"},
+            "wall_tok_per_s": gen / (wall_ms * 1e-3), "prefill_ms": prefill_ms,
+            "prefill_tok_per_s": prompt_len / (prefill_ms * 1e-3), "setup_s": setup, "ranks_agree": ranks_agree,
+            "distinct_tokens": len(set(out)), "token_checksum": int(sum((i + 1) * t for i, t in enumerate(out)) % (1 << 31)),
+            "kv_bytes_read_per_token": kv_bytes, "clocks": clocks}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def run_tp(args):
@@ -307,6 +391,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tp", action="store_true",
                     help="tensor-parallel mode: Qwen3-14B projections row-sharded over the ranks with all-gathers")
+    ap.add_argument("--tp-decode", action="store_true",
+                    help="config 4: Qwen3-14B tensor-parallel greedy decode over the ranks (prompt --prompt, --new-tokens)")
+    ap.add_argument("--prompt", type=int, default=32768)
+    ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -320,6 +408,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.tp_decode:
+        return run_tp_decode(args)
     if args.tp:
         return run_tp(args)
 

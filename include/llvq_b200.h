@@ -210,13 +210,30 @@ int llvq_op_qkv_rope_cache_h(const uint16_t* qkv_dev, const uint16_t* q_norm_dev
                              uint8_t* kq_dev, uint16_t* ks_dev, uint16_t* kb_dev, uint8_t* vq_dev, uint16_t* vs_dev,
                              uint16_t* vb_dev, int32_t n_heads, int32_t n_kv, int32_t head_dim, float eps,
                              llvq_stream_t stream);
-/* softmax(q k^T / sqrt(head_dim)) v over positions 0..*pos_dev of the int8 cache, grouped-query heads. */
+/* softmax(q k^T / sqrt(head_dim)) v over positions 0..*pos_dev of the int8 cache, grouped-query heads.
+ * Split-KV: the positions are cut into `splits` equal slices handled by separate CTAs and merged by a
+ * second kernel (splits = 1: single pass, scratch may be NULL). scratch_dev: n_heads * splits *
+ * (head_dim + 2) floats, caller-owned. */
 int llvq_op_attn_decode_int8_h(const uint16_t* q_dev, const uint8_t* kq_dev, const uint16_t* ks_dev, const uint16_t* kb_dev,
                                const uint8_t* vq_dev, const uint16_t* vs_dev, const uint16_t* vb_dev,
                                const int64_t* pos_dev, uint16_t* out_dev, int32_t n_heads, int32_t n_kv, int32_t head_dim,
-                               llvq_stream_t stream);
+                               int32_t splits, float* scratch_dev, llvq_stream_t stream);
 /* y[i] = silu(gate_up[i]) * gate_up[inter + i] */
 int llvq_op_silu_mul_h(const uint16_t* gate_up_dev, uint16_t* y_dev, int32_t inter, llvq_stream_t stream);
+
+/* Greedy head over a tied f16 embedding shard: logits = E[rows, hidden] h in f32, argmax with the
+ * lowest row on ties; writes the best logit and row_offset + its row. The reference reads the
+ * logits back and takes the argmax on the host (llvq-llm/src/model.rs:1041-1073). scratch_dev:
+ * LLVQ_LM_HEAD_SCRATCH_BYTES of device memory, caller-owned. hidden: a multiple of 8 up to 8192. */
+#define LLVQ_LM_HEAD_SCRATCH_BYTES 8192
+int llvq_op_lm_head_argmax_h(const uint16_t* embed_dev, const uint16_t* h_dev, int32_t rows, int32_t hidden,
+                             int64_t row_offset, void* scratch_dev, float* val_out_dev, int64_t* idx_out_dev,
+                             llvq_stream_t stream);
+
+/* Write the matrix as dense f16 [d_out, d_in] (row-major, out_dev caller-owned): what the
+ * reference's dense-decoded run keeps resident (llvq-llm/src/bin/fusedrun.rs:263-278), here a
+ * transient operand for long-prompt GEMMs. An index outside the ball raises the runtime's range flag. */
+int llvq_matrix_dequant_h(llvq_matrix* m, uint16_t* out_dev, llvq_stream_t stream);
 
 /* ---- decode probes --------------------------------------------------------- */
 

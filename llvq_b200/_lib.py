@@ -56,7 +56,10 @@ _SIGNATURES = {
     "llvq_gemv_h_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "llvq_op_add_rmsnorm_h": (C.c_int, [C.c_void_p] * 4 + [C.c_int32, C.c_float, C.c_void_p]),
     "llvq_op_qkv_rope_cache_h": (C.c_int, [C.c_void_p] * 13 + [C.c_int32] * 3 + [C.c_float, C.c_void_p]),
-    "llvq_op_attn_decode_int8_h": (C.c_int, [C.c_void_p] * 9 + [C.c_int32] * 3 + [C.c_void_p]),
+    "llvq_op_lm_head_argmax_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p]),
+    "llvq_matrix_dequant_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llvq_op_attn_decode_int8_h": (C.c_int, [C.c_void_p] * 9 + [C.c_int32] * 4 + [C.c_void_p, C.c_void_p]),
     "llvq_op_silu_mul_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "llvq_gemv_h_host_many": (C.c_int, [C.POINTER(HostCall), C.c_int32, C.c_void_p]),
     "llvq_gemv_f32_host_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -15,6 +15,7 @@
 #include "../../include/llvq_b200.h"
 #include "codebook.h"
 #include "decode_ops.cuh"
+#include "dense_ops.cuh"
 #include "gemm_tc.cuh"
 #include "gemv_sorted.cuh"
 #include "kernels_generic.cuh"
@@ -591,18 +592,25 @@ int llvq_op_qkv_rope_cache_h(const uint16_t* qkv, const uint16_t* q_norm, const 
 
 int llvq_op_attn_decode_int8_h(const uint16_t* q, const uint8_t* kq, const uint16_t* ks, const uint16_t* kb,
                                const uint8_t* vq, const uint16_t* vs, const uint16_t* vb, const int64_t* pos, uint16_t* out,
-                               int32_t n_heads, int32_t n_kv, int32_t head_dim, llvq_stream_t stream) {
+                               int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t splits, float* scratch,
+                               llvq_stream_t stream) {
     if (!q || !kq || !ks || !kb || !vq || !vs || !vb || !pos || !out) return fail(LLVQ_ERR_INVALID, "op_attn_decode: null argument");
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv) return fail(LLVQ_ERR_INVALID, "op_attn_decode: %d heads over %d", n_heads, n_kv);
+    if (splits < 1 || splits > 1024 || (splits > 1 && !scratch))
+        return fail(LLVQ_ERR_INVALID, "op_attn_decode: %d splits need a scratch buffer", splits);
     const KvCacheView kc{(unsigned char*)kq, (__half*)ks, (__half*)kb}, vc{(unsigned char*)vq, (__half*)vs, (__half*)vb};
     cudaStream_t s = (cudaStream_t)stream;
-    if (head_dim == 128)
-        attn_decode_kernel<128><<<n_heads, 128, 0, s>>>((const __half*)q, kc, vc, (const long long*)pos, (__half*)out, n_heads, n_kv);
-    else if (head_dim == 64)
-        attn_decode_kernel<64><<<n_heads, 128, 0, s>>>((const __half*)q, kc, vc, (const long long*)pos, (__half*)out, n_heads, n_kv);
-    else
+    const dim3 grid(n_heads, splits);
+    if (head_dim == 128) {
+        attn_decode_kernel<128><<<grid, 128, 0, s>>>((const __half*)q, kc, vc, (const long long*)pos, (__half*)out, scratch, n_heads, n_kv);
+        if (splits > 1) attn_combine_kernel<128><<<n_heads, 128, 0, s>>>(scratch, (__half*)out, splits);
+    } else if (head_dim == 64) {
+        attn_decode_kernel<64><<<grid, 128, 0, s>>>((const __half*)q, kc, vc, (const long long*)pos, (__half*)out, scratch, n_heads, n_kv);
+        if (splits > 1) attn_combine_kernel<64><<<n_heads, 64, 0, s>>>(scratch, (__half*)out, splits);
+    } else {
         return fail(LLVQ_ERR_UNSUPPORTED, "op_attn_decode: head_dim %d (64 or 128)", head_dim);
-    g_launches++;
+    }
+    g_launches += splits > 1 ? 2 : 1;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
 }
@@ -610,6 +618,40 @@ int llvq_op_attn_decode_int8_h(const uint16_t* q, const uint8_t* kq, const uint1
 int llvq_op_silu_mul_h(const uint16_t* gu, uint16_t* y, int32_t inter, llvq_stream_t stream) {
     if (!gu || !y || inter <= 0) return fail(LLVQ_ERR_INVALID, "op_silu_mul: bad argument");
     silu_mul_kernel<<<(inter + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const __half*)gu, (__half*)y, inter);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+int llvq_op_lm_head_argmax_h(const uint16_t* embed, const uint16_t* h, int32_t rows, int32_t hidden, int64_t row_offset,
+                             void* scratch, float* val_out, int64_t* idx_out, llvq_stream_t stream) {
+    if (!embed || !h || !scratch || !val_out || !idx_out || rows <= 0) return fail(LLVQ_ERR_INVALID, "op_lm_head_argmax: bad argument");
+    if (hidden <= 0 || hidden % 8 || hidden > kHeadMaxHidden)
+        return fail(LLVQ_ERR_UNSUPPORTED, "op_lm_head_argmax: hidden %d (a multiple of 8 up to %d)", hidden, kHeadMaxHidden);
+    if (((uintptr_t)embed & 15u) || ((uintptr_t)h & 15u)) return fail(LLVQ_ERR_INVALID, "op_lm_head_argmax: buffers must be 16-byte aligned");
+    int sms = 0, dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int grid = sms * 4;  // 32 warps per SM, each streaming one row at a time
+    const int want = (rows + kHeadThreads / 32 - 1) / (kHeadThreads / 32);
+    if (grid > want) grid = want;
+    if (grid > kHeadMaxGrid) grid = kHeadMaxGrid;
+    cudaStream_t s = (cudaStream_t)stream;
+    lm_head_argmax_kernel<<<grid, kHeadThreads, 0, s>>>((const __half*)embed, (const __half*)h, rows, hidden, (HeadBest*)scratch);
+    lm_head_pick_kernel<<<1, kHeadMaxGrid, 0, s>>>((const HeadBest*)scratch, grid, (long long)row_offset, val_out, (long long*)idx_out);
+    g_launches += 2;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+int llvq_matrix_dequant_h(llvq_matrix* m, uint16_t* out, llvq_stream_t stream) {
+    if (!m || !out) return fail(LLVQ_ERR_INVALID, "matrix_dequant_h: null argument");
+    llvq_runtime* rt = m->rt;
+    DeviceGuard g(rt->device);
+    const MatrixView mv = m->view();
+    const size_t items = (size_t)mv.d_out * (mv.nb + (mv.tail_w ? 1 : 0));
+    if (items == 0) return LLVQ_OK;
+    dequant_dense_kernel<<<(unsigned int)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(rt->F, rt->T, mv, (__half*)out, rt->d_err);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;

@@ -1,0 +1,140 @@
+// Two helpers around the fused projections that are not on the batch-1 hot path:
+//
+//   dequant_dense_kernel   writes a matrix as dense f16 [d_out, d_in] (codes decoded once, gain, row
+//                          scale and shell norm applied, tail columns copied). It feeds a transient
+//                          cuBLAS GEMM for long prompts, where the contraction is compute-bound and a
+//                          dense tile is the right operand; the reference's dense-decoded run
+//                          (llvq-llm/src/bin/fusedrun.rs:263-278) is the same weights kept resident.
+//   lm_head_argmax_kernel  greedy head over a tied f16 embedding: logits = E h in f32 with a fixed
+//   lm_head_pick_kernel    summation order per row, argmax with the lowest index on ties. A row's logit
+//                          does not depend on how the vocabulary is split over CTAs or GPUs, so a
+//                          sharded head picks the same token as a whole one (the reference reads the
+//                          logits back and takes the argmax on the host, llvq-llm/src/model.rs:1041-1073).
+#pragma once
+#include <cuda_fp16.h>
+
+#include "decode_fast.cuh"
+#include "decode_generic.cuh"
+#include "kernels_generic.cuh"
+
+namespace llvq {
+
+__global__ void __launch_bounds__(256)
+dequant_dense_kernel(FastTables F, DevTables G, MatrixView mv, __half* __restrict__ out, int* __restrict__ err_flag) {
+    const size_t item = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int per_row = mv.nb + (mv.tail_w ? 1 : 0);
+    if (item >= (size_t)mv.d_out * per_row) return;
+    const int r = (int)(item / per_row), b = (int)(item % per_row);
+    __half* dst = out + (size_t)r * mv.d_in + (size_t)b * kDim;
+    const float rs = mv.rscale[r];
+    if (b == mv.nb) {  // the tail columns of this row, already in weight units
+        for (int t = 0; t < mv.tail_w; ++t) {
+            const float w = mv.tail_f16 ? __half2float(((const __half*)mv.tail)[(size_t)r * mv.tail_w + t])
+                                        : ((const float*)mv.tail)[(size_t)r * mv.tail_w + t];
+            dst[t] = __float2half_rn(w);
+        }
+        return;
+    }
+    const unsigned long long v = load_code48(mv.codes, (size_t)r * mv.nb + b);
+    const float2 cent = mv.cent[r];
+    const float gain = (v & 1ull) ? cent.y : cent.x;
+    float w[kDim];
+    float scale = 0.0f, slow_scale = 0.0f;
+    const int path = decode_fast_any(
+        F, v >> 1, [&](int pos, float val) { w[pos] = val; },
+        [&](unsigned long long idx) { decode_generic12(G, idx, [&](int pos, int val) { w[pos] = (float)val; }, &slow_scale); },
+        &scale);
+    if (path == (int)kPathSlow) scale = slow_scale;
+    if (path == -2 && err_flag) atomicExch(err_flag, 1);  // an index outside the ball decodes to zeros
+    const float f = gain * scale * rs;
+#pragma unroll
+    for (int pos = 0; pos < kDim; ++pos) dst[pos] = __float2half_rn(w[pos] * f);
+}
+
+constexpr int kHeadThreads = 256;   // 8 warps, one embedding row per warp and step
+constexpr int kHeadMaxGrid = 1024;  // partial (value, row) pairs the pick kernel merges
+constexpr int kHeadMaxHidden = 8192;
+
+struct HeadBest {
+    float val;
+    int row;
+};
+
+__device__ __forceinline__ bool head_better(float v, int r, float bv, int br) { return v > bv || (v == bv && r < br); }
+
+// embed: [rows, hidden] f16 (16-byte aligned rows: hidden % 8 == 0); h: [hidden] f16.
+__global__ void __launch_bounds__(kHeadThreads)
+lm_head_argmax_kernel(const __half* __restrict__ embed, const __half* __restrict__ h, int rows, int hidden,
+                      HeadBest* __restrict__ partial) {
+    __shared__ __align__(16) __half hs[kHeadMaxHidden];
+    __shared__ HeadBest red[kHeadThreads / 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < hidden / 8; i += kHeadThreads)
+        reinterpret_cast<uint4*>(hs)[i] = reinterpret_cast<const uint4*>(h)[i];
+    __syncthreads();
+    const int vec = hidden / 8;
+    float best = -INFINITY;
+    int best_row = 0x7fffffff;
+    for (int r = blockIdx.x * (kHeadThreads / 32) + warp; r < rows; r += gridDim.x * (kHeadThreads / 32)) {
+        const uint4* src = reinterpret_cast<const uint4*>(embed + (size_t)r * hidden);
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int i = lane; i < vec; i += 32) {
+            const uint4 e = __ldg(src + i);
+            const uint4 a = reinterpret_cast<const uint4*>(hs)[i];
+            const __half2* eh = reinterpret_cast<const __half2*>(&e);
+            const __half2* ah = reinterpret_cast<const __half2*>(&a);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 ef = __half22float2(eh[j]), af = __half22float2(ah[j]);
+                acc = fmaf(ef.x, af.x, acc);
+                acc = fmaf(ef.y, af.y, acc);
+            }
+        }
+        acc = warp_sum_f(acc);  // xor butterfly: every lane ends with the same sum, same order for every row
+        if (head_better(acc, r, best, best_row)) {
+            best = acc;
+            best_row = r;
+        }
+    }
+    if (lane == 0) red[warp] = HeadBest{best, best_row};
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        HeadBest b = red[0];
+        for (int w = 1; w < kHeadThreads / 32; ++w)
+            if (head_better(red[w].val, red[w].row, b.val, b.row)) b = red[w];
+        partial[blockIdx.x] = b;
+    }
+}
+
+// One CTA: merge the partials; the row index is reported with `row_offset` added (a vocabulary shard).
+__global__ void __launch_bounds__(kHeadMaxGrid)
+lm_head_pick_kernel(const HeadBest* __restrict__ partial, int n, long long row_offset, float* __restrict__ val_out,
+                    long long* __restrict__ idx_out) {
+    __shared__ HeadBest red[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    HeadBest b = threadIdx.x < n ? partial[threadIdx.x] : HeadBest{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v = __shfl_xor_sync(0xffffffffu, b.val, o);
+        const int r = __shfl_xor_sync(0xffffffffu, b.row, o);
+        if (head_better(v, r, b.val, b.row)) b = HeadBest{v, r};
+    }
+    if (lane == 0) red[warp] = b;
+    __syncthreads();
+    if (warp == 0) {
+        b = red[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float v = __shfl_xor_sync(0xffffffffu, b.val, o);
+            const int r = __shfl_xor_sync(0xffffffffu, b.row, o);
+            if (head_better(v, r, b.val, b.row)) b = HeadBest{v, r};
+        }
+        if (lane == 0) {
+            *val_out = b.val;
+            *idx_out = row_offset + (b.row == 0x7fffffff ? 0 : b.row);  // all-NaN logits: row 0
+        }
+    }
+}
+
+}  // namespace llvq

@@ -66,6 +66,11 @@ def kv_dequantize(q, s, mn):
     return (g * s.float().unsqueeze(-1) + mn.float().unsqueeze(-1)).half().flatten(-2)
 
 
+def _silu(x):
+    import torch
+    return torch.nn.functional.silu(x)
+
+
 class Int8KvCache:
     """Fixed-capacity int8 KV cache of one block: [capacity, n_kv, head_dim] codes + per-group f16 scale/bias."""
 
@@ -83,33 +88,77 @@ class Int8KvCache:
         self.s[which].index_copy_(0, pos, s)
         self.b[which].index_copy_(0, pos, b)
 
-    def read(self, which: int):
-        return kv_dequantize(self.q[which], self.s[which], self.b[which])
+    def read(self, which: int, end: Optional[int] = None):
+        return kv_dequantize(self.q[which][:end], self.s[which][:end], self.b[which][:end])
 
     def bytes_per_position(self) -> int:
         return 2 * (self.q[0][0].numel() + 2 * 2 * self.s[0][0].numel())
 
 
+class TpGroup:
+    """Rank layout of a tensor-parallel model: rank r of `world` holds q heads [r H/world, (r+1) H/world),
+    the matching kv heads, rows [r I/world, ...) of gate/up, rows [r D/world, ...) of o/down and rows
+    [r V/world, ...) of the tied head. Every exchange is an all-gather of row shards in rank order."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+
+    def check(self, cfg: Qwen3Config) -> None:
+        for name, n in (("q heads", cfg.n_heads), ("kv heads", cfg.n_kv), ("intermediate rows", cfg.inter),
+                        ("hidden rows", cfg.hidden), ("vocabulary rows", cfg.vocab)):
+            if n % self.world:
+                raise ValueError(f"{n} {name} do not split over {self.world} ranks")
+
+    def gather_into(self, out, shard):
+        """out[world * n] <- shards [n] in rank order (1-D, preallocated: safe inside a graph capture)."""
+        self.dist.all_gather_into_tensor(out, shard, group=self.group)
+        return out
+
+    def gather_cols(self, shard):
+        """[L, n] shards -> [L, world * n]."""
+        import torch
+        L, n = shard.shape
+        buf = torch.empty(self.world * L, n, dtype=shard.dtype, device=shard.device)
+        self.dist.all_gather_into_tensor(buf, shard.contiguous(), group=self.group)
+        return buf.view(self.world, L, n).permute(1, 0, 2).reshape(L, self.world * n)
+
+
 class FusedQwen3:
-    """`proj(name_group, x)` hooks let the same loop run on fused projections or on a dense stand-in."""
+    """`gemv` / `gemm` / `head` hooks let the same loop run on fused projections or on a dense stand-in.
+    With a `TpGroup` the handles in `blocks` are this rank's row shards and `embed_head` its vocabulary rows."""
 
     def __init__(self, cfg: Qwen3Config, blocks: Sequence[dict], embed, final_norm, capacity: int,
-                 gemv: Callable, gemm: Callable, kv_int8: bool = True, ops=None):
+                 gemv: Callable, gemm: Callable, head: Callable, kv_int8: bool = True, ops=None,
+                 tp: Optional[TpGroup] = None, prefill_chunk: int = 2048):
         """blocks[i]: {"qkv", "o", "gate_up", "down": projection handles, "ln1", "ln2", "q_norm", "k_norm": f16 tensors}.
-        gemv(handle, x[d_in]) -> y[d_out]; gemm(handle, X[L, d_in]) -> Y[L, d_out] (both f16 on the GPU)."""
+        gemv(handle, x[d_in]) -> y[d_out]; gemm(handle, X[L, d_in]) -> Y[L, d_out] (both f16);
+        head(E[rows, hidden], h[hidden], row_offset) -> (best logit f32 [1], its row int64 [1])."""
         import torch
         self.cfg, self.blocks, self.embed, self.final_norm = cfg, list(blocks), embed, final_norm
-        self.gemv, self.gemm, self.capacity, self.kv_int8 = gemv, gemm, capacity, kv_int8
+        self.gemv, self.gemm, self.head, self.capacity, self.kv_int8 = gemv, gemm, head, capacity, kv_int8
+        self.tp = tp if tp is not None and tp.world > 1 else None
+        self.world = self.tp.world if self.tp else 1
+        self.rank = self.tp.rank if self.tp else 0
+        if self.tp:
+            self.tp.check(cfg)
+        self.h_loc, self.kv_loc, self.inter_loc = cfg.n_heads // self.world, cfg.n_kv // self.world, cfg.inter // self.world
+        self.prefill_chunk = prefill_chunk
+        self.sdpa_from = 1 << 28  # bytes of f32 scores above which the prompt attention is the library's fused kernel
         dev = embed.device
         self.device = dev
+        v_loc = cfg.vocab // self.world
+        self.embed_head = embed[self.rank * v_loc:(self.rank + 1) * v_loc]
+        self.head_offset = self.rank * v_loc
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=dev, dtype=torch.float32) / cfg.head_dim))
         ang = torch.arange(capacity, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
         self.cos, self.sin = ang.cos(), ang.sin()
         self.positions = torch.arange(capacity, device=dev)
         if kv_int8:
-            self.caches = [Int8KvCache(capacity, cfg.n_kv, cfg.head_dim, dev) for _ in blocks]
+            self.caches = [Int8KvCache(capacity, self.kv_loc, cfg.head_dim, dev) for _ in blocks]
         else:
-            self.caches = [[torch.zeros(capacity, cfg.n_kv, cfg.head_dim, dtype=torch.float16, device=dev) for _ in range(2)]
+            self.caches = [[torch.zeros(capacity, self.kv_loc, cfg.head_dim, dtype=torch.float16, device=dev) for _ in range(2)]
                            for _ in blocks]
         self._graph = None
         # `ops`: the C library (llvq_op_* kernels). With it and an int8 cache the token step runs the fused
@@ -117,14 +166,25 @@ class FusedQwen3:
         self.ops = ops if kv_int8 else None
         if self.ops is not None:
             f16 = dict(dtype=torch.float16, device=dev)
+            hd, w = cfg.head_dim, self.world
             self._x, self._h = torch.zeros(cfg.hidden, **f16), torch.zeros(cfg.hidden, **f16)
-            self._qkv = torch.zeros((cfg.n_heads + 2 * cfg.n_kv) * cfg.head_dim, **f16)
-            self._q, self._ctx = (torch.zeros(cfg.n_heads * cfg.head_dim, **f16) for _ in range(2))
-            self._o, self._down = torch.zeros(cfg.hidden, **f16), torch.zeros(cfg.hidden, **f16)
-            self._gu, self._act = torch.zeros(2 * cfg.inter, **f16), torch.zeros(cfg.inter, **f16)
+            self._qkv = torch.zeros((self.h_loc + 2 * self.kv_loc) * hd, **f16)
+            self._q = torch.zeros(self.h_loc * hd, **f16)
+            self._ctx, self._o, self._down = (torch.zeros(n, **f16) for n in (cfg.n_heads * hd, cfg.hidden, cfg.hidden))
+            self._gu, self._act = torch.zeros(2 * self.inter_loc, **f16), torch.zeros(cfg.inter, **f16)
+            # the shard a rank computes before the gather; the full buffer itself when there is one rank
+            self._ctx_loc = torch.zeros(self.h_loc * hd, **f16) if w > 1 else self._ctx
+            self._o_loc = torch.zeros(cfg.hidden // w, **f16) if w > 1 else self._o
+            self._down_loc = torch.zeros(cfg.hidden // w, **f16) if w > 1 else self._down
+            self._act_loc = torch.zeros(self.inter_loc, **f16) if w > 1 else self._act
+            # split-KV attention: one slice per ~256 cached positions, enough CTAs to fill the GPU at long contexts
+            self.attn_splits = max(1, min(64, capacity // 256))
+            self._attn_ws = torch.zeros(self.h_loc * self.attn_splits * (hd + 2), dtype=torch.float32, device=dev)
         # the token and its position live in fixed device tensors: a captured graph keeps their addresses
         self._tok = torch.zeros(1, dtype=torch.long, device=dev)
         self._pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self._best = torch.zeros(2, dtype=torch.long, device=dev)        # (logit bits, row) of this rank's shard
+        self._best_all = torch.zeros(2 * self.world, dtype=torch.long, device=dev)
 
     # ---- pieces ------------------------------------------------------------------
     def _rms(self, x, w):
@@ -139,65 +199,103 @@ class FusedQwen3:
         return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).half()
 
     def _proj(self, handle, h):
-        return self.gemv(handle, h[0])[None, :] if h.shape[0] == 1 else self.gemm(handle, h)
+        return self.gemv(handle, h[0])[None, :] if h.shape[0] == 1 else self.gemm(handle, h.contiguous())
 
-    def _block(self, i: int, x, pos):
-        """x: [L, hidden] f16, pos: int64 [L] absolute positions (consecutive)."""
+    def _all(self, shard):
+        return self.tp.gather_cols(shard) if self.tp else shard
+
+    def _attend(self, q, k_all, v_all, pos, end):
+        """q: [L, heads, hd]; k_all, v_all: [T, kv heads, hd] (cache contents); causal over absolute positions."""
         import torch
+        cfg = self.cfg
+        L, T = q.shape[0], k_all.shape[0]
+        groups = q.shape[1] // k_all.shape[1]
+        visible = self.positions[None, :T] <= pos[:, None]  # causal, and nothing beyond the write head
+        if L * T * q.shape[1] * 4 > self.sdpa_from:
+            # long prompts: the library's fused attention on f16 operands, scores never materialised
+            kh = k_all.repeat_interleave(groups, dim=1).permute(1, 0, 2)[None]
+            vh = v_all.repeat_interleave(groups, dim=1).permute(1, 0, 2)[None]
+            out = torch.nn.functional.scaled_dot_product_attention(q.permute(1, 0, 2)[None], kh, vh, attn_mask=visible[None, None])
+            return out[0].permute(1, 0, 2).reshape(L, -1)
+        kf = k_all.float().repeat_interleave(groups, dim=1)   # [T, heads, hd]
+        vf = v_all.float().repeat_interleave(groups, dim=1)
+        scores = torch.einsum("lhd,thd->hlt", q.float(), kf) * (1.0 / cfg.head_dim ** 0.5)
+        scores = scores.masked_fill(~visible[None], float("-inf"))
+        return torch.einsum("hlt,thd->lhd", torch.softmax(scores, dim=-1), vf).half().reshape(L, -1)
+
+    def _block(self, i: int, x, pos, end: Optional[int] = None):
+        """x: [L, hidden] f16, pos: int64 [L] absolute positions (consecutive); attention reads cache
+        positions [0, end) (the whole cache when the caller does not know the write head on the host)."""
         cfg, blk = self.cfg, self.blocks[i]
-        L = x.shape[0]
+        L, hd = x.shape[0], cfg.head_dim
+        end = self.capacity if end is None else end
         h = self._rms(x, blk["ln1"])
         qkv = self._proj(blk["qkv"], h)
-        nq, nk = cfg.n_heads * cfg.head_dim, cfg.n_kv * cfg.head_dim
-        q = qkv[:, :nq].reshape(L, cfg.n_heads, cfg.head_dim)
-        k = qkv[:, nq:nq + nk].reshape(L, cfg.n_kv, cfg.head_dim)
-        v = qkv[:, nq + nk:].reshape(L, cfg.n_kv, cfg.head_dim)
+        nq, nk = self.h_loc * hd, self.kv_loc * hd
+        q = qkv[:, :nq].reshape(L, self.h_loc, hd)
+        k = qkv[:, nq:nq + nk].reshape(L, self.kv_loc, hd)
+        v = qkv[:, nq + nk:].reshape(L, self.kv_loc, hd)
         q = self._rope(self._rms(q, blk["q_norm"]), pos)
         k = self._rope(self._rms(k, blk["k_norm"]), pos)
         cache = self.caches[i]
         if self.kv_int8:
             cache.write(0, pos, k)
             cache.write(1, pos, v.contiguous())
-            k_all, v_all = cache.read(0), cache.read(1)
+            k_all, v_all = cache.read(0, end), cache.read(1, end)
         else:
             cache[0].index_copy_(0, pos, k)
             cache[1].index_copy_(0, pos, v.contiguous())
-            k_all, v_all = cache[0], cache[1]
-        groups = cfg.n_heads // cfg.n_kv
-        kf = k_all.float().repeat_interleave(groups, dim=1)   # [T, heads, hd]
-        vf = v_all.float().repeat_interleave(groups, dim=1)
-        scores = torch.einsum("lhd,thd->hlt", q.float(), kf) * (1.0 / cfg.head_dim ** 0.5)
-        visible = self.positions[None, None, :] <= pos[None, :, None]  # causal, and nothing beyond the write head
-        scores = scores.masked_fill(~visible, float("-inf"))
-        ctx = torch.einsum("hlt,thd->lhd", torch.softmax(scores, dim=-1), vf).half().reshape(L, nq)
-        x = x + self._proj(blk["o"], ctx)
+            k_all, v_all = cache[0][:end], cache[1][:end]
+        ctx = self._all(self._attend(q, k_all, v_all, pos, end))
+        x = x + self._all(self._proj(blk["o"], ctx))
         h = self._rms(x, blk["ln2"])
         gu = self._proj(blk["gate_up"], h)
-        gated = (torch.nn.functional.silu(gu[:, :cfg.inter].float()) * gu[:, cfg.inter:].float()).half()
-        return x + self._proj(blk["down"], gated)
+        gated = (_silu(gu[:, :self.inter_loc].float()) * gu[:, self.inter_loc:].float()).half()
+        return x + self._all(self._proj(blk["down"], self._all(gated)))
 
-    def hidden(self, tokens, pos):
+    def hidden(self, tokens, pos, end: Optional[int] = None):
         x = self.embed.index_select(0, tokens)
         for i in range(len(self.blocks)):
-            x = self._block(i, x, pos)
+            x = self._block(i, x, pos, end)
         return x
 
+    def prefill(self, prompt: Sequence[int]):
+        """Run the prompt through the blocks in chunks of `prefill_chunk` tokens (each chunk attends to the
+        cache written so far); returns the hidden state of the last prompt token, [1, hidden]."""
+        import torch
+        toks = torch.tensor(list(prompt), device=self.device, dtype=torch.long)
+        x = None
+        for lo in range(0, len(prompt), self.prefill_chunk):
+            hi = min(len(prompt), lo + self.prefill_chunk)
+            x = self.hidden(toks[lo:hi], self.positions[lo:hi], end=hi)
+        return x[-1:]
+
+    def pick(self, h):
+        """Greedy token of the normalised hidden state h [hidden] -> int64 [1] (device)."""
+        val, idx = self.head(self.embed_head, h, self.head_offset)
+        if not self.tp:
+            return idx
+        self._best[0:1].view(val.dtype)[0:1].copy_(val)
+        self._best[1:2].copy_(idx)
+        self.tp.gather_into(self._best_all, self._best)
+        pairs = self._best_all.view(self.world, 2)
+        vals = pairs[:, 0:1].contiguous().view(val.dtype)[:, 0]
+        return pairs[:, 1].index_select(0, vals.argmax().reshape(1))  # first rank on ties = lowest row
+
     def logits_last(self, x):
+        """Full logits of the last row (diagnostics; the loop itself uses `pick`)."""
         h = self._rms(x[-1:], self.final_norm)
         return (h @ self.embed.t()).float()[0]
 
     # ---- the loop ----------------------------------------------------------------
     def generate(self, prompt: Sequence[int], max_new: int, use_graph: bool = False) -> List[int]:
         """Greedy continuation, `Qwen3::generate` (model.rs:1041-1073): prefill, then one token at a time."""
-        import torch
         if max_new == 0:
             return []
         n = len(prompt)
         if n + max_new > self.capacity:
             raise ValueError(f"{n} prompt + {max_new} new tokens exceed the cache capacity {self.capacity}")
-        toks = torch.tensor(list(prompt), device=self.device, dtype=torch.long)
-        x = self.hidden(toks, self.positions[:n])
-        nxt = self.logits_last(x).argmax()
+        nxt = self.pick(self._rms(self.prefill(prompt), self.final_norm)[0])
         out = [int(nxt)]
         self.start_decode(nxt, n)
         step = self._graph_step if use_graph else self._eager_step
@@ -215,15 +313,16 @@ class FusedQwen3:
         if self.ops is not None:
             return self._fused_step()
         x = self.hidden(self._tok, self._pos)
-        self._tok.copy_(self.logits_last(x).argmax().reshape(1))
+        self._tok.copy_(self.pick(self._rms(x[-1:], self.final_norm)[0]))
         self._pos += 1
 
     def _fused_step(self):
-        """One token: 4 fused GEMV launches and 4 small fused kernels per block, nothing else."""
+        """One token: 4 fused GEMV launches and 4 small fused kernels per block (+ 4 all-gathers of row
+        shards on a tensor-parallel model), then the greedy head."""
         import ctypes as C
         import torch
         from ._lib import check
-        L, cfg = self.ops, self.cfg
+        L, cfg, tp = self.ops, self.cfg, self.tp
         st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         p = lambda t: C.c_void_p(t.data_ptr())
         self._x.copy_(self.embed.index_select(0, self._tok)[0])
@@ -234,19 +333,27 @@ class FusedQwen3:
             self.gemv(blk["qkv"], self._h, out=self._qkv)
             check(L.llvq_op_qkv_rope_cache_h(p(self._qkv), p(blk["q_norm"]), p(blk["k_norm"]), p(self.cos), p(self.sin),
                                              p(self._pos), p(self._q), p(cache.q[0]), p(cache.s[0]), p(cache.b[0]),
-                                             p(cache.q[1]), p(cache.s[1]), p(cache.b[1]), cfg.n_heads, cfg.n_kv,
+                                             p(cache.q[1]), p(cache.s[1]), p(cache.b[1]), self.h_loc, self.kv_loc,
                                              cfg.head_dim, cfg.eps, st))
             check(L.llvq_op_attn_decode_int8_h(p(self._q), p(cache.q[0]), p(cache.s[0]), p(cache.b[0]), p(cache.q[1]),
-                                               p(cache.s[1]), p(cache.b[1]), p(self._pos), p(self._ctx), cfg.n_heads,
-                                               cfg.n_kv, cfg.head_dim, st))
-            self.gemv(blk["o"], self._ctx, out=self._o)
+                                               p(cache.s[1]), p(cache.b[1]), p(self._pos), p(self._ctx_loc), self.h_loc,
+                                               self.kv_loc, cfg.head_dim, self.attn_splits, p(self._attn_ws), st))
+            if tp:
+                tp.gather_into(self._ctx, self._ctx_loc)
+            self.gemv(blk["o"], self._ctx, out=self._o_loc)
+            if tp:
+                tp.gather_into(self._o, self._o_loc)
             check(L.llvq_op_add_rmsnorm_h(p(self._x), p(self._o), p(blk["ln2"]), p(self._h), cfg.hidden, cfg.eps, st))
             self.gemv(blk["gate_up"], self._h, out=self._gu)
-            check(L.llvq_op_silu_mul_h(p(self._gu), p(self._act), cfg.inter, st))
-            self.gemv(blk["down"], self._act, out=self._down)
+            check(L.llvq_op_silu_mul_h(p(self._gu), p(self._act_loc), self.inter_loc, st))
+            if tp:
+                tp.gather_into(self._act, self._act_loc)
+            self.gemv(blk["down"], self._act, out=self._down_loc)
+            if tp:
+                tp.gather_into(self._down, self._down_loc)
             delta = self._down
         check(L.llvq_op_add_rmsnorm_h(p(self._x), p(delta), p(self.final_norm), p(self._h), cfg.hidden, cfg.eps, st))
-        self._tok.copy_((self._h[None, :] @ self.embed.t()).float()[0].argmax().reshape(1))
+        self._tok.copy_(self.pick(self._h))
         self._pos += 1
 
     def _graph_step(self):
@@ -268,34 +375,89 @@ class FusedQwen3:
         self._graph.replay()
 
 
+def kernel_head(lib):
+    """The greedy-head hook backed by llvq_op_lm_head_argmax_h (scratch and outputs allocated once per device)."""
+    import ctypes as C
+    import torch
+    from ._lib import check
+    state = {}
+
+    def head(embed_rows, h, row_offset):
+        dev = embed_rows.device
+        if dev not in state:
+            state[dev] = (torch.zeros(8192, dtype=torch.uint8, device=dev), torch.zeros(1, dtype=torch.float32, device=dev),
+                          torch.zeros(1, dtype=torch.long, device=dev))
+        scratch, val, idx = state[dev]
+        if not embed_rows.is_contiguous() or h.dtype != torch.float16 or embed_rows.dtype != torch.float16:
+            raise ValueError("head: contiguous f16 embedding rows and an f16 hidden state")
+        check(lib.llvq_op_lm_head_argmax_h(C.c_void_p(embed_rows.data_ptr()), C.c_void_p(h.data_ptr()), embed_rows.shape[0],
+                                           embed_rows.shape[1], row_offset, C.c_void_p(scratch.data_ptr()),
+                                           C.c_void_p(val.data_ptr()), C.c_void_p(idx.data_ptr()),
+                                           C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return val, idx
+
+    return head
+
+
+def tp_rows(cfg: Qwen3Config, world: int, rank: int) -> dict:
+    """[lo, hi) of the rows of each projection that `rank` holds (whole heads for q, k, v)."""
+    hd = cfg.head_dim
+    hq, hk, it, hid = cfg.n_heads // world * hd, cfg.n_kv // world * hd, cfg.inter // world, cfg.hidden // world
+    return {"q": (rank * hq, (rank + 1) * hq), "k": (rank * hk, (rank + 1) * hk), "v": (rank * hk, (rank + 1) * hk),
+            "o": (rank * hid, (rank + 1) * hid), "gate": (rank * it, (rank + 1) * it), "up": (rank * it, (rank + 1) * it),
+            "down": (rank * hid, (rank + 1) * hid)}
+
+
 def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: int = 0x51, layers: Optional[int] = None,
-                    kv_int8: bool = True, fused_ops: bool = True):
+                    kv_int8: bool = True, fused_ops: bool = True, tp: Optional[TpGroup] = None, dense_prefill_from: int = 1024,
+                    keep_host: bool = True, device_codes: bool = False):
     """Random-weight model of BASELINE config 2/4: LLVQ codes for every projection, f16 N(0, 0.02)
-    norms and tied embedding (norm weights are 1 + N(0, 0.02) so that activations keep their scale)."""
+    norms and tied embedding (norm weights are 1 + N(0, 0.02) so that activations keep their scale).
+    With `tp` every rank draws and uploads only its own rows of each matrix (the same matrices for any
+    world size; `device_codes` draws the codes on the GPU, for models too large to draw on the host in
+    reasonable time). Prompts of `dense_prefill_from` rows or more go through a transient dense copy of each
+    projection and a library GEMM. Returns (model, host matrices per layer or [] when keep_host is off)."""
     import torch
     from . import synth
     n_layers = layers or cfg.layers
     dev = torch.device("cuda", rt.device)
     g = synth.SplitMix64(seed)
+    world, rank = (tp.world, tp.rank) if tp else (1, 0)
+    if tp:
+        tp.check(cfg)
+    rows = tp_rows(cfg, world, rank)
     mats, blocks = [], []
 
     def f16(n, base=0.0):
         return torch.from_numpy((base + 0.02 * g.gaussian(n)).astype(np.float16)).to(dev)
 
+    shp = {"q": (cfg.n_heads * cfg.head_dim, cfg.hidden), "k": (cfg.n_kv * cfg.head_dim, cfg.hidden),
+           "v": (cfg.n_kv * cfg.head_dim, cfg.hidden), "o": (cfg.hidden, cfg.n_heads * cfg.head_dim),
+           "gate": (cfg.inter, cfg.hidden), "up": (cfg.inter, cfg.hidden), "down": (cfg.hidden, cfg.inter)}
     for l in range(n_layers):
-        shp = {"q": (cfg.n_heads * cfg.head_dim, cfg.hidden), "k": (cfg.n_kv * cfg.head_dim, cfg.hidden),
-               "v": (cfg.n_kv * cfg.head_dim, cfg.hidden), "o": (cfg.hidden, cfg.n_heads * cfg.head_dim),
-               "gate": (cfg.inter, cfg.hidden), "up": (cfg.inter, cfg.hidden), "down": (cfg.hidden, cfg.inter)}
-        m = {n: synth.make_matrix(do, di, synth.matrix_seed(config_id, l, synth.PROJ_IDS[n]), f"l{l}.{n}")
-             for n, (do, di) in shp.items()}
-        mats.append(m)
+        if device_codes:
+            m = {n: synth.make_matrix_rows_cuda(do, di, synth.matrix_seed(config_id, l, synth.PROJ_IDS[n]), *rows[n], device=dev,
+                                                name=f"l{l}.{n}") for n, (do, di) in shp.items()}
+        else:
+            m = {n: synth.make_matrix_rows(do, di, synth.matrix_seed(config_id, l, synth.PROJ_IDS[n]), *rows[n], name=f"l{l}.{n}")
+                 for n, (do, di) in shp.items()}
+        if keep_host:
+            mats.append(m)
         blocks.append({"qkv": rt.upload_group([m["q"], m["k"], m["v"]], tail_f16=True), "o": rt.upload(m["o"], tail_f16=True),
                        "gate_up": rt.upload_group([m["gate"], m["up"]], tail_f16=True),
                        "down": rt.upload(m["down"], tail_f16=True),
                        "ln1": f16(cfg.hidden, 1.0), "ln2": f16(cfg.hidden, 1.0),
                        "q_norm": f16(cfg.head_dim, 1.0), "k_norm": f16(cfg.head_dim, 1.0)})
-    embed = f16(cfg.vocab * cfg.hidden).reshape(cfg.vocab, cfg.hidden)
+    if device_codes:
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        embed = (0.02 * torch.randn(cfg.vocab, cfg.hidden, device=dev, generator=gen)).half()
+    else:
+        embed = f16(cfg.vocab * cfg.hidden).reshape(cfg.vocab, cfg.hidden)
     final_norm = f16(cfg.hidden, 1.0)
-    model = FusedQwen3(cfg, blocks, embed, final_norm, capacity, gemv=rt.forward, gemm=rt.forward_batch, kv_int8=kv_int8,
-                       ops=rt.lib if fused_ops else None)
+
+    def gemm(proj, x):
+        return rt.forward_batch_dense(proj, x) if x.shape[0] >= dense_prefill_from else rt.forward_batch(proj, x)
+
+    model = FusedQwen3(cfg, blocks, embed, final_norm, capacity, gemv=rt.forward, gemm=gemm, head=kernel_head(rt.lib),
+                       kv_int8=kv_int8, ops=rt.lib if fused_ops else None, tp=tp)
     return model, mats

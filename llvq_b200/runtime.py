@@ -141,6 +141,28 @@ class FusedRuntime:
         check(self.lib.llvq_gemm_h(proj._h, x.data_ptr(), y.data_ptr(), x.shape[0], self._stream()))
         return y
 
+    def dequant(self, proj: FusedProj, out=None):
+        """The projection as dense f16 [d_out, d_in] (a transient operand: nothing keeps it)."""
+        import torch
+        w = out if out is not None else torch.empty(proj.d_out, proj.d_in, dtype=torch.float16,
+                                                    device=torch.device("cuda", self.device))
+        if w.dtype != torch.float16 or w.numel() != proj.d_out * proj.d_in or not w.is_contiguous():
+            raise ValueError("dequant: out must be a contiguous f16 tensor of d_out * d_in elements")
+        check(self.lib.llvq_matrix_dequant_h(proj._h, w.data_ptr(), self._stream()))
+        return w.view(proj.d_out, proj.d_in)
+
+    def forward_batch_dense(self, proj: FusedProj, x):
+        """f16 [B, d_in] -> f16 [B, d_out] for long prompts: the codes are decoded once into a transient
+        dense matrix (one reused buffer per runtime) and the contraction is a library GEMM."""
+        import torch
+        if x.dim() != 2 or x.shape[1] != proj.d_in or x.dtype != torch.float16:
+            raise ValueError("forward_batch_dense: x must be an f16 [B, d_in] tensor")
+        need = proj.d_out * proj.d_in
+        if getattr(self, "_dense_buf", None) is None or self._dense_buf.numel() < need:
+            self._dense_buf = torch.empty(need, dtype=torch.float16, device=x.device)
+        w = self.dequant(proj, out=self._dense_buf[:need])
+        return x @ w.t()
+
     def forward_host(self, proj: FusedProj, x_host: np.ndarray, y_host: np.ndarray):
         """Host buffers in and out (copies inside the call); returns after the result has landed."""
         if x_host.dtype == np.float32:

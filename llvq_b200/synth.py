@@ -43,6 +43,11 @@ class SplitMix64:
             z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
             return z ^ (z >> np.uint64(31))
 
+    def skip(self, n: int) -> None:
+        """Jump over n outputs (the generator is a counter: state advances by n * gamma)."""
+        with np.errstate(over="ignore"):
+            self.state = np.uint64(self.state + np.uint64(n) * _GAMMA)
+
     def uniform(self, n: int) -> np.ndarray:
         return (self.take(n) >> np.uint64(11)).astype(np.float64) * (1.0 / 9007199254740992.0)
 
@@ -95,6 +100,60 @@ class SynthMatrix:
 
 def matrix_seed(config: int, layer: int, proj: int) -> int:
     return SEED_BASE | (config << 24) | (layer << 8) | proj
+
+
+def make_matrix_rows(d_out: int, d_in: int, seed: int, lo: int, hi: int, name: str = "w") -> SynthMatrix:
+    """Rows [lo, hi) of make_matrix(d_out, d_in, seed), drawn without generating the other rows: what one
+    rank of a row-sharded projection needs (equal to make_matrix(...).rows(lo, hi) bit for bit)."""
+    g = SplitMix64(seed)
+    nb, tw = d_in // DIM, d_in % DIM
+    n_loc = hi - lo
+
+    def window(per_row, draw):
+        g.skip(lo * per_row)
+        out = draw(n_loc * per_row)
+        g.skip((d_out - hi) * per_row)
+        return out
+
+    idx = window(nb, lambda k: g.take(k)) % np.uint64(N12 + 1)
+    gain = window(nb, lambda k: g.take(k)) & np.uint64(1)
+    cen = np.sort(0.5 + g.uniform(2)).astype(np.float32).astype(np.float64)
+    # a normal consumes two outputs: the windows below skip in units of two
+    g.skip(2 * lo)
+    rs = np.abs(0.02 * g.gaussian(n_loc))
+    g.skip(2 * (d_out - hi))
+    g.skip(2 * lo * tw)
+    tail = (0.02 * g.gaussian(n_loc * tw)).astype(np.float32).reshape(n_loc, tw)
+    return SynthMatrix(f"{name}[{lo}:{hi}]", n_loc, d_in, pack_codes(idx, gain), cen, rs, tail)
+
+
+def make_matrix_rows_cuda(d_out: int, d_in: int, seed: int, lo: int, hi: int, device, tiles: int = 8,
+                          name: str = "w") -> SynthMatrix:
+    """Rows [lo, hi) of a large synthetic matrix whose codes are drawn on the GPU (torch's seeded generator:
+    uniform indices over the ball and uniform gain bits, as make_matrix, but another stream). The matrix is
+    cut into `tiles` equal row tiles, each with its own seed, so any rank layout whose shards are whole tiles
+    sees the same matrix. Centroids, row scales and tails come from the host generator as in make_matrix."""
+    import torch
+    if d_out % tiles or lo % (d_out // tiles) or hi % (d_out // tiles):
+        raise ValueError(f"rows [{lo}, {hi}) of {d_out} are not whole tiles of {d_out // tiles}")
+    nb, tw, per = d_in // DIM, d_in % DIM, d_out // tiles
+    parts = []
+    for t in range(lo // per, hi // per):
+        gen = torch.Generator(device=device).manual_seed((seed * 0x9E3779B1 + t) & 0x7FFFFFFFFFFFFFFF)
+        idx = torch.randint(0, N12 + 1, (per * nb,), dtype=torch.int64, device=device, generator=gen)
+        gain = torch.randint(0, 2, (per * nb,), dtype=torch.int64, device=device, generator=gen)
+        v = (idx << 1) | gain
+        shifts = torch.tensor([40, 32, 24, 16, 8, 0], dtype=torch.int64, device=device)
+        parts.append(((v[:, None] >> shifts[None, :]) & 0xFF).to(torch.uint8).reshape(-1).cpu().numpy())
+    g = SplitMix64(seed)
+    cen = np.sort(0.5 + g.uniform(2)).astype(np.float32).astype(np.float64)
+    g.skip(2 * lo)
+    rs = np.abs(0.02 * g.gaussian(hi - lo))
+    g.skip(2 * (d_out - hi))
+    g.skip(2 * lo * tw)
+    tail = (0.02 * g.gaussian((hi - lo) * tw)).astype(np.float32).reshape(hi - lo, tw)
+    codes = np.concatenate(parts) if parts else np.zeros(0, np.uint8)
+    return SynthMatrix(f"{name}[{lo}:{hi}]", hi - lo, d_in, codes, cen, rs, tail)
 
 
 def make_matrix(d_out: int, d_in: int, seed: int, name: str = "w") -> SynthMatrix:

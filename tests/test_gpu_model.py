@@ -29,7 +29,7 @@ def _dense_model(rt, oracle, cfg, mats, fused, capacity, kv_int8):
     lin = torch.nn.functional.linear
     return FusedQwen3(cfg, blocks, fused.embed, fused.final_norm, capacity,
                       gemv=lambda w, x: lin(x.float(), w.float()).half(),
-                      gemm=lambda w, x: lin(x.float(), w.float()).half(), kv_int8=kv_int8)
+                      gemm=lambda w, x: lin(x.float(), w.float()).half(), head=fused.head, kv_int8=kv_int8)
 
 
 @pytest.mark.parametrize("kv_int8", [True, False])
@@ -104,3 +104,119 @@ def test_int8_kv_cache_matches_the_reference_scheme():
     assert ((y.float() - x.float()).abs() <= 0.51 * step + 2e-3).all()
     q2, s2, b2 = kv_quantize(y)  # a second round trip moves nothing by more than one step
     assert ((kv_dequantize(q2, s2, b2).float() - y.float()).abs() <= step + 2e-3).all()
+
+
+@pytest.mark.parametrize("hd,heads,kv", [(128, 8, 2), (64, 4, 4)])
+def test_split_kv_attention_matches_a_float_reference_at_long_contexts(rt, hd, heads, kv):
+    """The sliced attention equals softmax(q k^T / sqrt(d)) v over the dequantised cache for any slice
+    count, including slices that hold no position (attention semantics of llvq-llm/src/model.rs:500-560)."""
+    import torch
+    from llvq_b200._lib import check
+    from llvq_b200.model import kv_dequantize, kv_quantize
+    L = rt.lib
+    torch.manual_seed(3)
+    cap = 4100
+    k = (torch.randn(cap, kv, hd, device="cuda") * 1.5).half()
+    v = torch.randn(cap, kv, hd, device="cuda").half()
+    kq, ks, kb = kv_quantize(k)
+    vq, vs, vb = kv_quantize(v)
+    kd, vd = kv_dequantize(kq, ks, kb).float(), kv_dequantize(vq, vs, vb).float()
+    q = torch.randn(heads, hd, device="cuda").half()
+    p = lambda t: t.data_ptr()
+    st = torch.cuda.current_stream().cuda_stream
+    for last in (0, 5, 1023, 4099):
+        pos = torch.tensor(last, device="cuda", dtype=torch.int64)
+        rep = heads // kv
+        kk = kd[: last + 1].repeat_interleave(rep, dim=1)  # [t, heads, hd]
+        vv = vd[: last + 1].repeat_interleave(rep, dim=1)
+        w = torch.softmax(torch.einsum("hd,thd->ht", q.float(), kk) / hd ** 0.5, dim=1)
+        want = torch.einsum("ht,thd->hd", w, vv)
+        outs = []
+        for splits in (1, 3, 16, 64):
+            out = torch.zeros(heads, hd, device="cuda", dtype=torch.float16)
+            ws = torch.full((heads * splits * (hd + 2),), float("nan"), device="cuda")
+            check(L.llvq_op_attn_decode_int8_h(p(q), p(kq), p(ks), p(kb), p(vq), p(vs), p(vb), p(pos), p(out),
+                                               heads, kv, hd, splits, p(ws), st))
+            torch.cuda.synchronize()
+            assert ((out.float() - want).abs().max() <= 2e-3 + 2e-3 * want.abs().max()).item(), (last, splits)
+            outs.append(out)
+        for o in outs[1:]:
+            assert (o.float() - outs[0].float()).abs().max().item() <= 2e-3
+    bad = L.llvq_op_attn_decode_int8_h(p(q), p(kq), p(ks), p(kb), p(vq), p(vs), p(vb), p(pos), p(out), heads, kv, hd, 4, None, st)
+    assert bad != 0  # several slices need the scratch buffer
+
+
+def test_chunked_prefill_and_library_attention_keep_the_tokens(rt):
+    """A prompt cut into chunks (each attending to the cache so far), the dense-transient GEMM route and the
+    fused-attention route for large score matrices all continue with the tokens of the one-chunk run."""
+    import torch
+    from llvq_b200.model import Qwen3Config, synthetic_model
+    cfg = Qwen3Config(hidden=24 * 10 + 16, inter=24 * 20 + 8, n_heads=4, n_kv=2, head_dim=64, layers=2, vocab=512)
+    g = np.random.default_rng(8)
+    prompt = [int(t) for t in g.integers(0, cfg.vocab, 150)]
+    base, _ = synthetic_model(rt, cfg, config_id=2, capacity=192)
+    want = base.generate(prompt, 12)
+    chunked, _ = synthetic_model(rt, cfg, config_id=2, capacity=192)
+    chunked.prefill_chunk = 64
+    assert chunked.generate(prompt, 12) == want
+    dense, _ = synthetic_model(rt, cfg, config_id=2, capacity=192, dense_prefill_from=32)
+    hd = dense.prefill(prompt)
+    hb = base.prefill(prompt)
+    assert ((hd.float() - hb.float()).norm() / hb.float().norm()).item() < 1e-2
+    # the fused-attention route (taken when the score matrix would be large) against the explicit softmax
+    q = torch.randn(70, 4, 64, device="cuda").half()
+    k = torch.randn(150, 2, 64, device="cuda").half()
+    v = torch.randn(150, 2, 64, device="cuda").half()
+    pos = torch.arange(80, 150, device="cuda")
+    small = base._attend(q, k, v, pos, 150)
+    base.sdpa_from = 0
+    big = base._attend(q, k, v, pos, 150)
+    assert ((big.float() - small.float()).abs().max()).item() < 5e-3
+
+
+def _tp_gpu_worker(rank, world, port, q):
+    import os
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from llvq_b200 import FusedRuntime
+        from llvq_b200.model import Qwen3Config, TpGroup, synthetic_model
+        cfg = Qwen3Config(hidden=24 * 10 + 16, inter=24 * 20 + 16, n_heads=4, n_kv=2, head_dim=64, layers=2, vocab=512)
+        rt = FusedRuntime(rank)
+        g = np.random.default_rng(21)
+        prompt = [int(t) for t in g.integers(0, cfg.vocab, 40)]
+        whole, _ = synthetic_model(rt, cfg, config_id=4, capacity=96)
+        want = whole.generate(prompt, 20)
+        sharded, _ = synthetic_model(rt, cfg, config_id=4, capacity=96, tp=TpGroup())
+        got = sharded.generate(prompt, 20)
+        graphed = sharded.generate(prompt, 20, use_graph=True)
+        q.put((rank, want, got, graphed))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_model_on_two_gpus_picks_the_single_gpu_tokens():
+    """Head-sharded attention, row-sharded projections and the sharded greedy head over NCCL: the tokens of
+    the whole model on one GPU (needs two GPUs; NVLS off, nothing waits on a peer outside NCCL)."""
+    import os
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 33000 + os.getpid() % 2000
+    procs = [ctx.Process(target=_tp_gpu_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, want, tokens, graphed in got:
+        assert tokens == want and graphed == want, (rank, want, tokens, graphed)

@@ -306,3 +306,52 @@ def test_batched_gemm_equals_gemv_semantics(rt):
     assert torch.equal(yb[0], yb[15])
     y1 = rt.forward(proj, x1).float()
     assert ((yb[0].float() - y1).norm() / y1.norm()).item() < 2e-3
+
+
+@pytest.mark.parametrize("d_out,d_in", [(40, 24 * 7 + 5), (64, 24 * 16), (17, 30), (8, 12)])
+def test_dense_dequant_matches_the_oracle_matrix(rt, oracle, d_out, d_in):
+    """llvq_matrix_dequant_h writes f16(oracle weight): same lattice points, gain, row scale and tail."""
+    torch = _torch()
+    from llvq_b200 import synth
+    m = synth.make_matrix(d_out, d_in, 0xDE45E + d_out)
+    proj = rt.upload(m, tail_f16=True)
+    w = rt.dequant(proj).cpu().numpy().astype(np.float64)
+    tail16 = m.tail.astype(np.float16).astype(np.float32)
+    want = oracle.decode_matrix(m.codes, d_out, d_in, m.centroids, m.row_scales, tail16).astype(np.float64)
+    assert w.shape == want.shape
+    # one f16 rounding of a product formed in f32: 2^-11 relative plus f32 product noise
+    assert (np.abs(w - want) <= np.abs(want) * 6e-4 + 1e-7).all()
+    assert (w[want == 0] == 0).all()  # the zeros of the lattice points stay zeros
+    x = synth.make_activation(d_in, 0x99, np.float16, batch=1100 if d_out == 40 else 20)
+    y = rt.forward_batch_dense(proj, torch.from_numpy(x).cuda()).cpu().numpy()
+    ref = oracle.gemv_f64(m.codes, d_out, d_in, m.centroids, m.row_scales, tail16, x.astype(np.float64))
+    assert rel_l2(y, ref) <= TOL_F16
+    assert not rt.poll_range_error()
+
+
+def test_greedy_head_kernel_matches_a_float_argmax(rt):
+    """llvq_op_lm_head_argmax_h: f32 logits of an f16 embedding shard, lowest row on ties, row offset added."""
+    torch = _torch()
+    from llvq_b200.model import kernel_head
+    head = kernel_head(rt.lib)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    for rows, hidden in ((151936, 2560), (1000, 64), (7, 8), (18992, 5120)):
+        e = (0.02 * torch.randn(rows, hidden, device="cuda", generator=g)).half()
+        h = torch.randn(hidden, device="cuda", generator=g).half()
+        logits = e.float() @ h.float()
+        val, idx = head(e, h, 1000)
+        torch.cuda.synchronize()
+        assert int(idx) - 1000 == int(logits.argmax()), (rows, hidden)
+        assert abs(float(val) - float(logits.max())) <= 1e-4 * max(1.0, abs(float(logits.max())))
+        # a shard of the rows reports the same logit for the same row (nothing depends on the split)
+        lo = rows // 3
+        v2, i2 = head(e[lo:], h, lo)
+        if int(logits.argmax()) >= lo:
+            assert int(i2) == int(logits.argmax()) and float(v2) == float(val)
+    e = torch.zeros(64, 16, device="cuda", dtype=torch.float16)
+    e[5] = 1.0
+    e[9] = 1.0
+    _, idx = head(e, torch.ones(16, device="cuda", dtype=torch.float16), 0)
+    assert int(idx) == 5
+    with pytest.raises(Exception):
+        head(torch.zeros(4, 12, device="cuda", dtype=torch.float16), torch.zeros(12, device="cuda", dtype=torch.float16), 0)
