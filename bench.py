@@ -21,6 +21,7 @@ CPU path alone, as the reference arm.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -234,7 +235,8 @@ def run_tp_decode(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # a rank that dies must end its peers' next collective with an error, not leave them waiting
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=300))
     rt = FusedRuntime(local_rank)
     cfg = Qwen3Config.named("qwen3-14b")
     layers = args.layers if args.layers != 36 else cfg.layers
@@ -256,8 +258,9 @@ def run_tp_decode(args):
     e[1].record()
     torch.cuda.synchronize()
     model.start_decode(nxt, prompt_len)
+    step = model._eager_step if args.no_graph else model._graph_step
     for _ in range(max(args.warmup, 3)):  # the first call captures the graph; the position moves on, as in a real run
-        model._graph_step()
+        step()
     model.start_decode(nxt, prompt_len)
     torch.cuda.synchronize()
     if world > 1:
@@ -269,7 +272,7 @@ def run_tp_decode(args):
     e[2].record()
     t1 = time.perf_counter()
     while len(out) < new_tokens:
-        model._graph_step()
+        step()
         out.append(int(model._tok))  # the per-token read-back of the reference's loop
     e[3].record()
     torch.cuda.synchronize()
@@ -296,15 +299,19 @@ def run_tp_decode(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "qwen3-14b-tp-greedy-decode", "layers": layers, "prompt_tokens": prompt_len,
                        "new_tokens": new_tokens, "parallelism": f"tp{world}", "kv_cache": "int8 g64, split-KV attention",
-                       "attn_splits": model.attn_splits, "graph": True,
+                       "attn_splits": model.attn_splits, "graph": not args.no_graph,
                        "collective": "nccl all_gather_into_tensor x4 per layer + 1 per token" if world > 1 else "none"},
             "wall_tok_per_s": gen / (wall_ms * 1e-3), "prefill_ms": prefill_ms,
             "prefill_tok_per_s": prompt_len / (prefill_ms * 1e-3), "setup_s": setup, "ranks_agree": ranks_agree,
             "distinct_tokens": len(set(out)), "token_checksum": int(sum((i + 1) * t for i, t in enumerate(out)) % (1 << 31)),
             "kv_bytes_read_per_token": kv_bytes, "clocks": clocks}))
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        # Every collective of this rank has completed (the reductions above were read on the host). Tearing the
+        # process group down while a captured graph still holds its collectives did not return on this stack,
+        # so the ranks leave without it: nothing is in flight and nothing waits on a peer.
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 def run_tp(args):
@@ -319,7 +326,8 @@ def run_tp(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # a rank that dies must end its peers' next collective with an error, not leave them waiting
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=300))
     rt = FusedRuntime(local_rank)
     shapes = synth.layer_shapes("qwen3-14b")
     layers = args.layers if args.layers != 36 else 40
@@ -393,6 +401,7 @@ def main():
                     help="tensor-parallel mode: Qwen3-14B projections row-sharded over the ranks with all-gathers")
     ap.add_argument("--tp-decode", action="store_true",
                     help="config 4: Qwen3-14B tensor-parallel greedy decode over the ranks (prompt --prompt, --new-tokens)")
+    ap.add_argument("--no-graph", action="store_true", help="--tp-decode: launch every token step eagerly")
     ap.add_argument("--prompt", type=int, default=32768)
     ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--gpus", type=int, default=1)
@@ -424,7 +433,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the measured path")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # a rank that dies must end its peers' next collective with an error, not leave them waiting
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=300))
     rt = FusedRuntime(local_rank)
     lib = _lib.load()
 

@@ -293,6 +293,38 @@ int gemv_host(llvq_matrix* m, const XT* xh, YT* yh, llvq_stream_t stream) {
 
 }  // namespace
 
+template <int HD, int G>
+static int launch_attn(const __half* q, const KvCacheView& kc, const KvCacheView& vc, const long long* pos, __half* out,
+                       float* scratch, int n_kv, int splits, cudaStream_t s) {
+    static bool configured = false;  // per instantiation
+    const int smem = (int)sizeof(AttnSmem<HD, G>);
+    if (!configured) {
+        CUDA_TRY(cudaFuncSetAttribute(attn_splitkv_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured = true;
+    }
+    attn_splitkv_kernel<HD, G><<<dim3(n_kv, splits), kAttnThreads, smem, s>>>(q, kc, vc, pos, out, scratch, n_kv);
+    if (splits > 1) attn_combine_kernel<HD><<<n_kv * G, HD, splits * sizeof(float), s>>>(scratch, out, splits);
+    g_launches += splits > 1 ? 2 : 1;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+template <int HD>
+static int launch_attn_g(int G, const __half* q, const KvCacheView& kc, const KvCacheView& vc, const long long* pos,
+                         __half* out, float* scratch, int n_kv, int splits, cudaStream_t s) {
+    switch (G) {
+        case 1: return launch_attn<HD, 1>(q, kc, vc, pos, out, scratch, n_kv, splits, s);
+        case 2: return launch_attn<HD, 2>(q, kc, vc, pos, out, scratch, n_kv, splits, s);
+        case 3: return launch_attn<HD, 3>(q, kc, vc, pos, out, scratch, n_kv, splits, s);
+        case 4: return launch_attn<HD, 4>(q, kc, vc, pos, out, scratch, n_kv, splits, s);
+        case 5: return launch_attn<HD, 5>(q, kc, vc, pos, out, scratch, n_kv, splits, s);
+        case 6: return launch_attn<HD, 6>(q, kc, vc, pos, out, scratch, n_kv, splits, s);
+        case 7: return launch_attn<HD, 7>(q, kc, vc, pos, out, scratch, n_kv, splits, s);
+        case 8: return launch_attn<HD, 8>(q, kc, vc, pos, out, scratch, n_kv, splits, s);
+    }
+    return fail(LLVQ_ERR_UNSUPPORTED, "op_attn_decode: %d query heads per KV head (1 to %d)", G, kAttnMaxG);
+}
+
 extern "C" {
 
 const char* llvq_last_error(void) { return g_error.c_str(); }
@@ -596,23 +628,16 @@ int llvq_op_attn_decode_int8_h(const uint16_t* q, const uint8_t* kq, const uint1
                                llvq_stream_t stream) {
     if (!q || !kq || !ks || !kb || !vq || !vs || !vb || !pos || !out) return fail(LLVQ_ERR_INVALID, "op_attn_decode: null argument");
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv) return fail(LLVQ_ERR_INVALID, "op_attn_decode: %d heads over %d", n_heads, n_kv);
-    if (splits < 1 || splits > 1024 || (splits > 1 && !scratch))
+    if (splits < 1 || splits > 4096 || (splits > 1 && !scratch))
         return fail(LLVQ_ERR_INVALID, "op_attn_decode: %d splits need a scratch buffer", splits);
+    if (((uintptr_t)kq & 15u) || ((uintptr_t)vq & 15u)) return fail(LLVQ_ERR_INVALID, "op_attn_decode: cache codes must be 16-byte aligned");
     const KvCacheView kc{(unsigned char*)kq, (__half*)ks, (__half*)kb}, vc{(unsigned char*)vq, (__half*)vs, (__half*)vb};
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(n_heads, splits);
-    if (head_dim == 128) {
-        attn_decode_kernel<128><<<grid, 128, 0, s>>>((const __half*)q, kc, vc, (const long long*)pos, (__half*)out, scratch, n_heads, n_kv);
-        if (splits > 1) attn_combine_kernel<128><<<n_heads, 128, 0, s>>>(scratch, (__half*)out, splits);
-    } else if (head_dim == 64) {
-        attn_decode_kernel<64><<<grid, 128, 0, s>>>((const __half*)q, kc, vc, (const long long*)pos, (__half*)out, scratch, n_heads, n_kv);
-        if (splits > 1) attn_combine_kernel<64><<<n_heads, 64, 0, s>>>(scratch, (__half*)out, splits);
-    } else {
-        return fail(LLVQ_ERR_UNSUPPORTED, "op_attn_decode: head_dim %d (64 or 128)", head_dim);
-    }
-    g_launches += splits > 1 ? 2 : 1;
-    CUDA_TRY(cudaGetLastError());
-    return LLVQ_OK;
+    if (head_dim == 128)
+        return launch_attn_g<128>(n_heads / n_kv, (const __half*)q, kc, vc, (const long long*)pos, (__half*)out, scratch, n_kv, splits, s);
+    if (head_dim == 64)
+        return launch_attn_g<64>(n_heads / n_kv, (const __half*)q, kc, vc, (const long long*)pos, (__half*)out, scratch, n_kv, splits, s);
+    return fail(LLVQ_ERR_UNSUPPORTED, "op_attn_decode: head_dim %d (64 or 128)", head_dim);
 }
 
 int llvq_op_silu_mul_h(const uint16_t* gu, uint16_t* y, int32_t inter, llvq_stream_t stream) {

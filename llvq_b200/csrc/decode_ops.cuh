@@ -7,13 +7,15 @@
 //   add_rmsnorm_kernel     x += delta (optional); y = x / rms(x) * w
 //   qkv_rope_cache_kernel  per head: q/k RMSNorm over head_dim, RoPE (rotate-half) at the
 //                          position read from device memory, q out; k and v quantised into the cache
-//   attn_decode_kernel     split-KV attention: CTA (head, slice) runs an online softmax over its slice of
-//   attn_combine_kernel    positions 0..pos with keys/values dequantised on the fly; slices merged after
+//   attn_splitkv_kernel    (attn_splitkv.cuh) split-KV attention over the int8 cache, one CTA per
+//   attn_combine_kernel    (KV head, slice of positions) serving all query heads of the group
 //   silu_mul_kernel        y = silu(gate) * up
 //
 // The position is always read from device memory so that a captured CUDA graph replays unchanged.
 #pragma once
 #include <cuda_fp16.h>
+
+#include "attn_splitkv.cuh"
 
 namespace llvq {
 
@@ -75,11 +77,6 @@ add_rmsnorm_kernel(__half* __restrict__ x, const __half* __restrict__ delta, con
     }
 }
 
-struct KvCacheView {
-    unsigned char* q;  // [capacity, n_kv, head_dim]
-    __half* s;         // [capacity, n_kv, head_dim / 64]
-    __half* b;
-};
 
 // Quantise the head_dim values of one head held by a warp (V values per lane, dims lane + 32 j) into
 // groups of 64: group g covers j in {2g, 2g + 1}. u8 affine, scale = range / 255 through f16, bias = min
@@ -146,110 +143,6 @@ __global__ void qkv_rope_cache_kernel(const __half* __restrict__ qkv, const __ha
     KvCacheView c = is_k ? kc : vc;
     const size_t slot = (size_t)pos * n_kv + kvh;
     quantize_head<V>(v, c.q + slot * HD, c.s + slot * (HD / 64), c.b + slot * (HD / 64), lane);
-}
-
-// Split-KV attention for one decoded token. grid = (n_heads, splits): CTA (h, s) covers the s-th
-// equal slice of positions 0..pos with 4 warps (warp w takes every 4th position of the slice), an online
-// softmax per warp merged through shared memory. With one split the result goes straight to `out`;
-// otherwise the CTA stores its (max, sum, unnormalised accumulator) into `partial` and
-// attn_combine_kernel merges the slices. Keys and values are dequantised on the fly.
-template <int HD>
-__global__ void attn_decode_kernel(const __half* __restrict__ q, KvCacheView kc, KvCacheView vc,
-                                   const long long* __restrict__ pos_ptr, __half* __restrict__ out,
-                                   float* __restrict__ partial, int n_heads, int n_kv) {
-    constexpr int V = HD / 32;
-    constexpr int kW = 4;
-    __shared__ float sm_m[kW], sm_l[kW], sm_acc[kW][HD];
-    const int head = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int splits = gridDim.y, split = blockIdx.y;
-    const int kvh = head / (n_heads / n_kv);
-    const int n_pos = (int)(*pos_ptr) + 1;
-    const int slice = (n_pos + splits - 1) / splits;
-    const int t0 = split * slice, t1 = min(n_pos, t0 + slice);
-    const float scale = rsqrtf((float)HD);
-    float qv[V], acc[V];
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-        qv[j] = __half2float(q[(size_t)head * HD + lane + 32 * j]) * scale;
-        acc[j] = 0.0f;
-    }
-    float m = -INFINITY, l = 0.0f;
-    for (int t = t0 + warp; t < t1; t += kW) {
-        const size_t slot = (size_t)t * n_kv + kvh;
-        const unsigned char* kq = kc.q + slot * HD;
-        float dot = 0.0f;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-            const int g = j / 2;  // dims lane + 32 j: group of 64
-            const float kval = __half2float(__float2half_rn(
-                (float)kq[lane + 32 * j] * __half2float(kc.s[slot * (HD / 64) + g]) + __half2float(kc.b[slot * (HD / 64) + g])));
-            dot += qv[j] * kval;
-        }
-        dot = warp_sum_f(dot);
-        const float m_new = fmaxf(m, dot);
-        const float corr = __expf(m - m_new), p = __expf(dot - m_new);
-        l = l * corr + p;
-        const unsigned char* vq = vc.q + slot * HD;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-            const int g = j / 2;
-            const float vval = __half2float(__float2half_rn(
-                (float)vq[lane + 32 * j] * __half2float(vc.s[slot * (HD / 64) + g]) + __half2float(vc.b[slot * (HD / 64) + g])));
-            acc[j] = acc[j] * corr + p * vval;
-        }
-        m = m_new;
-    }
-    if (lane == 0) {
-        sm_m[warp] = m;
-        sm_l[warp] = l;
-    }
-#pragma unroll
-    for (int j = 0; j < V; ++j) sm_acc[warp][lane + 32 * j] = acc[j];
-    __syncthreads();
-    if (warp == 0) {
-        float mm = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kW; ++w) mm = fmaxf(mm, sm_m[w]);
-        float ll = 0.0f, o[V];
-#pragma unroll
-        for (int j = 0; j < V; ++j) o[j] = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kW; ++w) {
-            const float f = sm_m[w] == -INFINITY ? 0.0f : __expf(sm_m[w] - mm);
-            ll += sm_l[w] * f;
-#pragma unroll
-            for (int j = 0; j < V; ++j) o[j] += sm_acc[w][lane + 32 * j] * f;
-        }
-        if (splits == 1) {
-#pragma unroll
-            for (int j = 0; j < V; ++j) out[(size_t)head * HD + lane + 32 * j] = __float2half_rn(o[j] / ll);
-        } else {
-            float* dst = partial + ((size_t)head * splits + split) * (HD + 2);
-            if (lane == 0) {
-                dst[0] = mm;  // -inf for an empty slice
-                dst[1] = ll;
-            }
-#pragma unroll
-            for (int j = 0; j < V; ++j) dst[2 + lane + 32 * j] = o[j];
-        }
-    }
-}
-
-// grid = n_heads, HD threads: merge the slices of attn_decode_kernel in slice order.
-template <int HD>
-__global__ void attn_combine_kernel(const float* __restrict__ partial, __half* __restrict__ out, int splits) {
-    const int head = blockIdx.x, d = threadIdx.x;
-    const float* src = partial + (size_t)head * splits * (HD + 2);
-    float mm = -INFINITY;
-    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src[(size_t)s * (HD + 2)]);
-    float ll = 0.0f, o = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = src[(size_t)s * (HD + 2)];
-        const float f = ms == -INFINITY ? 0.0f : __expf(ms - mm);
-        ll += src[(size_t)s * (HD + 2) + 1] * f;
-        o += src[(size_t)s * (HD + 2) + 2 + d] * f;
-    }
-    out[(size_t)head * HD + d] = __float2half_rn(o / ll);
 }
 
 __global__ void silu_mul_kernel(const __half* __restrict__ gu, __half* __restrict__ y, int inter) {

@@ -177,8 +177,10 @@ class FusedQwen3:
             self._o_loc = torch.zeros(cfg.hidden // w, **f16) if w > 1 else self._o
             self._down_loc = torch.zeros(cfg.hidden // w, **f16) if w > 1 else self._down
             self._act_loc = torch.zeros(self.inter_loc, **f16) if w > 1 else self._act
-            # split-KV attention: one slice per ~256 cached positions, enough CTAs to fill the GPU at long contexts
-            self.attn_splits = max(1, min(64, capacity // 256))
+            # split-KV attention: a CTA serves one KV head over one slice of the positions with 8 warps of 32
+            # positions each, so slices go down to 256 positions until there are two CTAs per SM
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            self.attn_splits = max(1, min(-(-capacity // 256), (2 * sms) // self.kv_loc))
             self._attn_ws = torch.zeros(self.h_loc * self.attn_splits * (hd + 2), dtype=torch.float32, device=dev)
         # the token and its position live in fixed device tensors: a captured graph keeps their addresses
         self._tok = torch.zeros(1, dtype=torch.long, device=dev)
