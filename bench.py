@@ -243,7 +243,8 @@ def run_tp_decode(args):
     prompt_len, new_tokens = args.prompt, args.new_tokens
     t0 = time.perf_counter()
     model, _ = synthetic_model(rt, cfg, config_id=4, capacity=prompt_len + new_tokens, layers=layers,
-                               tp=TpGroup() if world > 1 else None, keep_host=False, device_codes=True)
+                               tp=TpGroup(peer_lib=rt.lib if args.gather == "peer" else None) if world > 1 else None,
+                               keep_host=False, device_codes=True)
     torch.cuda.synchronize()
     setup = time.perf_counter() - t0
     rng = np.random.default_rng(0x4C0DE)
@@ -300,9 +301,11 @@ def run_tp_decode(args):
             "config": {"workload": "qwen3-14b-tp-greedy-decode", "layers": layers, "prompt_tokens": prompt_len,
                        "new_tokens": new_tokens, "parallelism": f"tp{world}", "kv_cache": "int8 g64, split-KV attention",
                        "attn_splits": model.attn_splits, "graph": not args.no_graph,
-                       "collective": "nccl all_gather_into_tensor x4 per layer + 1 per token" if world > 1 else "none"},
+                       "collective": ("none" if world == 1 else "peer-memory exchange kernel (stores + flags) x4 per layer + 1 per token"
+                                      if args.gather == "peer" else "nccl all_gather_into_tensor x4 per layer + 1 per token")},
             "wall_tok_per_s": gen / (wall_ms * 1e-3), "prefill_ms": prefill_ms,
             "prefill_tok_per_s": prompt_len / (prefill_ms * 1e-3), "setup_s": setup, "ranks_agree": ranks_agree,
+            "peer_errors": model.tp.peer.poll_error() if model.tp and model.tp.peer else None,
             "distinct_tokens": len(set(out)), "token_checksum": int(sum((i + 1) * t for i, t in enumerate(out)) % (1 << 31)),
             "kv_bytes_read_per_token": kv_bytes, "clocks": clocks}))
     if world > 1:
@@ -401,6 +404,8 @@ def main():
                     help="tensor-parallel mode: Qwen3-14B projections row-sharded over the ranks with all-gathers")
     ap.add_argument("--tp-decode", action="store_true",
                     help="config 4: Qwen3-14B tensor-parallel greedy decode over the ranks (prompt --prompt, --new-tokens)")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="--tp-decode: token-step all-gathers through peer memory (llvq_tp_exchange) or NCCL")
     ap.add_argument("--no-graph", action="store_true", help="--tp-decode: launch every token step eagerly")
     ap.add_argument("--prompt", type=int, default=32768)
     ap.add_argument("--new-tokens", type=int, default=128)

@@ -123,6 +123,15 @@ int llvq_matrix_upload_group(llvq_runtime* rt, const llvq_matrix_desc* descs, in
 void llvq_matrix_free(llvq_matrix* m);
 int llvq_matrix_dims(const llvq_matrix* m, int32_t* d_out, int32_t* d_in);
 
+/* Column split of the batch-1 GEMV: `splits` CTAs share every 8-row tile, each decoding its own range
+ * of column blocks; partial row sums are added in split order, so the result does not depend on
+ * scheduling (it does depend on the split count, in the last bits of the f32 sum). The upload takes
+ * the fewest splits the 128-block chunk allows (ceil(nblocks / 128)); more splits spread a matrix
+ * with few rows over more SMs. 0 restores the default. Tuning knob with no counterpart in the
+ * reference. Synchronises the device and reallocates the workspace: not for use inside a capture. */
+int llvq_matrix_set_splits(llvq_matrix* m, int32_t splits);
+int llvq_matrix_get_splits(const llvq_matrix* m, int32_t* splits);
+
 /* Bytes one GEMV must move at minimum: codes + tail + row scales (as stored in
  * the archive: f64) + x + y. Used by the benchmark's roofline. */
 int llvq_matrix_algorithmic_bytes(const llvq_matrix* m, int32_t x_elem_bytes, int32_t y_elem_bytes, uint64_t* out);
@@ -234,6 +243,39 @@ int llvq_op_lm_head_argmax_h(const uint16_t* embed_dev, const uint16_t* h_dev, i
  * reference's dense-decoded run keeps resident (llvq-llm/src/bin/fusedrun.rs:263-278), here a
  * transient operand for long-prompt GEMMs. An index outside the ball raises the runtime's range flag. */
 int llvq_matrix_dequant_h(llvq_matrix* m, uint16_t* out_dev, llvq_stream_t stream);
+
+/* ---- peer-memory all-gather of row shards (tensor-parallel token step) -------
+ * No counterpart in the reference, which is single-GPU. A rank owns one region =
+ * LLVQ_TP_FLAG_BYTES of flags followed by its gather buffers, maps the regions of its peers
+ * through CUDA IPC, and llvq_tp_exchange copies its shard into every rank's buffer with peer
+ * stores, releases a flag on each peer and waits (bounded) for the peers' flags in its own
+ * region. All ranks must issue the same sequence of exchanges. */
+#define LLVQ_TP_FLAG_BYTES 512
+#define LLVQ_TP_HANDLE_BYTES 64
+#define LLVQ_TP_ERR_PEER_TIMEOUT 4 /* bit of the error word: a peer's flag did not arrive in time */
+typedef struct llvq_tp_ctx llvq_tp_ctx;
+
+/* cudaMalloc + zero a region of LLVQ_TP_FLAG_BYTES + data_bytes; ipc_handle_out: LLVQ_TP_HANDLE_BYTES
+ * to hand to the peers (any transport). */
+int llvq_tp_region_create(int32_t device, size_t data_bytes, void** region_out, uint8_t* ipc_handle_out);
+int llvq_tp_region_open(int32_t device, const uint8_t* ipc_handle, void** region_out); /* a peer's region */
+int llvq_tp_region_close(int32_t device, void* peer_region);
+int llvq_tp_region_free(int32_t device, void* own_region);
+/* regions[p]: the region of rank p as mapped in this process (own region at index rank).
+ * spin_limit: polls before a wait gives up (0 = default, about a second). */
+int llvq_tp_ctx_create(int32_t device, int32_t rank, int32_t world, void* const* regions, uint32_t spin_limit,
+                       llvq_tp_ctx** out);
+void llvq_tp_ctx_destroy(llvq_tp_ctx* ctx);
+/* Gather: afterwards the buffer at region + buf_offset holds world shards of shard_bytes in rank
+ * order. site (0..15) names the flag row; reuse a site only for exchanges at least two apart. */
+int llvq_tp_exchange(llvq_tp_ctx* ctx, int32_t site, size_t buf_offset, const void* src_dev, uint32_t shard_bytes,
+                     llvq_stream_t stream);
+/* The same exchange for n ranks whose regions all live on one GPU, as ONE cooperative launch
+ * (ranks that wait on one another must not be separate launches on one GPU). For tests. */
+int llvq_tp_exchange_emulated(llvq_tp_ctx* const* ctxs, int32_t n, int32_t site, size_t buf_offset,
+                              const void* const* srcs_dev, uint32_t shard_bytes, llvq_stream_t stream);
+/* Read and clear the error word (synchronises the device). */
+int llvq_tp_poll_error(llvq_tp_ctx* ctx, int32_t* out);
 
 /* ---- decode probes --------------------------------------------------------- */
 

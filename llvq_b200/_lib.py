@@ -56,6 +56,18 @@ _SIGNATURES = {
     "llvq_gemv_h_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "llvq_op_add_rmsnorm_h": (C.c_int, [C.c_void_p] * 4 + [C.c_int32, C.c_float, C.c_void_p]),
     "llvq_op_qkv_rope_cache_h": (C.c_int, [C.c_void_p] * 13 + [C.c_int32] * 3 + [C.c_float, C.c_void_p]),
+    "llvq_matrix_set_splits": (C.c_int, [C.c_void_p, C.c_int32]),
+    "llvq_matrix_get_splits": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
+    "llvq_tp_region_create": (C.c_int, [C.c_int32, C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),
+    "llvq_tp_region_open": (C.c_int, [C.c_int32, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "llvq_tp_region_close": (C.c_int, [C.c_int32, C.c_void_p]),
+    "llvq_tp_region_free": (C.c_int, [C.c_int32, C.c_void_p]),
+    "llvq_tp_ctx_create": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_void_p), C.c_uint32, C.POINTER(C.c_void_p)]),
+    "llvq_tp_ctx_destroy": (None, [C.c_void_p]),
+    "llvq_tp_exchange": (C.c_int, [C.c_void_p, C.c_int32, C.c_size_t, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "llvq_tp_exchange_emulated": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_size_t, C.POINTER(C.c_void_p),
+                                            C.c_uint32, C.c_void_p]),
+    "llvq_tp_poll_error": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
     "llvq_op_lm_head_argmax_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p,
                                           C.c_void_p, C.c_void_p]),
     "llvq_matrix_dequant_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -16,6 +16,7 @@
 #include "codebook.h"
 #include "decode_ops.cuh"
 #include "dense_ops.cuh"
+#include "tp_exchange.cuh"
 #include "gemm_tc.cuh"
 #include "gemv_sorted.cuh"
 #include "kernels_generic.cuh"
@@ -78,6 +79,7 @@ struct llvq_runtime {
     uint64_t fingerprint = 0;
     int max_smem_optin = 0;
     int sm_count = 0;
+    int gemv_ctas_per_sm = 5;      // resident CTAs of the GEMV kernel per SM (its launch bounds)
     // split-K partials of the batched GEMM; grown on demand, shared by all matrices of the runtime
     float* gemm_ws = nullptr;
     size_t gemm_ws_bytes = 0;
@@ -195,6 +197,30 @@ void free_matrix_buffers(llvq_matrix* m) {
     cudaFree(m->split_counter);
 }
 
+// Column split of a matrix: `splits` CTAs share a row tile, each owning split_range column blocks.
+// At least ceil(nb / 128) (a CTA stages one 128-block chunk of the activation at a time and a split
+// never loops over more than its range); more splits spread a matrix with few rows over more SMs.
+// Frees and reallocates the partial-sum workspace: not while a launch on the matrix is in flight.
+int set_splits(llvq_matrix* m, int splits) {
+    const int min_splits = m->nb > kChunk ? (m->nb + kChunk - 1) / kChunk : 1;
+    if (splits < min_splits) splits = min_splits;
+    if (m->nb > 0 && splits > m->nb) splits = m->nb;
+    if (m->nb == 0) splits = 1;
+    cudaFree(m->split_ws);
+    cudaFree(m->split_counter);
+    m->split_ws = nullptr;
+    m->split_counter = nullptr;
+    m->split_range = m->nb > 0 ? (m->nb + splits - 1) / splits : 1;
+    m->splits = m->nb > 0 ? (m->nb + m->split_range - 1) / m->split_range : 1;  // no empty trailing split
+    if (m->splits > 1) {
+        const size_t tiles = ((size_t)m->d_out + 7) / 8;
+        CUDA_TRY(cudaMalloc((void**)&m->split_ws, (size_t)m->splits * m->d_out * sizeof(float)));
+        CUDA_TRY(cudaMalloc((void**)&m->split_counter, tiles * sizeof(int)));
+        CUDA_TRY(cudaMemset(m->split_counter, 0, tiles * sizeof(int)));
+    }
+    return LLVQ_OK;
+}
+
 int upload_impl(llvq_runtime* rt, const llvq_matrix_desc* descs, int n, llvq_matrix** out) {
     if (!rt || !descs || !out || n <= 0) return fail(LLVQ_ERR_INVALID, "upload: null argument");
     long long d_out = 0;
@@ -262,14 +288,9 @@ int upload_impl(llvq_runtime* rt, const llvq_matrix_desc* descs, int n, llvq_mat
     } else {
         UP_TRY(cudaMalloc(&m->tail, 16));  // never read; keeps the pointer valid
     }
-    // one chunk of at most 128 column blocks per CTA, the row cut into equal parts
-    m->splits = m->nb > kChunk ? (m->nb + kChunk - 1) / kChunk : 1;
-    m->split_range = m->nb > 0 ? (m->nb + m->splits - 1) / m->splits : 1;
-    if (m->splits > 1) {
-        const size_t tiles = ((size_t)m->d_out + 7) / 8;
-        UP_TRY(cudaMalloc((void**)&m->split_ws, (size_t)m->splits * m->d_out * sizeof(float)));
-        UP_TRY(cudaMalloc((void**)&m->split_counter, tiles * sizeof(int)));
-        UP_TRY(cudaMemset(m->split_counter, 0, tiles * sizeof(int)));
+    {
+        int st = set_splits(m.get(), 0);  // the fewest splits the chunk size allows
+        if (st) return bail(st);
     }
     UP_TRY(cudaMalloc(&m->x_stage, (size_t)m->d_in * sizeof(float) + 16));
     UP_TRY(cudaMalloc(&m->y_stage, (size_t)m->d_out * sizeof(float) + 16));
@@ -292,6 +313,11 @@ int gemv_host(llvq_matrix* m, const XT* xh, YT* yh, llvq_stream_t stream) {
 }
 
 }  // namespace
+
+struct llvq_tp_ctx {
+    int device = 0;
+    TpRank r{};
+};
 
 template <int HD, int G>
 static int launch_attn(const __half* q, const KvCacheView& kc, const KvCacheView& vc, const long long* pos, __half* out,
@@ -502,6 +528,19 @@ void llvq_matrix_free(llvq_matrix* m) {
     delete m;
 }
 
+int llvq_matrix_set_splits(llvq_matrix* m, int32_t splits) {
+    if (!m || splits < 0) return fail(LLVQ_ERR_INVALID, "matrix_set_splits: bad argument");
+    DeviceGuard g(m->rt->device);
+    CUDA_TRY(cudaDeviceSynchronize());
+    return set_splits(m, splits);
+}
+
+int llvq_matrix_get_splits(const llvq_matrix* m, int32_t* splits) {
+    if (!m || !splits) return fail(LLVQ_ERR_INVALID, "matrix_get_splits: null argument");
+    *splits = m->splits;
+    return LLVQ_OK;
+}
+
 int llvq_matrix_dims(const llvq_matrix* m, int32_t* d_out, int32_t* d_in) {
     if (!m) return fail(LLVQ_ERR_INVALID, "matrix_dims: null matrix");
     if (d_out) *d_out = m->d_out;
@@ -679,6 +718,138 @@ int llvq_matrix_dequant_h(llvq_matrix* m, uint16_t* out, llvq_stream_t stream) {
     dequant_dense_kernel<<<(unsigned int)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(rt->F, rt->T, mv, (__half*)out, rt->d_err);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+// ---- peer-memory all-gather of row shards (tensor-parallel token step) ----------------
+
+int llvq_tp_region_create(int32_t device, size_t data_bytes, void** region, uint8_t* ipc_handle) {
+    if (!region || !ipc_handle) return fail(LLVQ_ERR_INVALID, "tp_region_create: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == LLVQ_TP_HANDLE_BYTES, "IPC handle size");
+    static_assert(kTpFlagBytes == LLVQ_TP_FLAG_BYTES, "flag area size");
+    DeviceGuard g(device);
+    void* p = nullptr;
+    const size_t bytes = (size_t)kTpFlagBytes + data_bytes;
+    CUDA_TRY(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return fail(LLVQ_ERR_CUDA, "tp_region_create: %s", cudaGetErrorString(e));
+    }
+    std::memcpy(ipc_handle, &h, sizeof(h));
+    *region = p;
+    return LLVQ_OK;
+}
+
+int llvq_tp_region_open(int32_t device, const uint8_t* ipc_handle, void** region) {
+    if (!region || !ipc_handle) return fail(LLVQ_ERR_INVALID, "tp_region_open: null argument");
+    DeviceGuard g(device);
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, ipc_handle, sizeof(h));
+    CUDA_TRY(cudaIpcOpenMemHandle(region, h, cudaIpcMemLazyEnablePeerAccess));
+    return LLVQ_OK;
+}
+
+int llvq_tp_region_close(int32_t device, void* region) {
+    if (!region) return LLVQ_OK;
+    DeviceGuard g(device);
+    CUDA_TRY(cudaIpcCloseMemHandle(region));
+    return LLVQ_OK;
+}
+
+int llvq_tp_region_free(int32_t device, void* region) {
+    if (!region) return LLVQ_OK;
+    DeviceGuard g(device);
+    CUDA_TRY(cudaFree(region));
+    return LLVQ_OK;
+}
+
+int llvq_tp_ctx_create(int32_t device, int32_t rank, int32_t world, void* const* regions, uint32_t spin_limit,
+                       llvq_tp_ctx** out) {
+    if (!regions || !out) return fail(LLVQ_ERR_INVALID, "tp_ctx_create: null argument");
+    if (world < 1 || world > kTpMaxWorld || rank < 0 || rank >= world)
+        return fail(LLVQ_ERR_INVALID, "tp_ctx_create: rank %d of %d (at most %d ranks)", rank, world, kTpMaxWorld);
+    for (int p = 0; p < world; ++p)
+        if (!regions[p]) return fail(LLVQ_ERR_INVALID, "tp_ctx_create: region of rank %d is null", p);
+    DeviceGuard g(device);
+    std::unique_ptr<llvq_tp_ctx> c(new llvq_tp_ctx);
+    c->device = device;
+    c->r.rank = rank;
+    c->r.world = world;
+    c->r.spin_limit = spin_limit ? spin_limit : 4000000u;  // about a second of polling
+    for (int p = 0; p < world; ++p) c->r.region[p] = (unsigned char*)regions[p];
+    unsigned int* words = nullptr;
+    CUDA_TRY(cudaMalloc((void**)&words, 2 * sizeof(unsigned int)));
+    cudaError_t e = cudaMemset(words, 0, 2 * sizeof(unsigned int));
+    if (e != cudaSuccess) {
+        cudaFree(words);
+        return fail(LLVQ_ERR_CUDA, "tp_ctx_create: %s", cudaGetErrorString(e));
+    }
+    c->r.seq = words;
+    c->r.err = (int*)(words + 1);
+    *out = c.release();
+    return LLVQ_OK;
+}
+
+void llvq_tp_ctx_destroy(llvq_tp_ctx* c) {
+    if (!c) return;
+    DeviceGuard g(c->device);
+    cudaFree(c->r.seq);
+    delete c;
+}
+
+static int tp_fill_call(TpCall& call, const llvq_tp_ctx* c, int32_t site, size_t buf_offset, const void* src, uint32_t shard_bytes) {
+    if (!c || !src) return fail(LLVQ_ERR_INVALID, "tp_exchange: null argument");
+    if (site < 0 || site >= kTpMaxSites) return fail(LLVQ_ERR_INVALID, "tp_exchange: site %d (0..%d)", site, kTpMaxSites - 1);
+    if (buf_offset < (size_t)kTpFlagBytes || buf_offset > 0xffffffffull)
+        return fail(LLVQ_ERR_INVALID, "tp_exchange: buffer offset %zu lies inside the flag area or beyond 4 GiB", buf_offset);
+    call.r = c->r;
+    call.src = (const unsigned char*)src;
+    call.shard_bytes = shard_bytes;
+    call.buf_offset = (unsigned int)buf_offset;
+    call.site = site;
+    return LLVQ_OK;
+}
+
+int llvq_tp_exchange(llvq_tp_ctx* c, int32_t site, size_t buf_offset, const void* src, uint32_t shard_bytes,
+                     llvq_stream_t stream) {
+    TpCalls calls{};
+    int st = tp_fill_call(calls.c[0], c, site, buf_offset, src, shard_bytes);
+    if (st) return st;
+    tp_exchange_kernel<<<1, 32 * kTpMaxWorld, 0, (cudaStream_t)stream>>>(calls);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+int llvq_tp_exchange_emulated(llvq_tp_ctx* const* ctxs, int32_t n, int32_t site, size_t buf_offset, const void* const* srcs,
+                              uint32_t shard_bytes, llvq_stream_t stream) {
+    if (!ctxs || !srcs || n < 1 || n > kTpMaxWorld) return fail(LLVQ_ERR_INVALID, "tp_exchange_emulated: bad argument");
+    TpCalls calls{};
+    for (int i = 0; i < n; ++i) {
+        int st = tp_fill_call(calls.c[i], ctxs[i], site, buf_offset, srcs[i], shard_bytes);
+        if (st) return st;
+        if (ctxs[i]->device != ctxs[0]->device) return fail(LLVQ_ERR_INVALID, "tp_exchange_emulated: ranks on several devices");
+    }
+    DeviceGuard g(ctxs[0]->device);
+    // the CTAs wait on one another: a cooperative launch guarantees that all of them are resident
+    void* args[] = {&calls};
+    CUDA_TRY(cudaLaunchCooperativeKernel((const void*)tp_exchange_kernel, dim3(n), dim3(32 * kTpMaxWorld), args, 0,
+                                         (cudaStream_t)stream));
+    g_launches++;
+    return LLVQ_OK;
+}
+
+int llvq_tp_poll_error(llvq_tp_ctx* c, int32_t* out) {
+    if (!c || !out) return fail(LLVQ_ERR_INVALID, "tp_poll_error: null argument");
+    DeviceGuard g(c->device);
+    int v = 0;
+    CUDA_TRY(cudaMemcpy(&v, c->r.err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v) CUDA_TRY(cudaMemset(c->r.err, 0, sizeof(int)));
+    *out = v;
     return LLVQ_OK;
 }
 

@@ -98,12 +98,15 @@ class Int8KvCache:
 class TpGroup:
     """Rank layout of a tensor-parallel model: rank r of `world` holds q heads [r H/world, (r+1) H/world),
     the matching kv heads, rows [r I/world, ...) of gate/up, rows [r D/world, ...) of o/down and rows
-    [r V/world, ...) of the tied head. Every exchange is an all-gather of row shards in rank order."""
+    [r V/world, ...) of the tied head. Every exchange is an all-gather of row shards in rank order: NCCL
+    by default; with `peer_lib` (the C library) the gathers of the token step go through peer memory
+    (llvq_tp_exchange: peer stores + flags), the prompt's 2-D gathers stay on NCCL."""
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, peer_lib=None, spin_limit: int = 0):
         import torch.distributed as dist
         self.dist, self.group = dist, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.peer_lib, self.spin_limit, self.peer = peer_lib, spin_limit, None
 
     def check(self, cfg: Qwen3Config) -> None:
         for name, n in (("q heads", cfg.n_heads), ("kv heads", cfg.n_kv), ("intermediate rows", cfg.inter),
@@ -111,9 +114,22 @@ class TpGroup:
             if n % self.world:
                 raise ValueError(f"{n} {name} do not split over {self.world} ranks")
 
-    def gather_into(self, out, shard):
-        """out[world * n] <- shards [n] in rank order (1-D, preallocated: safe inside a graph capture)."""
-        self.dist.all_gather_into_tensor(out, shard, group=self.group)
+    def alloc(self, device, specs):
+        """Gathered buffers of the token step, one per site: specs = [(numel, dtype), ...] -> tensors."""
+        import torch
+        if self.peer_lib is None:
+            return [torch.zeros(n, dtype=dt, device=device) for n, dt in specs]
+        from .parallel import PeerExchange
+        sizes = [n * torch.empty(0, dtype=dt).element_size() for n, dt in specs]
+        self.peer = PeerExchange(self.peer_lib, device.index, sizes, group=self.group, spin_limit=self.spin_limit)
+        return [self.peer.buffer(i, dt) for i, (_, dt) in enumerate(specs)]
+
+    def gather_into(self, site: int, out, shard):
+        """out[world * n] <- shards [n] in rank order (1-D, preallocated by `alloc`: safe inside a graph capture)."""
+        if self.peer is not None:
+            self.peer.exchange(site, shard)
+        else:
+            self.dist.all_gather_into_tensor(out, shard, group=self.group)
         return out
 
     def gather_cols(self, shard):
@@ -170,8 +186,11 @@ class FusedQwen3:
             self._x, self._h = torch.zeros(cfg.hidden, **f16), torch.zeros(cfg.hidden, **f16)
             self._qkv = torch.zeros((self.h_loc + 2 * self.kv_loc) * hd, **f16)
             self._q = torch.zeros(self.h_loc * hd, **f16)
-            self._ctx, self._o, self._down = (torch.zeros(n, **f16) for n in (cfg.n_heads * hd, cfg.hidden, cfg.hidden))
-            self._gu, self._act = torch.zeros(2 * self.inter_loc, **f16), torch.zeros(cfg.inter, **f16)
+            gathered = [(cfg.n_heads * hd, torch.float16), (cfg.hidden, torch.float16), (cfg.inter, torch.float16),
+                        (cfg.hidden, torch.float16), (2 * self.world, torch.long)]
+            bufs = self.tp.alloc(dev, gathered) if self.tp else [torch.zeros(n, dtype=dt, device=dev) for n, dt in gathered]
+            self._ctx, self._o, self._act, self._down, self._best_all = bufs
+            self._gu = torch.zeros(2 * self.inter_loc, **f16)
             # the shard a rank computes before the gather; the full buffer itself when there is one rank
             self._ctx_loc = torch.zeros(self.h_loc * hd, **f16) if w > 1 else self._ctx
             self._o_loc = torch.zeros(cfg.hidden // w, **f16) if w > 1 else self._o
@@ -186,7 +205,8 @@ class FusedQwen3:
         self._tok = torch.zeros(1, dtype=torch.long, device=dev)
         self._pos = torch.zeros(1, dtype=torch.long, device=dev)
         self._best = torch.zeros(2, dtype=torch.long, device=dev)        # (logit bits, row) of this rank's shard
-        self._best_all = torch.zeros(2 * self.world, dtype=torch.long, device=dev)
+        if self.ops is None:
+            self._best_all = torch.zeros(2 * self.world, dtype=torch.long, device=dev)
 
     # ---- pieces ------------------------------------------------------------------
     def _rms(self, x, w):
@@ -279,7 +299,7 @@ class FusedQwen3:
             return idx
         self._best[0:1].view(val.dtype)[0:1].copy_(val)
         self._best[1:2].copy_(idx)
-        self.tp.gather_into(self._best_all, self._best)
+        self.tp.gather_into(4, self._best_all, self._best)
         pairs = self._best_all.view(self.world, 2)
         vals = pairs[:, 0:1].contiguous().view(val.dtype)[:, 0]
         return pairs[:, 1].index_select(0, vals.argmax().reshape(1))  # first rank on ties = lowest row
@@ -341,18 +361,18 @@ class FusedQwen3:
                                                p(cache.s[1]), p(cache.b[1]), p(self._pos), p(self._ctx_loc), self.h_loc,
                                                self.kv_loc, cfg.head_dim, self.attn_splits, p(self._attn_ws), st))
             if tp:
-                tp.gather_into(self._ctx, self._ctx_loc)
+                tp.gather_into(0, self._ctx, self._ctx_loc)
             self.gemv(blk["o"], self._ctx, out=self._o_loc)
             if tp:
-                tp.gather_into(self._o, self._o_loc)
+                tp.gather_into(1, self._o, self._o_loc)
             check(L.llvq_op_add_rmsnorm_h(p(self._x), p(self._o), p(blk["ln2"]), p(self._h), cfg.hidden, cfg.eps, st))
             self.gemv(blk["gate_up"], self._h, out=self._gu)
             check(L.llvq_op_silu_mul_h(p(self._gu), p(self._act_loc), self.inter_loc, st))
             if tp:
-                tp.gather_into(self._act, self._act_loc)
+                tp.gather_into(2, self._act, self._act_loc)
             self.gemv(blk["down"], self._act, out=self._down_loc)
             if tp:
-                tp.gather_into(self._down, self._down_loc)
+                tp.gather_into(3, self._down, self._down_loc)
             delta = self._down
         check(L.llvq_op_add_rmsnorm_h(p(self._x), p(delta), p(self.final_norm), p(self._h), cfg.hidden, cfg.eps, st))
         self._tok.copy_(self.pick(self._h))

@@ -200,6 +200,13 @@ def _tp_gpu_worker(rank, world, port, q):
         q.put((rank, "eager", want, got))
         graphed = sharded.generate(prompt, 20, use_graph=True)
         q.put((rank, "graph", want, graphed))
+        # the same model with the token-step gathers through peer memory (llvq_tp_exchange)
+        peer_tp = TpGroup(peer_lib=rt.lib)
+        peered, _ = synthetic_model(rt, cfg, config_id=4, capacity=96, tp=peer_tp)
+        q.put((rank, "peer eager", want, peered.generate(prompt, 20)))
+        q.put((rank, "peer graph", want, peered.generate(prompt, 20, use_graph=True)))
+        torch.cuda.synchronize()
+        q.put((rank, "peer errors", 0, peer_tp.peer.poll_error()))
         torch.cuda.synchronize()
     except BaseException:  # noqa: BLE001 - reported to the parent, which fails the test
         q.put((rank, "error", traceback.format_exc(), None))
@@ -227,7 +234,7 @@ def test_tensor_parallel_model_on_two_gpus_picks_the_single_gpu_tokens():
         p.start()
     got = []
     try:
-        while len(got) < 4:
+        while len(got) < 10:
             item = q.get(timeout=240)
             got.append(item)
             assert item[1] != "error", f"rank {item[0]} failed:\n{item[2]}"

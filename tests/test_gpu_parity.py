@@ -355,3 +355,110 @@ def test_greedy_head_kernel_matches_a_float_argmax(rt):
     assert int(idx) == 5
     with pytest.raises(Exception):
         head(torch.zeros(4, 12, device="cuda", dtype=torch.float16), torch.zeros(12, device="cuda", dtype=torch.float16), 0)
+
+
+def _tp_regions(L, n, data_bytes):
+    import ctypes as C
+    from llvq_b200._lib import check
+    regions = (C.c_void_p * n)()
+    for r in range(n):
+        p, h = C.c_void_p(), (C.c_uint8 * 64)()
+        check(L.llvq_tp_region_create(0, data_bytes, C.byref(p), h))
+        regions[r] = p.value
+    return regions
+
+
+def test_peer_exchange_protocol_with_all_ranks_in_one_cooperative_launch(rt):
+    """llvq_tp_exchange on one GPU: four ranks' regions in the same memory, the four exchanges run as ONE
+    cooperative launch (ranks that wait on each other are never separate launches on a GPU). Every region
+    ends up with all shards in rank order, over several rounds and two sites, with aligned and odd sizes."""
+    import ctypes as C
+    torch = _torch()
+    from llvq_b200._lib import check
+    from llvq_b200.parallel import _DeviceBytes
+    L, n = rt.lib, 4
+    flag_bytes, buf_bytes = 512, 4096
+    regions = _tp_regions(L, n, 2 * buf_bytes)
+    ctxs = (C.c_void_p * n)()
+    for r in range(n):
+        c = C.c_void_p()
+        check(L.llvq_tp_ctx_create(0, r, n, regions, 0, C.byref(c)))
+        ctxs[r] = c.value
+    views = [torch.as_tensor(_DeviceBytes(regions[r], flag_bytes + 2 * buf_bytes), device="cuda") for r in range(n)]
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for rnd, (site, shard_bytes) in enumerate([(0, 640), (1, 1001), (0, 16), (1, 2), (0, 1024)]):
+        shards = [torch.randint(0, 256, (shard_bytes,), dtype=torch.uint8, device="cuda", generator=g) for _ in range(n)]
+        srcs = (C.c_void_p * n)(*[s.data_ptr() for s in shards])
+        off = flag_bytes + site * buf_bytes
+        check(L.llvq_tp_exchange_emulated(ctxs, n, site, off, srcs, shard_bytes, st))
+        torch.cuda.synchronize()
+        want = torch.cat(shards)
+        for r in range(n):
+            assert torch.equal(views[r][off:off + n * shard_bytes], want), (rnd, r)
+            flags = views[r][:flag_bytes].view(torch.int32).view(16, 8)
+            assert flags[site, :n].tolist() == [rnd + 1] * n  # every source released exchange number rnd + 1 here
+    for r in range(n):
+        err = C.c_int32(-1)
+        check(L.llvq_tp_poll_error(ctxs[r], C.byref(err)))
+        assert err.value == 0
+        L.llvq_tp_ctx_destroy(ctxs[r])
+    del views
+    for r in range(n):
+        check(L.llvq_tp_region_free(0, regions[r]))
+
+
+def test_peer_exchange_wait_runs_out_and_reports_instead_of_hanging(rt):
+    """A peer that never shows up: the bounded wait gives up, the kernel returns, the error word says so and
+    the rank's own shard has still been delivered (nothing is made to fault or hang)."""
+    import ctypes as C
+    torch = _torch()
+    from llvq_b200._lib import check
+    from llvq_b200.parallel import _DeviceBytes
+    L = rt.lib
+    regions = _tp_regions(L, 2, 1024)
+    c = C.c_void_p()
+    check(L.llvq_tp_ctx_create(0, 0, 2, regions, 2000, C.byref(c)))  # rank 0 of 2; rank 1 never runs
+    shard = torch.arange(64, dtype=torch.uint8, device="cuda")
+    check(L.llvq_tp_exchange(c, 3, 512, C.c_void_p(shard.data_ptr()), 64, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    err = C.c_int32(0)
+    check(L.llvq_tp_poll_error(c, C.byref(err)))
+    assert err.value == 4
+    check(L.llvq_tp_poll_error(c, C.byref(err)))
+    assert err.value == 0  # reading clears it
+    peer = torch.as_tensor(_DeviceBytes(regions[1], 512 + 1024), device="cuda")
+    assert torch.equal(peer[512:576], shard) and int(peer[:512].view(torch.int32).view(16, 8)[3, 0]) == 1
+    assert L.llvq_tp_exchange(c, 16, 512, C.c_void_p(shard.data_ptr()), 64, None) != 0   # site out of range
+    assert L.llvq_tp_exchange(c, 0, 100, C.c_void_p(shard.data_ptr()), 64, None) != 0    # offset inside the flags
+    L.llvq_tp_ctx_destroy(c)
+    del peer
+    for r in range(2):
+        check(L.llvq_tp_region_free(0, regions[r]))
+
+
+@pytest.mark.parametrize("d_out,d_in", [(200, 24 * 70 + 9), (64, 24 * 213 + 8), (24, 24 * 33), (1000, 24 * 5 + 1), (16, 7)])
+def test_gemv_column_splits_agree_with_the_oracle(rt, oracle, d_out, d_in):
+    """Any column split gives the oracle's value within the f16 tolerance, the same bits on every launch,
+    and the default comes back with 0."""
+    import ctypes as C
+    torch = _torch()
+    from llvq_b200 import synth
+    from llvq_b200._lib import check
+    m = synth.make_matrix(d_out, d_in, 0x6A1D + d_out)
+    proj = rt.upload(m, tail_f16=True)
+    x = torch.from_numpy(synth.make_activation(d_in, 3, np.float16)).cuda()
+    nb = d_in // 24
+    got = C.c_int32()
+    check(rt.lib.llvq_matrix_get_splits(proj._h, C.byref(got)))
+    assert got.value == max(1, -(-nb // 128))
+    tail16 = m.tail.astype(np.float16).astype(np.float32)
+    ref = oracle.gemv_f64(m.codes, d_out, d_in, m.centroids, m.row_scales, tail16, x.cpu().numpy().astype(np.float64))
+    for n in (0, 1, 2, 3, 7, 50, 100000):
+        check(rt.lib.llvq_matrix_set_splits(proj._h, n))
+        check(rt.lib.llvq_matrix_get_splits(proj._h, C.byref(got)))
+        assert 1 <= got.value <= max(1, nb)
+        y = rt.forward(proj, x).clone()
+        assert rel_l2(y.cpu().numpy(), ref) <= TOL_F16, n
+        assert torch.equal(rt.forward(proj, x), y)  # the arrival counters are re-armed by the launch itself
+    assert not rt.poll_range_error()
