@@ -126,8 +126,8 @@ int llvq_matrix_dims(const llvq_matrix* m, int32_t* d_out, int32_t* d_in);
 /* Column split of the batch-1 GEMV: `splits` CTAs share every 8-row tile, each decoding its own range
  * of column blocks; partial row sums are added in split order, so the result does not depend on
  * scheduling (it does depend on the split count, in the last bits of the f32 sum). The upload takes
- * the fewest splits the 128-block chunk allows (ceil(nblocks / 128)); more splits spread a matrix
- * with few rows over more SMs. 0 restores the default. Tuning knob with no counterpart in the
+ * the fewest splits the 128-block chunk allows (ceil(nblocks / 128)), more for a matrix with so few
+ * rows that its grid would leave most SMs idle. 0 restores that default. Tuning knob with no counterpart in the
  * reference. Synchronises the device and reallocates the workspace: not for use inside a capture. */
 int llvq_matrix_set_splits(llvq_matrix* m, int32_t splits);
 int llvq_matrix_get_splits(const llvq_matrix* m, int32_t* splits);

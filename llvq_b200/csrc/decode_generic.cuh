@@ -178,49 +178,66 @@ LLVQ_HD unsigned long long exact_div_params(int n) {
 #endif
 }
 
-template <typename CntT>
-LLVQ_HD int unrank_step32(unsigned int& rank, unsigned int& m, int& n, CntT& cnt, int k) {
+// One slot of a multiset unranking with all candidates evaluated at once. `cum` holds the running
+// cumulative counts, one per byte (byte j = items left of kinds 0..j; bytes past the last kind equal n).
+// The thresholds T_j = M * cum_j / n are exact integers (each M * c_i / n is), independent of one
+// another, and the chosen kind is the number of thresholds at or below the rank: no loop-carried
+// subtraction, so a single thread gets instruction-level parallelism out of it.
+template <int KMAX, typename CumT>
+LLVQ_HD int unrank_step32(unsigned int& rank, unsigned int& m, int& n, CumT& cum) {
     const unsigned long long prm = exact_div_params(n);
     const unsigned int inv = (unsigned int)prm, a = (unsigned int)(prm >> 32);
-    int chosen = k - 1;
-    for (int j = 0; j < k; ++j) {
-        const unsigned int c = (unsigned int)(cnt >> (8 * j)) & 0xffu;
-        if (c == 0) continue;
-        const unsigned int mj = (unsigned int)(((unsigned long long)m * c) >> a) * inv;
-        if (rank < mj || j == k - 1) {
-            m = mj;
-            chosen = j;
-            break;
-        }
-        rank -= mj;
+    // the thresholds ascend, so the last one at or below the rank is the lower bound of the chosen
+    // kind and the first one above it (M if none) its upper bound
+    unsigned int lo = 0, hi = m;
+    int chosen = 0;
+#pragma unroll
+    for (int j = KMAX - 2; j >= 0; --j) {
+        const unsigned int cj = (unsigned int)(cum >> (8 * j)) & 0xffu;
+        const unsigned int t = (unsigned int)(((unsigned long long)m * cj) >> a) * inv;
+        const bool below = rank >= t;  // t = M for the bytes past the last kind: never reached
+        chosen += below ? 1 : 0;
+        hi = below ? hi : t;
+        lo = (below && t > lo) ? t : lo;
     }
-    cnt -= (CntT)1 << (8 * chosen);
+    rank -= lo;
+    m = hi - lo;
+    CumT ones = 0;
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) ones |= (CumT)1 << (8 * j);
+    cum -= ones << (8 * chosen);
     n -= 1;
     return chosen;
 }
 
-// Contract of decode_generic, for idx in the cap-12 ball (anything else is refused).
+// The class-local half of decode_generic12: `local` is the rank of the point inside class `ci` of the
+// cap-12 ball (what a caller that has already searched the class passes on, sparing a second search).
+// Emits the 24 coordinates in position order, returns the shell.
 template <class Emit>
-LLVQ_HD int decode_generic12(const DevTables& T, unsigned long long idx, Emit emit, float* scale) {
-    if (idx == 0 || idx > kN12) {
-#pragma unroll
-        for (int pos = 0; pos < kDim; ++pos) emit(pos, 0);
-        *scale = 0.0f;
-        return idx == 0 ? 0 : 255;
-    }
-    const unsigned long long i = idx - 1;
-    const int ci = find_class(T, i);
+LLVQ_HD int decode_class12(const DevTables& T, int ci, unsigned long long local, Emit emit, float* scale) {
     const DevClass c = T.cls[ci];
-    unsigned long long local = i - c.offset;
     *scale = c.inv_norm;
     unsigned int rank_a, m_a = (unsigned int)c.arr_a, rank_b = 0, m_b = (unsigned int)c.arr_b;
-    unsigned long long cnt_a = c.cnts_a;
-    unsigned int cnt_b = c.cnts_b;
+    // byte-wise prefix sums of the counts in one multiplication (no byte exceeds 24, so no carries)
+    unsigned long long cum_a = c.cnts_a * 0x0101010101010101ull;
+    unsigned int cum_b = c.cnts_b * 0x01010101u;
     int n_a, n_b = 0;
     unsigned int cw, sw = 0, sf = 0;
     if (c.odd) {
-        rank_a = (unsigned int)(local % m_a);
-        cw = T.golay[local / m_a];
+        // local = g * m_a + r with g < 4096: the quotient has 12 bits, so 32-bit pieces are enough
+        unsigned int g = (unsigned int)(((float)(unsigned int)(local >> 32) * 4294967296.0f + (float)(unsigned int)local) /
+                                        (float)m_a);
+        long long rem = (long long)(local - (unsigned long long)g * m_a);  // float estimate, fixed up exactly
+        while (rem < 0) {
+            g -= 1;
+            rem += m_a;
+        }
+        while (rem >= (long long)m_a) {
+            g += 1;
+            rem -= m_a;
+        }
+        rank_a = (unsigned int)rem;
+        cw = T.golay[g];
         n_a = kDim;
     } else {
         sf = (unsigned int)local & ((1u << c.free_n) - 1u);
@@ -242,7 +259,7 @@ LLVQ_HD int decode_generic12(const DevTables& T, unsigned long long idx, Emit em
         const unsigned int bit = (cw >> pos) & 1u;
         int val;
         if (c.odd || bit) {
-            const int j = unrank_step32(rank_a, m_a, n_a, cnt_a, (int)c.n_a);
+            const int j = unrank_step32<8>(rank_a, m_a, n_a, cum_a);
             const int v = (int)((c.vals_a >> (4 * j)) & 15u);
             if (c.odd) {
                 const int a = (v & 3) == 3 ? v : -v;
@@ -252,7 +269,7 @@ LLVQ_HD int decode_generic12(const DevTables& T, unsigned long long idx, Emit em
                 sw >>= 1;
             }
         } else {
-            const int j = unrank_step32(rank_b, m_b, n_b, cnt_b, (int)c.n_b);
+            const int j = unrank_step32<4>(rank_b, m_b, n_b, cum_b);
             const int v = (int)((c.vals_b >> (4 * j)) & 15u);
             val = v;
             if (v) {
@@ -263,6 +280,20 @@ LLVQ_HD int decode_generic12(const DevTables& T, unsigned long long idx, Emit em
         emit(pos, val);
     }
     return c.shell;
+}
+
+// Contract of decode_generic, for idx in the cap-12 ball (anything else is refused).
+template <class Emit>
+LLVQ_HD int decode_generic12(const DevTables& T, unsigned long long idx, Emit emit, float* scale) {
+    if (idx == 0 || idx > kN12) {
+#pragma unroll
+        for (int pos = 0; pos < kDim; ++pos) emit(pos, 0);
+        *scale = 0.0f;
+        return idx == 0 ? 0 : 255;
+    }
+    const unsigned long long i = idx - 1;
+    const int ci = find_class(T, i);
+    return decode_class12(T, ci, i - T.cls[ci].offset, emit, scale);
 }
 
 // Big-endian 48-bit record of block b: idx = v >> 1, gain = v & 1

@@ -217,7 +217,7 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
                 const Classified c = classify12(F, v >> 1);
                 if (c.ci >= 0) {
                     path = c.path;
-                    const unsigned long long loc = path == kPathSlow ? (v >> 1) : c.local;  // generic wants the index
+                    const unsigned long long loc = c.local;
                     S.items[f] = make_uint2((unsigned int)loc, (unsigned int)(loc >> 32) | (unsigned int)c.ci << 15 |
                                                                    (unsigned int)(v & 1ull) << 24);
                 } else {
@@ -273,8 +273,8 @@ gemv_sorted_kernel(FastTables F, DevTables G, MatrixView mv, const XT* __restric
                     scale = bits_to_float(q3.x);
                     even_fast(F, local, q0.z, q1, q2, dot);
                 } else if (fam == kPathSlow) {
-                    decode_generic12(G, local, [&](int pos, int v) { acc = fmaf((float)v, xb[pos * kChunkPad], acc); },
-                                     &scale);
+                    decode_class12(G, ci, local, [&](int pos, int v) { acc = fmaf((float)v, xb[pos * kChunkPad], acc); },
+                                   &scale);
                 } else {
                     const Quad q0 = load_quad(rec, 0), q1 = load_quad(rec, 1);
                     unsigned int g, r;
