@@ -398,7 +398,15 @@ def run_tp(args):
         dist.destroy_process_group()
 
 
+def _quiet_nccl():
+    """The image exports NCCL_DEBUG=VERSION, which makes NCCL print a banner on stdout ahead of the one JSON
+    line a rank-0 run must print; anything the user set beyond that (INFO, WARN) is left alone."""
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
+
+
 def main():
+    _quiet_nccl()
     ap = argparse.ArgumentParser()
     ap.add_argument("--tp", action="store_true",
                     help="tensor-parallel mode: Qwen3-14B projections row-sharded over the ranks with all-gathers")
