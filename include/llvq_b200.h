@@ -244,6 +244,31 @@ int llvq_op_lm_head_argmax_h(const uint16_t* embed_dev, const uint16_t* h_dev, i
  * transient operand for long-prompt GEMMs. An index outside the ball raises the runtime's range flag. */
 int llvq_matrix_dequant_h(llvq_matrix* m, uint16_t* out_dev, llvq_stream_t stream);
 
+/* ---- activation rotation ------------------------------------------------------
+ * Every sealed matrix was quantised in a rotated basis, Q = (Q_odd (x) H_m) D built from its
+ * rotation seed (llvq-quant/src/rotation.rs:51-68); the runtime rotates the activation once per
+ * shared input and feeds the f32 result to llvq_gemv_f32x_h. This replaces FusedRuntime::rotate /
+ * the rot_apply kernel (llvq-llm/src/fused_cuda.rs:362-379, llvq-cuda/kernels/rotate.cu:38-67) and
+ * RotationTables::build (llvq-llm/src/fused.rs:678-725). Odd factors up to 32, as the reference. */
+typedef struct llvq_rotation llvq_rotation;
+/* Build the tables from (width, seed) on the host and upload them. */
+int llvq_rotation_create(llvq_runtime* rt, int32_t n, uint64_t seed, llvq_rotation** out);
+/* The same from tables the caller already holds: signbits = ceil(n / 32) words, bit i & 31 of word
+ * i >> 5 set = negative; small = Q_odd, k x k row-major f32 (k = n / largest power of two in n; may be
+ * NULL when k = 1). */
+int llvq_rotation_create_from_tables(llvq_runtime* rt, int32_t n, const uint32_t* signbits, const float* small,
+                                     llvq_rotation** out);
+/* Host only (no GPU needed): the tables of (width, seed) into caller buffers of ceil(n / 32) words and
+ * k * k floats (either may be NULL), and 1 / sqrt(m). */
+int llvq_rotation_build_tables(int32_t n, uint64_t seed, uint32_t* signbits_out, float* small_out, float* inv_sqrt_m_out);
+void llvq_rotation_free(llvq_rotation* rot);
+int llvq_rotation_info(const llvq_rotation* rot, int32_t* n, int32_t* m, int32_t* k, float* inv_sqrt_m);
+/* Copy the host tables out (either pointer may be NULL): ceil(n / 32) words, k * k floats. */
+int llvq_rotation_tables(const llvq_rotation* rot, uint32_t* signbits_out, float* small_out);
+/* x' = Q x for `batch` activations: f16 [batch, n] in, f32 [batch, n] out, both device memory, one
+ * launch (one CTA per activation). */
+int llvq_rotate_h(llvq_rotation* rot, const uint16_t* x_dev, float* xr_dev, int32_t batch, llvq_stream_t stream);
+
 /* ---- peer-memory all-gather of row shards (tensor-parallel token step) -------
  * No counterpart in the reference, which is single-GPU. A rank owns one region =
  * LLVQ_TP_FLAG_BYTES of flags followed by its gather buffers, maps the regions of its peers

@@ -58,6 +58,14 @@ _SIGNATURES = {
     "llvq_op_qkv_rope_cache_h": (C.c_int, [C.c_void_p] * 13 + [C.c_int32] * 3 + [C.c_float, C.c_void_p]),
     "llvq_matrix_set_splits": (C.c_int, [C.c_void_p, C.c_int32]),
     "llvq_matrix_get_splits": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
+    "llvq_rotation_create": (C.c_int, [C.c_void_p, C.c_int32, C.c_uint64, C.POINTER(C.c_void_p)]),
+    "llvq_rotation_create_from_tables": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "llvq_rotation_build_tables": (C.c_int, [C.c_int32, C.c_uint64, C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]),
+    "llvq_rotation_free": (None, [C.c_void_p]),
+    "llvq_rotation_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                    C.POINTER(C.c_float)]),
+    "llvq_rotation_tables": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llvq_rotate_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "llvq_tp_region_create": (C.c_int, [C.c_int32, C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),
     "llvq_tp_region_open": (C.c_int, [C.c_int32, C.c_void_p, C.POINTER(C.c_void_p)]),
     "llvq_tp_region_close": (C.c_int, [C.c_int32, C.c_void_p]),

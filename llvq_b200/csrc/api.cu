@@ -7,6 +7,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cmath>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -16,6 +17,8 @@
 #include "codebook.h"
 #include "decode_ops.cuh"
 #include "dense_ops.cuh"
+#include "rotate.cuh"
+#include "rotation.h"
 #include "tp_exchange.cuh"
 #include "gemm_tc.cuh"
 #include "gemv_sorted.cuh"
@@ -324,6 +327,14 @@ int gemv_host(llvq_matrix* m, const XT* xh, YT* yh, llvq_stream_t stream) {
 }
 
 }  // namespace
+
+struct llvq_rotation {
+    llvq_runtime* rt = nullptr;
+    RotationTables t;
+    unsigned int* d_signbits = nullptr;
+    float* d_small = nullptr;
+    size_t smem = 0;
+};
 
 struct llvq_tp_ctx {
     int device = 0;
@@ -727,6 +738,105 @@ int llvq_matrix_dequant_h(llvq_matrix* m, uint16_t* out, llvq_stream_t stream) {
     const size_t items = (size_t)mv.d_out * (mv.nb + (mv.tail_w ? 1 : 0));
     if (items == 0) return LLVQ_OK;
     dequant_dense_kernel<<<(unsigned int)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(rt->F, rt->T, mv, (__half*)out, rt->d_err);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+// ---- activation rotation ------------------------------------------------------------
+
+static int rotation_upload(llvq_runtime* rt, RotationTables&& t, llvq_rotation** out) {
+    if (t.k > kRotMaxOdd)
+        return fail(LLVQ_ERR_UNSUPPORTED, "rotation: width %d has the odd factor %d, beyond %d", t.n, t.k, kRotMaxOdd);
+    const size_t smem = ((size_t)t.n + (size_t)t.k * t.k) * sizeof(float);
+    if (smem > (size_t)rt->max_smem_optin)
+        return fail(LLVQ_ERR_UNSUPPORTED, "rotation: width %d needs %zu bytes of shared memory, the device gives %d", t.n, smem,
+                    rt->max_smem_optin);
+    DeviceGuard g(rt->device);
+    std::unique_ptr<llvq_rotation> r(new llvq_rotation);
+    r->rt = rt;
+    r->smem = smem;
+    r->t = std::move(t);
+    cudaError_t e = cudaMalloc((void**)&r->d_signbits, r->t.signbits.size() * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&r->d_small, r->t.small.size() * sizeof(float));
+    if (e == cudaSuccess)
+        e = cudaMemcpy(r->d_signbits, r->t.signbits.data(), r->t.signbits.size() * sizeof(unsigned int), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(r->d_small, r->t.small.data(), r->t.small.size() * sizeof(float), cudaMemcpyHostToDevice);
+    static size_t configured = 0;
+    if (e == cudaSuccess && smem > configured) {
+        e = cudaFuncSetAttribute(rot_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) configured = smem;
+    }
+    if (e != cudaSuccess) {
+        cudaFree(r->d_signbits);
+        cudaFree(r->d_small);
+        return fail(LLVQ_ERR_CUDA, "rotation upload: %s", cudaGetErrorString(e));
+    }
+    *out = r.release();
+    return LLVQ_OK;
+}
+
+int llvq_rotation_create(llvq_runtime* rt, int32_t n, uint64_t seed, llvq_rotation** out) {
+    if (!rt || !out || n <= 0) return fail(LLVQ_ERR_INVALID, "rotation_create: bad argument");
+    return rotation_upload(rt, build_rotation(n, seed), out);
+}
+
+int llvq_rotation_create_from_tables(llvq_runtime* rt, int32_t n, const uint32_t* signbits, const float* small, llvq_rotation** out) {
+    if (!rt || !out || n <= 0 || !signbits) return fail(LLVQ_ERR_INVALID, "rotation_create_from_tables: bad argument");
+    RotationTables t;
+    t.n = n;
+    t.m = n & -n;
+    t.k = n / t.m;
+    if (t.k > 1 && !small) return fail(LLVQ_ERR_INVALID, "rotation_create_from_tables: width %d needs a %d x %d mix", n, t.k, t.k);
+    if (t.k > kRotMaxOdd)
+        return fail(LLVQ_ERR_UNSUPPORTED, "rotation: width %d has the odd factor %d, beyond %d", n, t.k, kRotMaxOdd);
+    t.signbits.assign(signbits, signbits + ((size_t)n + 31) / 32);
+    if (t.k > 1) t.small.assign(small, small + (size_t)t.k * t.k);
+    else t.small.assign(1, 1.0f);
+    t.inv = (float)(1.0 / std::sqrt((double)t.m));
+    return rotation_upload(rt, std::move(t), out);
+}
+
+int llvq_rotation_build_tables(int32_t n, uint64_t seed, uint32_t* signbits, float* small, float* inv) {
+    if (n <= 0) return fail(LLVQ_ERR_INVALID, "rotation_build_tables: width %d", n);
+    const RotationTables t = build_rotation(n, seed);
+    if (signbits) std::memcpy(signbits, t.signbits.data(), t.signbits.size() * sizeof(uint32_t));
+    if (small) std::memcpy(small, t.small.data(), t.small.size() * sizeof(float));
+    if (inv) *inv = t.inv;
+    return LLVQ_OK;
+}
+
+void llvq_rotation_free(llvq_rotation* r) {
+    if (!r) return;
+    DeviceGuard g(r->rt->device);
+    cudaFree(r->d_signbits);
+    cudaFree(r->d_small);
+    delete r;
+}
+
+int llvq_rotation_info(const llvq_rotation* r, int32_t* n, int32_t* m, int32_t* k, float* inv) {
+    if (!r) return fail(LLVQ_ERR_INVALID, "rotation_info: null rotation");
+    if (n) *n = r->t.n;
+    if (m) *m = r->t.m;
+    if (k) *k = r->t.k;
+    if (inv) *inv = r->t.inv;
+    return LLVQ_OK;
+}
+
+int llvq_rotation_tables(const llvq_rotation* r, uint32_t* signbits, float* small) {
+    if (!r) return fail(LLVQ_ERR_INVALID, "rotation_tables: null rotation");
+    if (signbits) std::memcpy(signbits, r->t.signbits.data(), r->t.signbits.size() * sizeof(uint32_t));
+    if (small) std::memcpy(small, r->t.small.data(), r->t.small.size() * sizeof(float));
+    return LLVQ_OK;
+}
+
+int llvq_rotate_h(llvq_rotation* r, const uint16_t* x, float* xr, int32_t batch, llvq_stream_t stream) {
+    if (!r || !x || !xr || batch < 0) return fail(LLVQ_ERR_INVALID, "rotate_h: bad argument");
+    if (batch == 0) return LLVQ_OK;
+    if (((uintptr_t)x & 1u) || ((uintptr_t)xr & 3u)) return fail(LLVQ_ERR_INVALID, "rotate_h: misaligned buffer");
+    DeviceGuard g(r->rt->device);
+    rot_apply_kernel<<<batch, kRotThreads, r->smem, (cudaStream_t)stream>>>((const __half*)x, r->d_signbits, r->d_small, xr, r->t.n,
+                                                                        r->t.m, r->t.k, r->t.inv);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;

@@ -63,6 +63,28 @@ class FusedProj:
             pass
 
 
+class DeviceRotation:
+    """Handle of one uploaded rotation (sign bitmap, odd mix, 1/sqrt(m))."""
+
+    def __init__(self, rt: "FusedRuntime", handle: int, n: int):
+        self.rt, self._h, self.n = rt, C.c_void_p(handle), n
+        m, k, inv = C.c_int32(), C.c_int32(), C.c_float()
+        check(rt.lib.llvq_rotation_info(self._h, None, C.byref(m), C.byref(k), C.byref(inv)))
+        self.m, self.k, self.inv = m.value, k.value, inv.value
+
+    def tables(self):
+        """(signbits uint32 [ceil(n/32)], small float32 [k, k]) as uploaded."""
+        sb = np.zeros((self.n + 31) // 32, np.uint32)
+        small = np.zeros((self.k, self.k), np.float32)
+        check(self.rt.lib.llvq_rotation_tables(self._h, sb.ctypes.data, small.ctypes.data))
+        return sb, small
+
+    def free(self) -> None:
+        if self._h:
+            self.rt.lib.llvq_rotation_free(self._h)
+            self._h = C.c_void_p(None)
+
+
 class FusedRuntime:
     """Per-GPU decoder tables, verified against the published codebook fingerprint on creation."""
 
@@ -103,6 +125,23 @@ class FusedRuntime:
         h = C.c_void_p()
         check(self.lib.llvq_matrix_upload_group(self._h, arr, len(ms), C.byref(h)))
         return FusedProj(self, h.value, "|".join(m.name for m in ms), [m.d_out for m in ms])
+
+    # -- rotation ---------------------------------------------------------------
+    def rotation(self, n: int, seed: int) -> "DeviceRotation":
+        """The incoherence rotation of width n built from a matrix's rotation seed (RotationTables::build)."""
+        h = C.c_void_p()
+        check(self.lib.llvq_rotation_create(self._h, n, seed & 0xFFFFFFFFFFFFFFFF, C.byref(h)))
+        return DeviceRotation(self, h.value, n)
+
+    def rotate(self, rot: "DeviceRotation", x, out=None):
+        """f16 activation [n] or [B, n] -> the same in the rotated basis, f32; FusedRuntime::rotate.
+        Its output is what forward_rotated consumes; one rotation serves every projection of a group."""
+        import torch
+        if not x.is_cuda or x.dtype != torch.float16 or not x.is_contiguous() or x.shape[-1] != rot.n or x.dim() > 2:
+            raise ValueError(f"rotate: a contiguous CUDA f16 activation of {rot.n} elements (or a batch of them)")
+        xr = out if out is not None else torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        check(self.lib.llvq_rotate_h(rot._h, x.data_ptr(), xr.data_ptr(), x.numel() // rot.n, self._stream()))
+        return xr
 
     # -- forward ----------------------------------------------------------------
     @staticmethod
