@@ -160,37 +160,50 @@ def gemm_section(rt, torch, synth, layers=3, iters=4):
     return out
 
 
-def decode_section(rt, torch, prompt_len=128, new_tokens=256):
+def decode_section(rt, torch, prompt_len=128, new_tokens=256, rotations=False):
     """BASELINE config 2: Qwen3-4B-architecture greedy decode at batch 1 (36 layers, random LLVQ codes, f16
     tied embedding, int8 KV cache), 128 random prompt tokens then 256 generated; the token step is replayed
-    from a CUDA graph. tok/s counts the generated tokens over the decode phase (prefill reported apart)."""
+    from a CUDA graph. tok/s counts the generated tokens over the decode phase (prefill reported apart).
+    With `rotations` the same model is timed a second time with an incoherence rotation in front of every
+    projection group (4 more launches per layer), as a real artifact needs; the configuration itself has none."""
     from llvq_b200.model import Qwen3Config, synthetic_model
     cfg = Qwen3Config.named(MODEL)
     t0 = time.perf_counter()
-    model, _ = synthetic_model(rt, cfg, config_id=2, capacity=prompt_len + new_tokens)
+    model, _ = synthetic_model(rt, cfg, config_id=2, capacity=prompt_len + new_tokens, rotations=rotations)
     setup = time.perf_counter() - t0
     rng = np.random.default_rng(0x2C0DE)
     prompt = [int(t) for t in rng.integers(0, cfg.vocab, prompt_len)]
-    model.generate(prompt, 4, use_graph=True)  # captures the graph
-    times = []
-    for _ in range(2):
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        nxt = model.pick(model._rms(model.prefill(prompt), model.final_norm)[0])
-        torch.cuda.synchronize()
-        t1 = time.perf_counter()
-        model.start_decode(nxt, prompt_len)
-        out = [int(nxt)]
-        while len(out) < new_tokens:
-            model._graph_step()
-            out.append(int(model._tok))
-        torch.cuda.synchronize()
-        times.append((t1 - t0, time.perf_counter() - t1))
-    prefill_s, decode_s = min(t[0] for t in times), min(t[1] for t in times)
-    return {"workload": "qwen3-4b-greedy-decode", "prompt_tokens": prompt_len, "new_tokens": new_tokens,
-            "tok_per_s": (new_tokens - 1) / decode_s, "ms_per_token": decode_s / (new_tokens - 1) * 1e3,
-            "prefill_ms": prefill_s * 1e3, "prefill_tok_per_s": prompt_len / prefill_s, "kv_cache": "int8 g64",
-            "graph": True, "setup_s": setup, "distinct_tokens": len(set(out))}
+
+    def timed():
+        model._graph = None
+        model.generate(prompt, 4, use_graph=True)  # captures the graph
+        times = []
+        for _ in range(2):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            nxt = model.pick(model._rms(model.prefill(prompt), model.final_norm)[0])
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            model.start_decode(nxt, prompt_len)
+            out = [int(nxt)]
+            while len(out) < new_tokens:
+                model._graph_step()
+                out.append(int(model._tok))
+            torch.cuda.synchronize()
+            times.append((t1 - t0, time.perf_counter() - t1))
+        prefill_s, decode_s = min(t[0] for t in times), min(t[1] for t in times)
+        return {"tok_per_s": (new_tokens - 1) / decode_s, "ms_per_token": decode_s / (new_tokens - 1) * 1e3,
+                "prefill_ms": prefill_s * 1e3, "prefill_tok_per_s": prompt_len / prefill_s, "distinct_tokens": len(set(out))}
+
+    held = [{k: blk.pop(k) for k in list(blk) if k.startswith("rot_")} for blk in model.blocks]
+    res = {"workload": "qwen3-4b-greedy-decode", "prompt_tokens": prompt_len, "new_tokens": new_tokens, "kv_cache": "int8 g64",
+           "graph": True, "setup_s": setup}
+    res.update(timed())
+    if rotations:
+        for blk, rots in zip(model.blocks, held):
+            blk.update(rots)
+        res["with_rotations"] = timed()
+    return res
 
 
 def run_reference(args):
@@ -425,6 +438,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemm", action="store_true", help="skip the batched-GEMM (config 3) side measurement")
     ap.add_argument("--no-decode", action="store_true", help="skip the greedy-decode (config 2) side measurement")
+    ap.add_argument("--rotations", action="store_true",
+                    help="time the config-2 decode a second time with an activation rotation per projection group")
     ap.add_argument("--no-groups", action="store_true",
                     help="launch q, k, v and gate, up separately instead of row-concatenated")
     args = ap.parse_args()
@@ -564,7 +579,7 @@ def main():
     if not args.no_gemm:
         out["gemm"] = gemm_section(rt, torch, synth)
     if not args.no_decode:
-        out["decode"] = decode_section(rt, torch)
+        out["decode"] = decode_section(rt, torch, rotations=args.rotations)
     if not args.no_cpu_baseline:
         cb, _ = cpu_baseline()
         out["cpu_baseline"] = cb

@@ -147,13 +147,19 @@ class FusedQwen3:
 
     def __init__(self, cfg: Qwen3Config, blocks: Sequence[dict], embed, final_norm, capacity: int,
                  gemv: Callable, gemm: Callable, head: Callable, kv_int8: bool = True, ops=None,
-                 tp: Optional[TpGroup] = None, prefill_chunk: int = 2048):
+                 tp: Optional[TpGroup] = None, prefill_chunk: int = 2048, rotate: Optional[Callable] = None,
+                 gemv_rotated: Optional[Callable] = None):
         """blocks[i]: {"qkv", "o", "gate_up", "down": projection handles, "ln1", "ln2", "q_norm", "k_norm": f16 tensors}.
         gemv(handle, x[d_in]) -> y[d_out]; gemm(handle, X[L, d_in]) -> Y[L, d_out] (both f16);
-        head(E[rows, hidden], h[hidden], row_offset) -> (best logit f32 [1], its row int64 [1])."""
+        head(E[rows, hidden], h[hidden], row_offset) -> (best logit f32 [1], its row int64 [1]).
+        A block may carry "rot_qkv", "rot_o", "rot_gate_up", "rot_down": the rotation of the activation that
+        group consumes (one per shared activation, llvq-llm/src/rotplan.rs); then rotate(rot, x f16 [.., n]) ->
+        f32 and gemv_rotated(handle, xr f32 [d_in], out=) -> f16 are used, as FusedRuntime::rotate and
+        forward_rotated are in the reference (llvq-llm/src/fused_cuda.rs:362-402)."""
         import torch
         self.cfg, self.blocks, self.embed, self.final_norm = cfg, list(blocks), embed, final_norm
         self.gemv, self.gemm, self.head, self.capacity, self.kv_int8 = gemv, gemm, head, capacity, kv_int8
+        self.rotate, self.gemv_rotated = rotate, gemv_rotated
         self.tp = tp if tp is not None and tp.world > 1 else None
         self.world = self.tp.world if self.tp else 1
         self.rank = self.tp.rank if self.tp else 0
@@ -191,6 +197,8 @@ class FusedQwen3:
             bufs = self.tp.alloc(dev, gathered) if self.tp else [torch.zeros(n, dtype=dt, device=dev) for n, dt in gathered]
             self._ctx, self._o, self._act, self._down, self._best_all = bufs
             self._gu = torch.zeros(2 * self.inter_loc, **f16)
+            # f32 staging of a rotated activation, one buffer per width
+            self._xr = {n: torch.zeros(n, dtype=torch.float32, device=dev) for n in {cfg.hidden, cfg.n_heads * hd, cfg.inter}}
             # the shard a rank computes before the gather; the full buffer itself when there is one rank
             self._ctx_loc = torch.zeros(self.h_loc * hd, **f16) if w > 1 else self._ctx
             self._o_loc = torch.zeros(cfg.hidden // w, **f16) if w > 1 else self._o
@@ -220,8 +228,12 @@ class FusedQwen3:
         x1, x2 = x.float().chunk(2, dim=-1)
         return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).half()
 
-    def _proj(self, handle, h):
-        return self.gemv(handle, h[0])[None, :] if h.shape[0] == 1 else self.gemm(handle, h.contiguous())
+    def _proj(self, blk, name, h):
+        handle, rot = blk[name], blk.get("rot_" + name)
+        if rot is None:
+            return self.gemv(handle, h[0])[None, :] if h.shape[0] == 1 else self.gemm(handle, h.contiguous())
+        xr = self.rotate(rot, h.contiguous())  # f32, one rotation for every projection of the group
+        return self.gemv_rotated(handle, xr[0])[None, :] if h.shape[0] == 1 else self.gemm(handle, xr.half())
 
     def _all(self, shard):
         return self.tp.gather_cols(shard) if self.tp else shard
@@ -252,7 +264,7 @@ class FusedQwen3:
         L, hd = x.shape[0], cfg.head_dim
         end = self.capacity if end is None else end
         h = self._rms(x, blk["ln1"])
-        qkv = self._proj(blk["qkv"], h)
+        qkv = self._proj(blk, "qkv", h)
         nq, nk = self.h_loc * hd, self.kv_loc * hd
         q = qkv[:, :nq].reshape(L, self.h_loc, hd)
         k = qkv[:, nq:nq + nk].reshape(L, self.kv_loc, hd)
@@ -269,11 +281,11 @@ class FusedQwen3:
             cache[1].index_copy_(0, pos, v.contiguous())
             k_all, v_all = cache[0][:end], cache[1][:end]
         ctx = self._all(self._attend(q, k_all, v_all, pos, end))
-        x = x + self._all(self._proj(blk["o"], ctx))
+        x = x + self._all(self._proj(blk, "o", ctx))
         h = self._rms(x, blk["ln2"])
-        gu = self._proj(blk["gate_up"], h)
+        gu = self._proj(blk, "gate_up", h)
         gated = (_silu(gu[:, :self.inter_loc].float()) * gu[:, self.inter_loc:].float()).half()
-        return x + self._all(self._proj(blk["down"], self._all(gated)))
+        return x + self._all(self._proj(blk, "down", self._all(gated)))
 
     def hidden(self, tokens, pos, end: Optional[int] = None):
         x = self.embed.index_select(0, tokens)
@@ -338,6 +350,16 @@ class FusedQwen3:
         self._tok.copy_(self.pick(self._rms(x[-1:], self.final_norm)[0]))
         self._pos += 1
 
+    def _gemv(self, blk, name, x, out):
+        """Token-step projection into a fixed buffer, through the group's rotation when it has one."""
+        rot = blk.get("rot_" + name)
+        if rot is None:
+            self.gemv(blk[name], x, out=out)
+        else:
+            xr = self._xr[x.numel()]
+            self.rotate(rot, x, out=xr)
+            self.gemv_rotated(blk[name], xr, out=out)
+
     def _fused_step(self):
         """One token: 4 fused GEMV launches and 4 small fused kernels per block (+ 4 all-gathers of row
         shards on a tensor-parallel model), then the greedy head."""
@@ -352,7 +374,7 @@ class FusedQwen3:
         for blk, cache in zip(self.blocks, self.caches):
             check(L.llvq_op_add_rmsnorm_h(p(self._x), p(delta) if delta is not None else None, p(blk["ln1"]), p(self._h),
                                           cfg.hidden, cfg.eps, st))
-            self.gemv(blk["qkv"], self._h, out=self._qkv)
+            self._gemv(blk, "qkv", self._h, self._qkv)
             check(L.llvq_op_qkv_rope_cache_h(p(self._qkv), p(blk["q_norm"]), p(blk["k_norm"]), p(self.cos), p(self.sin),
                                              p(self._pos), p(self._q), p(cache.q[0]), p(cache.s[0]), p(cache.b[0]),
                                              p(cache.q[1]), p(cache.s[1]), p(cache.b[1]), self.h_loc, self.kv_loc,
@@ -362,15 +384,15 @@ class FusedQwen3:
                                                self.kv_loc, cfg.head_dim, self.attn_splits, p(self._attn_ws), st))
             if tp:
                 tp.gather_into(0, self._ctx, self._ctx_loc)
-            self.gemv(blk["o"], self._ctx, out=self._o_loc)
+            self._gemv(blk, "o", self._ctx, self._o_loc)
             if tp:
                 tp.gather_into(1, self._o, self._o_loc)
             check(L.llvq_op_add_rmsnorm_h(p(self._x), p(self._o), p(blk["ln2"]), p(self._h), cfg.hidden, cfg.eps, st))
-            self.gemv(blk["gate_up"], self._h, out=self._gu)
+            self._gemv(blk, "gate_up", self._h, self._gu)
             check(L.llvq_op_silu_mul_h(p(self._gu), p(self._act_loc), self.inter_loc, st))
             if tp:
                 tp.gather_into(2, self._act, self._act_loc)
-            self.gemv(blk["down"], self._act, out=self._down_loc)
+            self._gemv(blk, "down", self._act, self._down_loc)
             if tp:
                 tp.gather_into(3, self._down, self._down_loc)
             delta = self._down
@@ -432,12 +454,13 @@ def tp_rows(cfg: Qwen3Config, world: int, rank: int) -> dict:
 
 def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: int = 0x51, layers: Optional[int] = None,
                     kv_int8: bool = True, fused_ops: bool = True, tp: Optional[TpGroup] = None, dense_prefill_from: int = 1024,
-                    keep_host: bool = True, device_codes: bool = False):
+                    keep_host: bool = True, device_codes: bool = False, rotations: bool = False):
     """Random-weight model of BASELINE config 2/4: LLVQ codes for every projection, f16 N(0, 0.02)
     norms and tied embedding (norm weights are 1 + N(0, 0.02) so that activations keep their scale).
     With `tp` every rank draws and uploads only its own rows of each matrix (the same matrices for any
     world size; `device_codes` draws the codes on the GPU, for models too large to draw on the host in
-    reasonable time). Prompts of `dense_prefill_from` rows or more go through a transient dense copy of each
+    reasonable time). `rotations` gives every group its incoherence rotation (one per shared activation, seeded
+    per layer and group), as every real artifact has; the BASELINE configurations are drawn without. Prompts of `dense_prefill_from` rows or more go through a transient dense copy of each
     projection and a library GEMM. Returns (model, host matrices per layer or [] when keep_host is off)."""
     import torch
     from . import synth
@@ -470,6 +493,10 @@ def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: i
                        "down": rt.upload(m["down"], tail_f16=True),
                        "ln1": f16(cfg.hidden, 1.0), "ln2": f16(cfg.hidden, 1.0),
                        "q_norm": f16(cfg.head_dim, 1.0), "k_norm": f16(cfg.head_dim, 1.0)})
+        if rotations:
+            widths = {"qkv": cfg.hidden, "o": cfg.n_heads * cfg.head_dim, "gate_up": cfg.hidden, "down": cfg.inter}
+            for gi, (name, width) in enumerate(widths.items()):
+                blocks[-1]["rot_" + name] = rt.rotation(width, synth.matrix_seed(config_id, l, 16 + gi))
     if device_codes:
         gen = torch.Generator(device=dev).manual_seed(seed)
         embed = (0.02 * torch.randn(cfg.vocab, cfg.hidden, device=dev, generator=gen)).half()
@@ -481,5 +508,6 @@ def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: i
         return rt.forward_batch_dense(proj, x) if x.shape[0] >= dense_prefill_from else rt.forward_batch(proj, x)
 
     model = FusedQwen3(cfg, blocks, embed, final_norm, capacity, gemv=rt.forward, gemm=gemm, head=kernel_head(rt.lib),
-                       kv_int8=kv_int8, ops=rt.lib if fused_ops else None, tp=tp)
+                       kv_int8=kv_int8, ops=rt.lib if fused_ops else None, tp=tp, rotate=rt.rotate,
+                       gemv_rotated=rt.forward_rotated)
     return model, mats

@@ -29,16 +29,18 @@ def _dense_model(rt, oracle, cfg, mats, fused, capacity, kv_int8):
     lin = torch.nn.functional.linear
     return FusedQwen3(cfg, blocks, fused.embed, fused.final_norm, capacity,
                       gemv=lambda w, x: lin(x.float(), w.float()).half(),
-                      gemm=lambda w, x: lin(x.float(), w.float()).half(), head=fused.head, kv_int8=kv_int8)
+                      gemm=lambda w, x: lin(x.float(), w.float()).half(), head=fused.head, kv_int8=kv_int8,
+                      rotate=fused.rotate, gemv_rotated=lambda w, xr, out=None: lin(xr, w.float()).half())
 
 
-@pytest.mark.parametrize("kv_int8", [True, False])
-def test_greedy_tokens_match_the_dense_decoded_run(rt, oracle, kv_int8):
+@pytest.mark.parametrize("kv_int8,rotations", [(True, False), (False, False), (True, True)])
+def test_greedy_tokens_match_the_dense_decoded_run(rt, oracle, kv_int8, rotations):
     import torch
     from llvq_b200.model import Qwen3Config, synthetic_model
-    cfg = Qwen3Config(hidden=24 * 10 + 16, inter=24 * 20 + 8, n_heads=4, n_kv=2, head_dim=64, layers=2, vocab=512)
+    # widths 256 (power of two: no odd mix) and 496 = 16 * 31 (the largest odd factors the rotation serves)
+    cfg = Qwen3Config(hidden=24 * 10 + 16, inter=24 * 20 + 16, n_heads=4, n_kv=2, head_dim=64, layers=2, vocab=512)
     capacity = 64
-    fused, mats = synthetic_model(rt, cfg, config_id=2, capacity=capacity, kv_int8=kv_int8)
+    fused, mats = synthetic_model(rt, cfg, config_id=2, capacity=capacity, kv_int8=kv_int8, rotations=rotations)
     dense = _dense_model(rt, oracle, cfg, mats, fused, capacity, kv_int8)
     g = np.random.default_rng(5)
     prompt = [int(t) for t in g.integers(0, cfg.vocab, 20)]  # 20 >= 16: the prefill takes the tensor-core GEMM
