@@ -269,6 +269,14 @@ int llvq_rotation_tables(const llvq_rotation* rot, uint32_t* signbits_out, float
  * launch (one CTA per activation). */
 int llvq_rotate_h(llvq_rotation* rot, const uint16_t* x_dev, float* xr_dev, int32_t batch, llvq_stream_t stream);
 
+/* The two decode-step kernels that feed a rotated projection group, with the rotation folded in (the
+ * normalised / gated activation keeps its f16 rounding, so the f32 result equals the two-kernel
+ * sequence bit for bit): x += delta; xr = Q f16(x / rms(x) * w), and xr = Q f16(silu(gate) * up). */
+int llvq_op_add_rmsnorm_rotate_h(uint16_t* x_dev, const uint16_t* delta_dev, const uint16_t* w_dev, llvq_rotation* rot,
+                                 float* xr_dev, int32_t n, float eps, llvq_stream_t stream);
+int llvq_op_silu_mul_rotate_h(const uint16_t* gate_up_dev, llvq_rotation* rot, float* xr_dev, int32_t inter,
+                              llvq_stream_t stream);
+
 /* ---- peer-memory all-gather of row shards (tensor-parallel token step) -------
  * No counterpart in the reference, which is single-GPU. A rank owns one region =
  * LLVQ_TP_FLAG_BYTES of flags followed by its gather buffers, maps the regions of its peers

@@ -66,6 +66,9 @@ _SIGNATURES = {
                                     C.POINTER(C.c_float)]),
     "llvq_rotation_tables": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "llvq_rotate_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
+    "llvq_op_add_rmsnorm_rotate_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_float,
+                                              C.c_void_p]),
+    "llvq_op_silu_mul_rotate_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "llvq_tp_region_create": (C.c_int, [C.c_int32, C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),
     "llvq_tp_region_open": (C.c_int, [C.c_int32, C.c_void_p, C.POINTER(C.c_void_p)]),
     "llvq_tp_region_close": (C.c_int, [C.c_int32, C.c_void_p]),

@@ -748,7 +748,7 @@ int llvq_matrix_dequant_h(llvq_matrix* m, uint16_t* out, llvq_stream_t stream) {
 static int rotation_upload(llvq_runtime* rt, RotationTables&& t, llvq_rotation** out) {
     if (t.k > kRotMaxOdd)
         return fail(LLVQ_ERR_UNSUPPORTED, "rotation: width %d has the odd factor %d, beyond %d", t.n, t.k, kRotMaxOdd);
-    const size_t smem = ((size_t)t.n + (size_t)t.k * t.k) * sizeof(float);
+    const size_t smem = rot_smem_floats(t.n, t.k) * sizeof(float);
     if (smem > (size_t)rt->max_smem_optin)
         return fail(LLVQ_ERR_UNSUPPORTED, "rotation: width %d needs %zu bytes of shared memory, the device gives %d", t.n, smem,
                     rt->max_smem_optin);
@@ -837,6 +837,46 @@ int llvq_rotate_h(llvq_rotation* r, const uint16_t* x, float* xr, int32_t batch,
     DeviceGuard g(r->rt->device);
     rot_apply_kernel<<<batch, kRotThreads, r->smem, (cudaStream_t)stream>>>((const __half*)x, r->d_signbits, r->d_small, xr, r->t.n,
                                                                         r->t.m, r->t.k, r->t.inv);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+static int rot_fused_prepare(llvq_rotation* r, int n, const char* who) {
+    if (r->t.n != n) return fail(LLVQ_ERR_INVALID, "%s: the rotation is %d wide, the activation %d", who, r->t.n, n);
+    static size_t configured_norm = 0, configured_silu = 0;  // raise each kernel's shared-memory limit once per size
+    if (r->smem > configured_norm) {
+        CUDA_TRY(cudaFuncSetAttribute(add_rmsnorm_rotate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)r->smem));
+        configured_norm = r->smem;
+    }
+    if (r->smem > configured_silu) {
+        CUDA_TRY(cudaFuncSetAttribute(silu_mul_rotate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)r->smem));
+        configured_silu = r->smem;
+    }
+    return LLVQ_OK;
+}
+
+int llvq_op_add_rmsnorm_rotate_h(uint16_t* x, const uint16_t* delta, const uint16_t* w, llvq_rotation* r, float* xr, int32_t n,
+                                 float eps, llvq_stream_t stream) {
+    if (!x || !w || !r || !xr || n <= 0 || (n & 1) || n > 16384)
+        return fail(LLVQ_ERR_INVALID, "op_add_rmsnorm_rotate: bad argument (n even, <= 16384)");
+    DeviceGuard g(r->rt->device);
+    int st = rot_fused_prepare(r, n, "op_add_rmsnorm_rotate");
+    if (st) return st;
+    add_rmsnorm_rotate_kernel<<<1, kRotThreads, r->smem, (cudaStream_t)stream>>>(
+        (__half*)x, (const __half*)delta, (const __half*)w, r->d_signbits, r->d_small, xr, n, r->t.m, r->t.k, r->t.inv, eps);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+int llvq_op_silu_mul_rotate_h(const uint16_t* gu, llvq_rotation* r, float* xr, int32_t inter, llvq_stream_t stream) {
+    if (!gu || !r || !xr || inter <= 0) return fail(LLVQ_ERR_INVALID, "op_silu_mul_rotate: bad argument");
+    DeviceGuard g(r->rt->device);
+    int st = rot_fused_prepare(r, inter, "op_silu_mul_rotate");
+    if (st) return st;
+    silu_mul_rotate_kernel<<<1, kRotThreads, r->smem, (cudaStream_t)stream>>>((const __half*)gu, r->d_signbits, r->d_small, xr,
+                                                                              inter, r->t.m, r->t.k, r->t.inv);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;

@@ -36,24 +36,40 @@ __device__ __forceinline__ void wht_radix(float* s, int base, int stride) {
     for (int j = 0; j < R; ++j) s[base + j * stride] = v[j];
 }
 
-// grid = rows of the batch (one CTA rotates one activation). Dynamic shared memory: n floats of the
-// vector, then k * k floats of Q_odd.
-__global__ void __launch_bounds__(kRotThreads)
-rot_apply_kernel(const __half* __restrict__ x, const unsigned int* __restrict__ signbits, const float* __restrict__ small,
-                 float* __restrict__ out, int n, int m, int k, float inv) {
-    extern __shared__ float rot_s[];
-    float* s = rot_s;
-    float* q = rot_s + n;
-    const int tid = threadIdx.x;
-    x += (size_t)blockIdx.x * n;
-    out += (size_t)blockIdx.x * n;
-    for (int i = tid; i < n; i += kRotThreads) {
-        const float v = __half2float(x[i]);
-        s[i] = ((signbits[i >> 5] >> (i & 31)) & 1u) ? -v : v;
-    }
-    for (int i = tid; i < k * k; i += kRotThreads) q[i] = small[i];
-    __syncthreads();
+// Row stride of Q_odd in shared memory: k rounded up to the compile-time bound of rot_mix (zero padded).
+__host__ __device__ inline int rot_qstride(int k) { return k <= 1 ? 1 : k <= 4 ? 4 : k <= 8 ? 8 : k <= 16 ? 16 : k <= 24 ? 24 : 32; }
 
+// Odd mix: thread j owns column j of the k x m matrix held in s: its k values go to registers once, every
+// output row is one ascending chain of fused multiply-adds over them (the zero padding adds nothing), and the
+// rows of Q_odd come from shared memory four at a time (all threads read the same address: a broadcast).
+template <int KB>
+__device__ __forceinline__ void rot_mix(const float* s, const float* q, float* __restrict__ out, int m, int k, float inv,
+                                        int tid) {
+    for (int j = tid; j < m; j += kRotThreads) {
+        float col[KB];
+#pragma unroll
+        for (int t = 0; t < KB; ++t) col[t] = t < k ? s[t * m + j] * inv : 0.0f;
+        for (int g = 0; g < k; ++g) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int t = 0; t < KB; t += 4) {
+                const float4 qq = *reinterpret_cast<const float4*>(q + g * KB + t);
+                acc = __fmaf_rn(qq.x, col[t], acc);
+                acc = __fmaf_rn(qq.y, col[t + 1], acc);
+                acc = __fmaf_rn(qq.z, col[t + 2], acc);
+                acc = __fmaf_rn(qq.w, col[t + 3], acc);
+            }
+            out[g * m + j] = acc;
+        }
+    }
+}
+
+// The transform proper, for a CTA of kRotThreads threads whose signed vector already sits in s[0, n)
+// and whose Q_odd sits in q, k rows of rot_qstride(k) floats, zero padded and 16-byte aligned (a barrier
+// after both were written is the caller's): Hadamard
+// passes, then scale and odd mix into out.
+__device__ __forceinline__ void rot_transform(float* s, const float* q, float* __restrict__ out, int n, int m, int k,
+                                              float inv, int tid) {
     for (int stride = 1; stride < m;) {
         const int r = min(8, m / stride);  // 8, or what is left of m: 4 or 2
         const int groups = n / r;
@@ -67,17 +83,119 @@ rot_apply_kernel(const __half* __restrict__ x, const unsigned int* __restrict__ 
         __syncthreads();
         stride *= r;
     }
-
     if (k == 1) {
         for (int i = tid; i < n; i += kRotThreads) out[i] = s[i] * inv;
         return;
     }
-    for (int i = tid; i < n; i += kRotThreads) {
-        const int g = i / m, j = i - g * m;
-        float acc = 0.0f;
-        for (int t = 0; t < k; ++t) acc = __fmaf_rn(q[g * k + t], s[t * m + j] * inv, acc);
-        out[i] = acc;
+    if (k <= 4) rot_mix<4>(s, q, out, m, k, inv, tid);
+    else if (k <= 8) rot_mix<8>(s, q, out, m, k, inv, tid);
+    else if (k <= 16) rot_mix<16>(s, q, out, m, k, inv, tid);
+    else if (k <= 24) rot_mix<24>(s, q, out, m, k, inv, tid);
+    else rot_mix<32>(s, q, out, m, k, inv, tid);
+}
+
+__device__ __forceinline__ void rot_stage_q(float* q, const float* __restrict__ small, int k, int tid) {
+    const int stride = rot_qstride(k);
+    for (int i = tid; i < k * stride; i += kRotThreads) {
+        const int g = i / stride, t = i - g * stride;
+        q[i] = t < k ? small[g * k + t] : 0.0f;
     }
+}
+
+// Floats of dynamic shared memory a rotation of width n needs: the vector (rounded up to a multiple of 4 so
+// that Q_odd starts 16-byte aligned) and the padded Q_odd.
+__host__ __device__ inline size_t rot_smem_floats(int n, int k) { return (size_t)((n + 3) & ~3) + (size_t)k * rot_qstride(k); }
+
+__device__ __forceinline__ float rot_signed(const unsigned int* __restrict__ signbits, int i, float v) {
+    return ((signbits[i >> 5] >> (i & 31)) & 1u) ? -v : v;
+}
+
+// grid = rows of the batch (one CTA rotates one activation). Dynamic shared memory: n floats of the
+// vector, then k * k floats of Q_odd.
+__global__ void __launch_bounds__(kRotThreads)
+rot_apply_kernel(const __half* __restrict__ x, const unsigned int* __restrict__ signbits, const float* __restrict__ small,
+                 float* __restrict__ out, int n, int m, int k, float inv) {
+    extern __shared__ float rot_s[];
+    float* s = rot_s;
+    float* q = rot_s + ((n + 3) & ~3);
+    const int tid = threadIdx.x;
+    x += (size_t)blockIdx.x * n;
+    out += (size_t)blockIdx.x * n;
+    for (int i = tid; i < n; i += kRotThreads) s[i] = rot_signed(signbits, i, __half2float(x[i]));
+    rot_stage_q(q, small, k, tid);
+    __syncthreads();
+    rot_transform(s, q, out, n, m, k, inv, tid);
+}
+
+// add + RMSNorm of the residual stream (as add_rmsnorm_kernel: x += delta in f16, y = f16(x / rms * w)) with
+// the rotation of y folded in: the normalised activation never goes to memory, its rotated f32 form does.
+// One CTA of 1024 threads; the f16 rounding of y is kept, so the result equals the two-kernel sequence bit for bit.
+__global__ void __launch_bounds__(kRotThreads)
+add_rmsnorm_rotate_kernel(__half* __restrict__ x, const __half* __restrict__ delta, const __half* __restrict__ w,
+                          const unsigned int* __restrict__ signbits, const float* __restrict__ small,
+                          float* __restrict__ out, int n, int m, int k, float inv, float eps) {
+    extern __shared__ float rot_s[];
+    __shared__ float red[32];
+    float* s = rot_s;
+    float* q = rot_s + ((n + 3) & ~3);
+    const int tid = threadIdx.x;
+    constexpr int kMaxPairs = 8;  // up to 16 384 elements
+    const int pairs = n >> 1;
+    float2 v[kMaxPairs];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kMaxPairs; ++j) {
+        const int i = tid + j * kRotThreads;
+        v[j] = make_float2(0.0f, 0.0f);
+        if (i < pairs) {
+            v[j] = __half22float2(reinterpret_cast<const __half2*>(x)[i]);
+            if (delta) {
+                const float2 d = __half22float2(reinterpret_cast<const __half2*>(delta)[i]);
+                const __half2 sum = __floats2half2_rn(v[j].x + d.x, v[j].y + d.y);  // the stream stays f16
+                reinterpret_cast<__half2*>(x)[i] = sum;
+                v[j] = __half22float2(sum);
+            }
+            ss += v[j].x * v[j].x + v[j].y * v[j].y;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    rot_stage_q(q, small, k, tid);
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) tot += red[j];
+    const float r = rsqrtf(tot / (float)n + eps);
+#pragma unroll
+    for (int j = 0; j < kMaxPairs; ++j) {
+        const int i = tid + j * kRotThreads;
+        if (i < pairs) {
+            const float2 wf = __half22float2(reinterpret_cast<const __half2*>(w)[i]);
+            const float2 y = __half22float2(__floats2half2_rn(v[j].x * r * wf.x, v[j].y * r * wf.y));
+            s[2 * i] = rot_signed(signbits, 2 * i, y.x);
+            s[2 * i + 1] = rot_signed(signbits, 2 * i + 1, y.y);
+        }
+    }
+    __syncthreads();
+    rot_transform(s, q, out, n, m, k, inv, tid);
+}
+
+// y = silu(gate) * up rounded to f16 (as silu_mul_kernel), rotated: the input of the down projection.
+__global__ void __launch_bounds__(kRotThreads)
+silu_mul_rotate_kernel(const __half* __restrict__ gu, const unsigned int* __restrict__ signbits,
+                       const float* __restrict__ small, float* __restrict__ out, int n, int m, int k, float inv) {
+    extern __shared__ float rot_s[];
+    float* s = rot_s;
+    float* q = rot_s + ((n + 3) & ~3);
+    const int tid = threadIdx.x;
+    for (int i = tid; i < n; i += kRotThreads) {
+        const float g = __half2float(gu[i]), u = __half2float(gu[n + i]);
+        s[i] = rot_signed(signbits, i, __half2float(__float2half_rn(g / (1.0f + __expf(-g)) * u)));
+    }
+    rot_stage_q(q, small, k, tid);
+    __syncthreads();
+    rot_transform(s, q, out, n, m, k, inv, tid);
 }
 
 }  // namespace llvq

@@ -371,10 +371,22 @@ class FusedQwen3:
         p = lambda t: C.c_void_p(t.data_ptr())
         self._x.copy_(self.embed.index_select(0, self._tok)[0])
         delta = None
+
+        def norm_then(blk, name, ln, delta, out):
+            """x += delta; RMSNorm; the group's projection: with a rotation, normalisation and rotation are one kernel."""
+            rot = blk.get("rot_" + name)
+            if rot is None:
+                check(L.llvq_op_add_rmsnorm_h(p(self._x), p(delta) if delta is not None else None, p(blk[ln]), p(self._h),
+                                              cfg.hidden, cfg.eps, st))
+                self.gemv(blk[name], self._h, out=out)
+            else:
+                xr = self._xr[cfg.hidden]
+                check(L.llvq_op_add_rmsnorm_rotate_h(p(self._x), p(delta) if delta is not None else None, p(blk[ln]), rot._h,
+                                                     p(xr), cfg.hidden, cfg.eps, st))
+                self.gemv_rotated(blk[name], xr, out=out)
+
         for blk, cache in zip(self.blocks, self.caches):
-            check(L.llvq_op_add_rmsnorm_h(p(self._x), p(delta) if delta is not None else None, p(blk["ln1"]), p(self._h),
-                                          cfg.hidden, cfg.eps, st))
-            self._gemv(blk, "qkv", self._h, self._qkv)
+            norm_then(blk, "qkv", "ln1", delta, self._qkv)
             check(L.llvq_op_qkv_rope_cache_h(p(self._qkv), p(blk["q_norm"]), p(blk["k_norm"]), p(self.cos), p(self.sin),
                                              p(self._pos), p(self._q), p(cache.q[0]), p(cache.s[0]), p(cache.b[0]),
                                              p(cache.q[1]), p(cache.s[1]), p(cache.b[1]), self.h_loc, self.kv_loc,
@@ -387,12 +399,17 @@ class FusedQwen3:
             self._gemv(blk, "o", self._ctx, self._o_loc)
             if tp:
                 tp.gather_into(1, self._o, self._o_loc)
-            check(L.llvq_op_add_rmsnorm_h(p(self._x), p(self._o), p(blk["ln2"]), p(self._h), cfg.hidden, cfg.eps, st))
-            self._gemv(blk, "gate_up", self._h, self._gu)
-            check(L.llvq_op_silu_mul_h(p(self._gu), p(self._act_loc), self.inter_loc, st))
-            if tp:
-                tp.gather_into(2, self._act, self._act_loc)
-            self._gemv(blk, "down", self._act, self._down_loc)
+            norm_then(blk, "gate_up", "ln2", self._o, self._gu)
+            rot_down = blk.get("rot_down")
+            if rot_down is not None and not tp:  # one rank holds the whole SwiGLU product: gate, rotate, project
+                xr = self._xr[cfg.inter]
+                check(L.llvq_op_silu_mul_rotate_h(p(self._gu), rot_down._h, p(xr), cfg.inter, st))
+                self.gemv_rotated(blk["down"], xr, out=self._down_loc)
+            else:
+                check(L.llvq_op_silu_mul_h(p(self._gu), p(self._act_loc), self.inter_loc, st))
+                if tp:
+                    tp.gather_into(2, self._act, self._act_loc)
+                self._gemv(blk, "down", self._act, self._down_loc)
             if tp:
                 tp.gather_into(3, self._down, self._down_loc)
             delta = self._down

@@ -111,3 +111,40 @@ def test_rotation_refuses_what_it_cannot_serve(rt):
         import torch
         rot = rt.rotation(64, 1)
         rt.rotate(rot, torch.zeros(63, dtype=torch.float16, device="cuda"))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [2560, 4096, 9728, 496])
+def test_fused_norm_and_gate_kernels_equal_the_two_kernel_sequence(rt, n):
+    """add+RMSNorm+rotate and SiLU*up+rotate keep the f16 rounding of the intermediate activation, so they
+    give exactly the bits of the separate kernel followed by the rotation."""
+    import ctypes as C
+    import torch
+    from llvq_b200._lib import check
+    L = rt.lib
+    rot = rt.rotation(n, 0x9000 + n)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: C.c_void_p(t.data_ptr())
+    g = torch.Generator(device="cuda").manual_seed(n)
+    for with_delta in (True, False):
+        x0 = torch.randn(n, device="cuda", generator=g).half()
+        delta = (0.3 * torch.randn(n, device="cuda", generator=g)).half()
+        w = (1.0 + 0.02 * torch.randn(n, device="cuda", generator=g)).half()
+        xa, xb = x0.clone(), x0.clone()
+        h = torch.empty(n, device="cuda", dtype=torch.float16)
+        check(L.llvq_op_add_rmsnorm_h(p(xa), p(delta) if with_delta else None, p(w), p(h), n, 1e-6, st))
+        want = rt.rotate(rot, h)
+        got = torch.empty(n, device="cuda", dtype=torch.float32)
+        check(L.llvq_op_add_rmsnorm_rotate_h(p(xb), p(delta) if with_delta else None, p(w), rot._h, p(got), n, 1e-6, st))
+        torch.cuda.synchronize()
+        assert torch.equal(got, want) and torch.equal(xa, xb)
+    gu = torch.randn(2 * n, device="cuda", generator=g).half()
+    act = torch.empty(n, device="cuda", dtype=torch.float16)
+    check(L.llvq_op_silu_mul_h(p(gu), p(act), n, st))
+    want = rt.rotate(rot, act)
+    got = torch.empty(n, device="cuda", dtype=torch.float32)
+    check(L.llvq_op_silu_mul_rotate_h(p(gu), rot._h, p(got), n, st))
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    other = rt.rotation(64, 1)
+    assert L.llvq_op_silu_mul_rotate_h(p(gu), other._h, p(got), n, st) != 0  # width mismatch is a status
