@@ -412,10 +412,9 @@ def run_tp(args):
 
 
 def _quiet_nccl():
-    """The image exports NCCL_DEBUG=VERSION, which makes NCCL print a banner on stdout ahead of the one JSON
-    line a rank-0 run must print; anything the user set beyond that (INFO, WARN) is left alone."""
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"
+    """NCCL prints a version banner on stdout at the VERSION and WARN debug levels, ahead of the one JSON line a
+    rank-0 run must print: send whatever NCCL logs to stderr instead (the level itself is left alone)."""
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
 
 
 def main():
