@@ -3,7 +3,7 @@
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
 
-Workload (`config.workload` = "qwen3-4b-layer-gemv"): BASELINE config 1 — the seven
+Workload (`config.workload` = "qwen3-4b-layer-gemv"): benchmark configuration 1 — the seven
 projections of a Qwen3-4B layer (q 4096x2560, k/v 1024x2560, o 2560x4096, gate/up
 9728x2560, down 2560x9728) at batch 1 with f16 activations, on seeded synthetic
 codes. One step = one pass over the seven projections of L distinct layers
@@ -127,7 +127,7 @@ def cpu_baseline(layers_sample=1, min_seconds=6.0, max_seconds=30.0):
 
 
 def gemm_section(rt, torch, synth, layers=3, iters=4):
-    """BASELINE config 3: batched dequant-GEMM (tcgen05) on Qwen3-8B projection shapes, B = 16 and 64.
+    """benchmark configuration 3: batched dequant-GEMM (tcgen05) on Qwen3-8B projection shapes, B = 16 and 64.
     `layers` distinct layers per pass (152 MB of codes) so no matrix is re-read warm."""
     shapes = synth.layer_shapes("qwen3-8b")
     projs = []
@@ -161,7 +161,7 @@ def gemm_section(rt, torch, synth, layers=3, iters=4):
 
 
 def decode_section(rt, torch, prompt_len=128, new_tokens=256, rotations=False):
-    """BASELINE config 2: Qwen3-4B-architecture greedy decode at batch 1 (36 layers, random LLVQ codes, f16
+    """benchmark configuration 2: Qwen3-4B-architecture greedy decode at batch 1 (36 layers, random LLVQ codes, f16
     tied embedding, int8 KV cache), 128 random prompt tokens then 256 generated; the token step is replayed
     from a CUDA graph. tok/s counts the generated tokens over the decode phase (prefill reported apart).
     With `rotations` the same model is timed a second time with an incoherence rotation in front of every
@@ -236,7 +236,7 @@ def run_reference(args):
 
 
 def run_tp_decode(args):
-    """BASELINE config 4: Qwen3-14B-architecture greedy decode, tensor-parallel over the ranks (q/k/v by heads, the
+    """benchmark configuration 4: Qwen3-14B-architecture greedy decode, tensor-parallel over the ranks (q/k/v by heads, the
     other projections and the tied head by rows, NCCL all-gathers of the row shards), int8 split-KV attention over a
     long random prompt, then `new_tokens` greedy tokens at batch 1 replayed from a CUDA graph. `value` = generated
     tokens per second over the decode phase (device-timed, max over ranks); the prefill is reported apart."""
@@ -331,7 +331,7 @@ def run_tp_decode(args):
 
 
 def run_tp(args):
-    """BASELINE config 4 (GEMV part): Qwen3-14B projections row-sharded over the ranks, f16 activations,
+    """benchmark configuration 4 (GEMV part): Qwen3-14B projections row-sharded over the ranks, f16 activations,
     NCCL all-gather of every output the next projection needs whole (4 per layer). Strong scaling:
     the job is the same 40-layer pass at every N; `value` = whole-job algorithmic GB/s."""
     import torch

@@ -472,12 +472,12 @@ def tp_rows(cfg: Qwen3Config, world: int, rank: int) -> dict:
 def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: int = 0x51, layers: Optional[int] = None,
                     kv_int8: bool = True, fused_ops: bool = True, tp: Optional[TpGroup] = None, dense_prefill_from: int = 1024,
                     keep_host: bool = True, device_codes: bool = False, rotations: bool = False):
-    """Random-weight model of BASELINE config 2/4: LLVQ codes for every projection, f16 N(0, 0.02)
+    """Random-weight model of benchmark configurations 2 and 4: LLVQ codes for every projection, f16 N(0, 0.02)
     norms and tied embedding (norm weights are 1 + N(0, 0.02) so that activations keep their scale).
     With `tp` every rank draws and uploads only its own rows of each matrix (the same matrices for any
     world size; `device_codes` draws the codes on the GPU, for models too large to draw on the host in
     reasonable time). `rotations` gives every group its incoherence rotation (one per shared activation, seeded
-    per layer and group), as every real artifact has; the BASELINE configurations are drawn without. Prompts of `dense_prefill_from` rows or more go through a transient dense copy of each
+    per layer and group), as every real artifact has; the benchmark configurationurations are drawn without. Prompts of `dense_prefill_from` rows or more go through a transient dense copy of each
     projection and a library GEMM. Returns (model, host matrices per layer or [] when keep_host is off)."""
     import torch
     from . import synth

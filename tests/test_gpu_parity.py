@@ -1,6 +1,6 @@
 """GPU parity: the CUDA path, called through the C ABI, against the CPU oracle.
 
-Bit-exact for the lattice decode; for the GEMV the tolerances BASELINE.json states:
+Bit-exact for the lattice decode; for the GEMV the tolerances the benchmark specification states:
 relative L2 <= 1e-5 with f32 activations, <= 1e-3 with f16 activations, plus the
 reference's own per-row criterion max |got - ref| / sum |w_i x_i| < 1e-5 for f32
 (llvq-cuda/src/bin/matvec.rs:63,114-120).
@@ -103,7 +103,7 @@ def test_gemv_f32_small_and_ragged(rt, oracle, d_out, d_in):
 
 
 def test_gemv_config0_up_proj_f32(rt, oracle):
-    """BASELINE config 0: W 9728 x 2560 (106 blocks + 16 tail columns), f32 activation."""
+    """benchmark configuration 0: W 9728 x 2560 (106 blocks + 16 tail columns), f32 activation."""
     from llvq_b200 import synth
     m = synth.make_matrix(9728, 2560, synth.matrix_seed(0, 0, synth.PROJ_IDS["up"]), "up")
     x = synth.make_activation(2560, synth.matrix_seed(0, 0, 5))
@@ -116,7 +116,7 @@ def test_gemv_config0_up_proj_f32(rt, oracle):
 
 
 def test_gemv_config1_layer_f16(rt, oracle):
-    """BASELINE config 1: the seven projections of one Qwen3-4B layer, f16 activations and results."""
+    """benchmark configuration 1: the seven projections of one Qwen3-4B layer, f16 activations and results."""
     from llvq_b200 import synth
     layer = synth.make_layer("qwen3-4b", 1, 0)
     for name, m in layer.items():
@@ -280,7 +280,7 @@ def test_batched_gemm_ragged_shapes(rt, oracle, d_out, d_in, batch):
 
 
 def test_batched_gemm_config3_qwen3_8b_shapes(rt, oracle):
-    """BASELINE config 3: tree-verify batches of 16 and 64 on Qwen3-8B shapes (k_proj and a slice of gate_proj)."""
+    """benchmark configuration 3: tree-verify batches of 16 and 64 on Qwen3-8B shapes (k_proj and a slice of gate_proj)."""
     torch = _torch()
     from llvq_b200 import synth
     for d_out, d_in in ((1024, 4096), (1536, 4096), (512, 12288)):
