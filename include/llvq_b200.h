@@ -244,6 +244,50 @@ int llvq_op_lm_head_argmax_h(const uint16_t* embed_dev, const uint16_t* h_dev, i
  * transient operand for long-prompt GEMMs. An index outside the ball raises the runtime's range flag. */
 int llvq_matrix_dequant_h(llvq_matrix* m, uint16_t* out_dev, llvq_stream_t stream);
 
+/* ---- model container ----------------------------------------------------------
+ * Reader of the reference's file format, "LVQ1".."LVQ4" (llvq-artifact/src/format.rs:301-382 for a
+ * matrix record, :588-619 for the header, src/sealed.rs:224-343 for raw tensors and blobs). The file is
+ * mapped read-only; a matrix's code stream is used where it lies (47-bit index + 1 gain bit per block
+ * is the 6-byte record the kernels read), so llvq_archive_matrix_desc + llvq_matrix_upload load a
+ * projection without decoding or re-packing anything. Needs no GPU. A version-4 file whose codebook
+ * fingerprint is not 0x338f420f11866319 is refused; every length field is checked against the bytes
+ * present. Pointers handed out stay valid until llvq_archive_close. */
+typedef struct llvq_archive llvq_archive;
+typedef struct {
+    const char* name;
+    int32_t d_out, d_in, shell_cap, n_centroids, index_bits, gain_bits, has_rotation;
+    uint64_t rotation_seed;
+    const double* centroids;  /* n_centroids */
+    const double* row_scales; /* d_out */
+    const float* tail;        /* d_out * (d_in % 24), as stored */
+    const uint8_t* stream;    /* (index_bits + gain_bits) bits per block, MSB first, row-major blocks */
+    uint64_t stream_bytes;
+} llvq_archive_matrix_info;
+typedef struct {
+    const char* name;
+    int32_t tag; /* 0: f16 values (data = 2 bytes each); 1: group-affine quantised (w = scale q + bias) */
+    int32_t rank, bits, group;
+    const uint64_t* dims;
+    const uint8_t* data; /* unaligned: copy before reinterpreting */
+    uint64_t data_bytes;
+    const uint8_t* scales; /* tag 1: `groups` f16 values each */
+    const uint8_t* biases;
+    uint64_t groups;
+} llvq_archive_raw_info;
+
+int llvq_archive_open(const char* path, llvq_archive** out);
+/* The same over bytes the caller keeps alive until close. */
+int llvq_archive_open_memory(const void* data, size_t bytes, llvq_archive** out);
+void llvq_archive_close(llvq_archive* a);
+int llvq_archive_counts(const llvq_archive* a, int32_t* version, int32_t* n_matrices, int32_t* n_raw, int32_t* n_blobs,
+                        int32_t* has_fingerprint, uint64_t* fingerprint);
+int llvq_archive_matrix(const llvq_archive* a, int32_t i, llvq_archive_matrix_info* out);
+/* Fill an upload descriptor that points into the archive; refuses records the kernels do not serve
+ * (shell cap other than 12, other than 2 gain centroids) with LLVQ_ERR_UNSUPPORTED. */
+int llvq_archive_matrix_desc(const llvq_archive* a, int32_t i, int32_t tail_mode, llvq_matrix_desc* out);
+int llvq_archive_raw(const llvq_archive* a, int32_t i, llvq_archive_raw_info* out);
+int llvq_archive_blob(const llvq_archive* a, int32_t i, const char** name, const uint8_t** data, uint64_t* bytes);
+
 /* ---- activation rotation ------------------------------------------------------
  * Every sealed matrix was quantised in a rotated basis, Q = (Q_odd (x) H_m) D built from its
  * rotation seed (llvq-quant/src/rotation.rs:51-68); the runtime rotates the activation once per

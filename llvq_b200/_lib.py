@@ -25,6 +25,19 @@ class HostCall(C.Structure):
     _fields_ = [("m", C.c_void_p), ("x_host", C.c_void_p), ("y_host", C.c_void_p)]
 
 
+class ArchiveMatrixInfo(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("d_out", C.c_int32), ("d_in", C.c_int32), ("shell_cap", C.c_int32),
+                ("n_centroids", C.c_int32), ("index_bits", C.c_int32), ("gain_bits", C.c_int32), ("has_rotation", C.c_int32),
+                ("rotation_seed", C.c_uint64), ("centroids", C.POINTER(C.c_double)), ("row_scales", C.POINTER(C.c_double)),
+                ("tail", C.POINTER(C.c_float)), ("stream", C.POINTER(C.c_uint8)), ("stream_bytes", C.c_uint64)]
+
+
+class ArchiveRawInfo(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("tag", C.c_int32), ("rank", C.c_int32), ("bits", C.c_int32), ("group", C.c_int32),
+                ("dims", C.POINTER(C.c_uint64)), ("data", C.POINTER(C.c_uint8)), ("data_bytes", C.c_uint64),
+                ("scales", C.POINTER(C.c_uint8)), ("biases", C.POINTER(C.c_uint8)), ("groups", C.c_uint64)]
+
+
 class LlvqError(RuntimeError):
     def __init__(self, status: int, message: str):
         super().__init__(f"llvq status {status}: {message}")
@@ -58,6 +71,15 @@ _SIGNATURES = {
     "llvq_op_qkv_rope_cache_h": (C.c_int, [C.c_void_p] * 13 + [C.c_int32] * 3 + [C.c_float, C.c_void_p]),
     "llvq_matrix_set_splits": (C.c_int, [C.c_void_p, C.c_int32]),
     "llvq_matrix_get_splits": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
+    "llvq_archive_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "llvq_archive_open_memory": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "llvq_archive_close": (None, [C.c_void_p]),
+    "llvq_archive_counts": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_int32)] * 5 + [C.POINTER(C.c_uint64)]),
+    "llvq_archive_matrix": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(ArchiveMatrixInfo)]),
+    "llvq_archive_matrix_desc": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(MatrixDesc)]),
+    "llvq_archive_raw": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(ArchiveRawInfo)]),
+    "llvq_archive_blob": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_char_p), C.POINTER(C.POINTER(C.c_uint8)),
+                                   C.POINTER(C.c_uint64)]),
     "llvq_rotation_create": (C.c_int, [C.c_void_p, C.c_int32, C.c_uint64, C.POINTER(C.c_void_p)]),
     "llvq_rotation_create_from_tables": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
     "llvq_rotation_build_tables": (C.c_int, [C.c_int32, C.c_uint64, C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]),

@@ -17,6 +17,7 @@
 #include "codebook.h"
 #include "decode_ops.cuh"
 #include "dense_ops.cuh"
+#include "archive.h"
 #include "rotate.cuh"
 #include "rotation.h"
 #include "tp_exchange.cuh"
@@ -327,6 +328,10 @@ int gemv_host(llvq_matrix* m, const XT* xh, YT* yh, llvq_stream_t stream) {
 }
 
 }  // namespace
+
+struct llvq_archive {
+    Archive a;
+};
 
 struct llvq_rotation {
     llvq_runtime* rt = nullptr;
@@ -740,6 +745,125 @@ int llvq_matrix_dequant_h(llvq_matrix* m, uint16_t* out, llvq_stream_t stream) {
     dequant_dense_kernel<<<(unsigned int)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(rt->F, rt->T, mv, (__half*)out, rt->d_err);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+// ---- model container ------------------------------------------------------------------
+
+namespace {
+// points of the ball of shells 2..cap, from the class enumeration (built once, on the host)
+const uint64_t* ball_sizes() {
+    static uint64_t ball[16] = {0};
+    static bool ready = false;
+    if (!ready) {
+        Codebook cb;
+        for (const ClassInfo& c : cb.classes)
+            for (int cap = c.shell; cap <= 13; ++cap) ball[cap] += c.card;
+        ready = true;
+    }
+    return ball;
+}
+
+int archive_finish(std::unique_ptr<llvq_archive>& h, const std::string& err, llvq_archive** out) {
+    if (!err.empty()) return fail(LLVQ_ERR_INVALID, "archive: %s", err.c_str());
+    *out = h.release();
+    return LLVQ_OK;
+}
+}  // namespace
+
+int llvq_archive_open(const char* path, llvq_archive** out) {
+    if (!path || !out) return fail(LLVQ_ERR_INVALID, "archive_open: null argument");
+    std::unique_ptr<llvq_archive> h(new llvq_archive);
+    const std::string err = open_archive(path, LLVQ_PUBLISHED_FINGERPRINT, ball_sizes(), h->a);
+    return archive_finish(h, err, out);
+}
+
+int llvq_archive_open_memory(const void* data, size_t bytes, llvq_archive** out) {
+    if (!data || !out) return fail(LLVQ_ERR_INVALID, "archive_open_memory: null argument");
+    std::unique_ptr<llvq_archive> h(new llvq_archive);
+    const std::string err = parse_archive((const unsigned char*)data, bytes, LLVQ_PUBLISHED_FINGERPRINT, ball_sizes(), h->a);
+    return archive_finish(h, err, out);
+}
+
+void llvq_archive_close(llvq_archive* a) { delete a; }
+
+int llvq_archive_counts(const llvq_archive* a, int32_t* version, int32_t* n_matrices, int32_t* n_raw, int32_t* n_blobs,
+                        int32_t* has_fingerprint, uint64_t* fingerprint) {
+    if (!a) return fail(LLVQ_ERR_INVALID, "archive_counts: null archive");
+    if (version) *version = a->a.version;
+    if (n_matrices) *n_matrices = (int32_t)a->a.matrices.size();
+    if (n_raw) *n_raw = (int32_t)a->a.raws.size();
+    if (n_blobs) *n_blobs = (int32_t)a->a.blobs.size();
+    if (has_fingerprint) *has_fingerprint = a->a.has_fingerprint ? 1 : 0;
+    if (fingerprint) *fingerprint = a->a.fingerprint;
+    return LLVQ_OK;
+}
+
+int llvq_archive_matrix(const llvq_archive* a, int32_t i, llvq_archive_matrix_info* out) {
+    if (!a || !out) return fail(LLVQ_ERR_INVALID, "archive_matrix: null argument");
+    if (i < 0 || (size_t)i >= a->a.matrices.size()) return fail(LLVQ_ERR_INVALID, "archive_matrix: no matrix %d", i);
+    const ArchiveMatrix& m = a->a.matrices[i];
+    out->name = m.name.c_str();
+    out->d_out = m.d_out;
+    out->d_in = m.d_in;
+    out->shell_cap = m.shell_cap;
+    out->n_centroids = m.n_centroids;
+    out->index_bits = m.index_bits;
+    out->gain_bits = m.gain_bits;
+    out->has_rotation = m.has_rotation ? 1 : 0;
+    out->rotation_seed = m.rotation_seed;
+    out->centroids = m.centroids.data();
+    out->row_scales = m.row_scales.data();
+    out->tail = m.tail.data();
+    out->stream = m.stream;
+    out->stream_bytes = m.stream_bytes;
+    return LLVQ_OK;
+}
+
+int llvq_archive_matrix_desc(const llvq_archive* a, int32_t i, int32_t tail_mode, llvq_matrix_desc* out) {
+    if (!a || !out) return fail(LLVQ_ERR_INVALID, "archive_matrix_desc: null argument");
+    if (i < 0 || (size_t)i >= a->a.matrices.size()) return fail(LLVQ_ERR_INVALID, "archive_matrix_desc: no matrix %d", i);
+    const ArchiveMatrix& m = a->a.matrices[i];
+    // what the kernels read in place: 47-bit index + 1 gain bit = 6 bytes per block
+    if (m.shell_cap != 12 || m.n_centroids != 2)
+        return fail(LLVQ_ERR_UNSUPPORTED, "%s: shell cap %d with %d gain centroids; the kernels serve cap 12 with 2 (48-bit records)",
+                    m.name.c_str(), m.shell_cap, m.n_centroids);
+    out->d_out = m.d_out;
+    out->d_in = m.d_in;
+    out->shell_cap = m.shell_cap;
+    out->tail_mode = tail_mode;
+    out->codes = m.stream;
+    out->centroids = m.centroids.data();
+    out->row_scales = m.row_scales.data();
+    out->tail = m.tail.data();
+    return LLVQ_OK;
+}
+
+int llvq_archive_raw(const llvq_archive* a, int32_t i, llvq_archive_raw_info* out) {
+    if (!a || !out) return fail(LLVQ_ERR_INVALID, "archive_raw: null argument");
+    if (i < 0 || (size_t)i >= a->a.raws.size()) return fail(LLVQ_ERR_INVALID, "archive_raw: no raw tensor %d", i);
+    const ArchiveRaw& t = a->a.raws[i];
+    out->name = t.name.c_str();
+    out->tag = t.tag;
+    out->rank = (int32_t)t.dims.size();
+    out->bits = t.bits;
+    out->group = t.group;
+    out->dims = t.dims.data();
+    out->data = t.data;
+    out->data_bytes = t.data_bytes;
+    out->scales = t.scales;
+    out->biases = t.biases;
+    out->groups = t.groups;
+    return LLVQ_OK;
+}
+
+int llvq_archive_blob(const llvq_archive* a, int32_t i, const char** name, const uint8_t** data, uint64_t* bytes) {
+    if (!a) return fail(LLVQ_ERR_INVALID, "archive_blob: null archive");
+    if (i < 0 || (size_t)i >= a->a.blobs.size()) return fail(LLVQ_ERR_INVALID, "archive_blob: no blob %d", i);
+    const ArchiveBlob& b = a->a.blobs[i];
+    if (name) *name = b.name.c_str();
+    if (data) *data = b.data;
+    if (bytes) *bytes = b.bytes;
     return LLVQ_OK;
 }
 
