@@ -528,3 +528,64 @@ def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: i
                        kv_int8=kv_int8, ops=rt.lib if fused_ops else None, tp=tp, rotate=rt.rotate,
                        gemv_rotated=rt.forward_rotated)
     return model, mats
+
+
+def load_archive_model(rt, ar, capacity: int, kv_int8: bool = True, fused_ops: bool = True, dense_prefill_from: int = 1024):
+    """A decode loop over a sealed container (`llvq_b200.archive.LvqArchive`): what the reference's fusedrun does
+    with a `.llvq` file (llvq-llm/src/bin/fusedrun.rs, fused::load at llvq-llm/src/fused.rs:1147). The projections
+    `model.layers.{i}.self_attn.{q,k,v,o}_proj.weight` / `mlp.{gate,up,down}_proj.weight` are uploaded straight
+    from the file (q|k|v and gate|up as row groups), every group gets the rotation its records name (the records
+    of a group must agree on it, as they consume one activation), the raw tensors give the tied f16 embedding and
+    the norms, and `config.json` the shape. Quantised embeddings (tag 1) are not served by this loader."""
+    import ctypes as C
+    import json
+    import torch
+    from ._lib import MatrixDesc, check
+    from .runtime import FusedProj
+    blobs = dict(ar.blob(i) for i in range(ar.n_blobs))
+    if "config.json" not in blobs:
+        raise ValueError("the container carries no config.json: not a sealed, self-contained file")
+    c = json.loads(blobs["config.json"])
+    hd = c.get("head_dim") or c["hidden_size"] // c["num_attention_heads"]
+    cfg = Qwen3Config(c["hidden_size"], c["intermediate_size"], c["num_attention_heads"], c["num_key_value_heads"], hd,
+                      c["num_hidden_layers"], c["vocab_size"], float(c.get("rope_theta", 1e6)), float(c.get("rms_norm_eps", 1e-6)))
+    dev = torch.device("cuda", rt.device)
+    index = {ar.matrix(i)["name"]: i for i in range(ar.n_matrices)}
+    raws = {}
+    for i in range(ar.n_raw):
+        t = ar.raw(i)
+        if t["tag"] != 0:
+            raise ValueError(f"{t['name']}: stored group-affine quantised; this loader takes f16 raw tensors")
+        raws[t["name"]] = torch.from_numpy(t["data"].astype(np.float16)).to(dev)
+
+    def group(layer: int, names):
+        ids = [index[f"model.layers.{layer}.{n}.weight"] for n in names]
+        descs = (MatrixDesc * len(ids))()
+        for k, i in enumerate(ids):
+            check(ar.lib.llvq_archive_matrix_desc(ar._h, i, 1, C.byref(descs[k])))
+        h = C.c_void_p()
+        check(rt.lib.llvq_matrix_upload_group(rt._h, descs, len(ids), C.byref(h)))
+        seeds = {ar.matrix(i)["rotation_seed"] for i in ids}
+        if len(seeds) != 1:
+            raise ValueError(f"layer {layer} {names}: the records of one group name different rotations {seeds}")
+        seed = seeds.pop()
+        proj = FusedProj(rt, h.value, "|".join(names), [descs[k].d_out for k in range(len(ids))])
+        return proj, (rt.rotation(descs[0].d_in, seed) if seed is not None else None)
+
+    blocks = []
+    for l in range(cfg.layers):
+        blk = {"ln1": raws[f"model.layers.{l}.input_layernorm.weight"], "ln2": raws[f"model.layers.{l}.post_attention_layernorm.weight"],
+               "q_norm": raws[f"model.layers.{l}.self_attn.q_norm.weight"], "k_norm": raws[f"model.layers.{l}.self_attn.k_norm.weight"]}
+        for key, names in (("qkv", ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"]), ("o", ["self_attn.o_proj"]),
+                           ("gate_up", ["mlp.gate_proj", "mlp.up_proj"]), ("down", ["mlp.down_proj"])):
+            blk[key], rot = group(l, names)
+            if rot is not None:
+                blk["rot_" + key] = rot
+        blocks.append(blk)
+
+    def gemm(proj, x):
+        return rt.forward_batch_dense(proj, x) if x.shape[0] >= dense_prefill_from else rt.forward_batch(proj, x)
+
+    return FusedQwen3(cfg, blocks, raws["model.embed_tokens.weight"].contiguous(), raws["model.norm.weight"], capacity,
+                      gemv=rt.forward, gemm=gemm, head=kernel_head(rt.lib), kv_int8=kv_int8, ops=rt.lib if fused_ops else None,
+                      rotate=rt.rotate, gemv_rotated=rt.forward_rotated)

@@ -123,3 +123,67 @@ def test_projection_uploaded_from_the_file_equals_the_direct_upload(rt, oracle, 
     tail16 = m.tail.astype(np.float16).astype(np.float32)
     ref = oracle.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales, tail16, x.cpu().numpy().astype(np.float64))
     assert np.linalg.norm(y.cpu().numpy() - ref) / np.linalg.norm(ref) <= 1e-3
+
+
+@pytest.mark.gpu
+def test_decode_loop_from_a_sealed_file_matches_the_loop_built_from_the_same_arrays(rt, tmp_path):
+    """file -> tokens: write a small self-contained model with the format-restating writer (rotation seed per
+    group, f16 embedding and norms, config.json), load it with load_archive_model, and compare the greedy tokens
+    with the loop assembled directly from the same matrices."""
+    import json
+    import torch
+    from llvq_b200 import synth
+    from llvq_b200.archive import LvqArchive
+    from llvq_b200.model import FusedQwen3, Qwen3Config, kernel_head, load_archive_model
+    cfg = Qwen3Config(hidden=256, inter=496, n_heads=4, n_kv=2, head_dim=64, layers=2, vocab=384)
+    g = np.random.default_rng(3)
+    f16 = lambda *s, base=0.0: (base + 0.02 * g.standard_normal(s)).astype(np.float16)
+    shp = {"self_attn.q_proj": (256, 256), "self_attn.k_proj": (128, 256), "self_attn.v_proj": (128, 256),
+           "self_attn.o_proj": (256, 256), "mlp.gate_proj": (496, 256), "mlp.up_proj": (496, 256), "mlp.down_proj": (256, 496)}
+    groups = {"qkv": ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"], "o": ["self_attn.o_proj"],
+              "gate_up": ["mlp.gate_proj", "mlp.up_proj"], "down": ["mlp.down_proj"]}
+    recs, raws, host = [], [], []
+    emb, final = f16(cfg.vocab, cfg.hidden), f16(cfg.hidden, base=1.0)
+    raws += [W.raw_f16("model.embed_tokens.weight", emb), W.raw_f16("model.norm.weight", final)]
+    for l in range(cfg.layers):
+        layer = {"mats": {}, "seeds": {}}
+        for gi, (key, names) in enumerate(groups.items()):
+            seed = 0x5000 + 16 * l + gi
+            layer["seeds"][key] = seed
+            for n in names:
+                m = synth.make_matrix(*shp[n], 900 + 10 * l + len(layer["mats"]))
+                layer["mats"][n] = m
+                idx, gain = synth.unpack_codes(m.codes)
+                recs.append(W.matrix_record(f"model.layers.{l}.{n}.weight", m.d_out, m.d_in, idx, gain, m.centroids, m.row_scales,
+                                            m.tail, rotation_seed=seed))
+        for nm, arr in (("input_layernorm", f16(cfg.hidden, base=1.0)), ("post_attention_layernorm", f16(cfg.hidden, base=1.0)),
+                        ("self_attn.q_norm", f16(64, base=1.0)), ("self_attn.k_norm", f16(64, base=1.0))):
+            layer[nm] = arr
+            raws.append(W.raw_f16(f"model.layers.{l}.{nm}.weight", arr))
+        host.append(layer)
+    config = {"hidden_size": 256, "intermediate_size": 496, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+              "num_hidden_layers": 2, "vocab_size": 384, "rope_theta": 1e6, "rms_norm_eps": 1e-6}
+    path = os.path.join(tmp_path, "tiny.llvq")
+    with open(path, "wb") as f:
+        f.write(W.container(4, recs, raws, [W.blob("config.json", json.dumps(config).encode()), W.blob("tokenizer.json", b"{}")]))
+    prompt = [int(t) for t in g.integers(0, cfg.vocab, 24)]
+    with LvqArchive(path=path) as ar:
+        model = load_archive_model(rt, ar, capacity=64)
+        assert model.cfg == cfg and "rot_down" in model.blocks[0]
+        got = model.generate(prompt, 16)
+        graphed = model.generate(prompt, 16, use_graph=True)
+    dev = torch.device("cuda")
+    t = lambda a: torch.from_numpy(a).to(dev)
+    blocks = []
+    for layer in host:
+        blk = {"ln1": t(layer["input_layernorm"]), "ln2": t(layer["post_attention_layernorm"]),
+               "q_norm": t(layer["self_attn.q_norm"]), "k_norm": t(layer["self_attn.k_norm"])}
+        for key, names in groups.items():
+            ms = [layer["mats"][n] for n in names]
+            blk[key] = rt.upload_group(ms, tail_f16=True) if len(ms) > 1 else rt.upload(ms[0], tail_f16=True)
+            blk["rot_" + key] = rt.rotation(ms[0].d_in, layer["seeds"][key])
+        blocks.append(blk)
+    direct = FusedQwen3(cfg, blocks, t(emb), t(final), 64, gemv=rt.forward, gemm=rt.forward_batch, head=kernel_head(rt.lib),
+                        ops=rt.lib, rotate=rt.rotate, gemv_rotated=rt.forward_rotated)
+    want = direct.generate(prompt, 16)
+    assert got == want and graphed == want and len(set(want)) >= 1
