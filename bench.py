@@ -575,11 +575,13 @@ def main():
     }
     for p in projs:
         p.free()
-    if not args.no_gemm:
+    # side measurements of the single-GPU configurations (3: batched GEMM, 2: greedy decode) and the CPU baseline
+    # belong to the N = 1 line; a multi-rank run reports the replicated GEMV pass only
+    if not args.no_gemm and world == 1:
         out["gemm"] = gemm_section(rt, torch, synth)
-    if not args.no_decode:
+    if not args.no_decode and world == 1:
         out["decode"] = decode_section(rt, torch, rotations=args.rotations)
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:
         cb, _ = cpu_baseline()
         out["cpu_baseline"] = cb
     print(json.dumps(out))
