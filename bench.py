@@ -160,7 +160,7 @@ def gemm_section(rt, torch, synth, layers=3, iters=4):
     return out
 
 
-def decode_section(rt, torch, prompt_len=128, new_tokens=256, rotations=False):
+def decode_section(rt, torch, prompt_len=128, new_tokens=256, rotations=False, embed_q8=False):
     """benchmark configuration 2: Qwen3-4B-architecture greedy decode at batch 1 (36 layers, random LLVQ codes, f16
     tied embedding, int8 KV cache), 128 random prompt tokens then 256 generated; the token step is replayed
     from a CUDA graph. tok/s counts the generated tokens over the decode phase (prefill reported apart).
@@ -199,6 +199,13 @@ def decode_section(rt, torch, prompt_len=128, new_tokens=256, rotations=False):
     res = {"workload": "qwen3-4b-greedy-decode", "prompt_tokens": prompt_len, "new_tokens": new_tokens, "kv_cache": "int8 g64",
            "graph": True, "setup_s": setup}
     res.update(timed())
+    if embed_q8:  # the same model with the tied embedding carried as int8 g64 (the reference's embedq payload)
+        from llvq_b200.model import Q8Embedding
+        f16_emb, f16_head = model.emb, model.emb_head
+        model.emb = Q8Embedding.quantize(rt.lib, model.emb.dense())
+        model.emb_head = model.emb
+        res["with_int8_head"] = timed()
+        model.emb, model.emb_head = f16_emb, f16_head
     if rotations:
         for blk, rots in zip(model.blocks, held):
             blk.update(rots)
@@ -437,6 +444,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemm", action="store_true", help="skip the batched-GEMM (config 3) side measurement")
     ap.add_argument("--no-decode", action="store_true", help="skip the greedy-decode (config 2) side measurement")
+    ap.add_argument("--embed-q8", action="store_true",
+                    help="time the config-2 decode a second time with the tied embedding / head carried as int8 g64")
     ap.add_argument("--rotations", action="store_true",
                     help="time the config-2 decode a second time with an activation rotation per projection group")
     ap.add_argument("--no-groups", action="store_true",
@@ -580,7 +589,7 @@ def main():
     if not args.no_gemm and world == 1:
         out["gemm"] = gemm_section(rt, torch, synth)
     if not args.no_decode and world == 1:
-        out["decode"] = decode_section(rt, torch, rotations=args.rotations)
+        out["decode"] = decode_section(rt, torch, rotations=args.rotations, embed_q8=args.embed_q8)
     if not args.no_cpu_baseline and world == 1:
         cb, _ = cpu_baseline()
         out["cpu_baseline"] = cb

@@ -239,6 +239,17 @@ int llvq_op_lm_head_argmax_h(const uint16_t* embed_dev, const uint16_t* h_dev, i
                              int64_t row_offset, void* scratch_dev, float* val_out_dev, int64_t* idx_out_dev,
                              llvq_stream_t stream);
 
+/* The same head over an embedding carried as int8 g64 (w = scale * q + bias per group of 64 along the row,
+ * f16 scale and bias, f32 multiply then add, not contracted): tv_q8_h of llvq-llm/kernels/emb_q8.cu:80-106,
+ * with the argmax taken on the device. hidden: a multiple of 64 up to 8192; scales/biases [rows, hidden / 64]. */
+int llvq_op_lm_head_argmax_q8_h(const uint8_t* wq_dev, const uint16_t* scales_dev, const uint16_t* biases_dev,
+                                const uint16_t* h_dev, int32_t rows, int32_t hidden, int64_t row_offset, void* scratch_dev,
+                                float* val_out_dev, int64_t* idx_out_dev, llvq_stream_t stream);
+/* Token ids (int64, device) -> dequantised f16 rows [n_tokens, hidden]: emb_q8_gather (emb_q8.cu:53-66). */
+int llvq_op_embed_gather_q8_h(const uint8_t* wq_dev, const uint16_t* scales_dev, const uint16_t* biases_dev,
+                              const int64_t* ids_dev, int32_t n_tokens, int32_t rows, int32_t hidden, uint16_t* y_dev,
+                              llvq_stream_t stream);
+
 /* Write the matrix as dense f16 [d_out, d_in] (row-major, out_dev caller-owned): what the
  * reference's dense-decoded run keeps resident (llvq-llm/src/bin/fusedrun.rs:263-278), here a
  * transient operand for long-prompt GEMMs. An index outside the ball raises the runtime's range flag. */

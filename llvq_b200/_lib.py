@@ -103,6 +103,8 @@ _SIGNATURES = {
     "llvq_tp_poll_error": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
     "llvq_op_lm_head_argmax_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p,
                                           C.c_void_p, C.c_void_p]),
+    "llvq_op_lm_head_argmax_q8_h": (C.c_int, [C.c_void_p] * 4 + [C.c_int32, C.c_int32, C.c_int64] + [C.c_void_p] * 4),
+    "llvq_op_embed_gather_q8_h": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p, C.c_void_p]),
     "llvq_matrix_dequant_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "llvq_op_attn_decode_int8_h": (C.c_int, [C.c_void_p] * 9 + [C.c_int32] * 4 + [C.c_void_p, C.c_void_p]),
     "llvq_op_silu_mul_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),

@@ -735,6 +735,42 @@ int llvq_op_lm_head_argmax_h(const uint16_t* embed, const uint16_t* h, int32_t r
     return LLVQ_OK;
 }
 
+int llvq_op_lm_head_argmax_q8_h(const uint8_t* wq, const uint16_t* scales, const uint16_t* biases, const uint16_t* h, int32_t rows,
+                                int32_t hidden, int64_t row_offset, void* scratch, float* val_out, int64_t* idx_out,
+                                llvq_stream_t stream) {
+    if (!wq || !scales || !biases || !h || !scratch || !val_out || !idx_out || rows <= 0)
+        return fail(LLVQ_ERR_INVALID, "op_lm_head_argmax_q8: bad argument");
+    if (hidden <= 0 || hidden % 64 || hidden > kHeadMaxHidden)
+        return fail(LLVQ_ERR_UNSUPPORTED, "op_lm_head_argmax_q8: hidden %d (a multiple of 64 up to %d)", hidden, kHeadMaxHidden);
+    if ((uintptr_t)wq & 15u) return fail(LLVQ_ERR_INVALID, "op_lm_head_argmax_q8: the codes must be 16-byte aligned");
+    int sms = 0, dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int grid = sms * 4;
+    const int want = (rows + kHeadThreads / 32 - 1) / (kHeadThreads / 32);
+    if (grid > want) grid = want;
+    if (grid > kHeadMaxGrid) grid = kHeadMaxGrid;
+    cudaStream_t s = (cudaStream_t)stream;
+    lm_head_argmax_q8_kernel<<<grid, kHeadThreads, 0, s>>>(wq, (const __half*)scales, (const __half*)biases, (const __half*)h, rows,
+                                                           hidden, (HeadBest*)scratch);
+    lm_head_pick_kernel<<<1, kHeadMaxGrid, 0, s>>>((const HeadBest*)scratch, grid, (long long)row_offset, val_out, (long long*)idx_out);
+    g_launches += 2;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+int llvq_op_embed_gather_q8_h(const uint8_t* wq, const uint16_t* scales, const uint16_t* biases, const int64_t* ids, int32_t n_tokens,
+                              int32_t rows, int32_t hidden, uint16_t* y, llvq_stream_t stream) {
+    if (!wq || !scales || !biases || !ids || !y || n_tokens < 0 || rows <= 0 || hidden <= 0)
+        return fail(LLVQ_ERR_INVALID, "op_embed_gather_q8: bad argument");
+    if (n_tokens == 0) return LLVQ_OK;
+    embed_gather_q8_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>(wq, (const __half*)scales, (const __half*)biases,
+                                                                     (const long long*)ids, (__half*)y, hidden, rows);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
 int llvq_matrix_dequant_h(llvq_matrix* m, uint16_t* out, llvq_stream_t stream) {
     if (!m || !out) return fail(LLVQ_ERR_INVALID, "matrix_dequant_h: null argument");
     llvq_runtime* rt = m->rt;

@@ -107,6 +107,74 @@ lm_head_argmax_kernel(const __half* __restrict__ embed, const __half* __restrict
     }
 }
 
+// ---- the tied embedding carried as int8 g64 (the reference's emb_q8.cu: w = scale * q + bias per group
+// of 64 along the row, f16 scale and bias, one f32 multiply and one f32 add, never contracted) ----
+
+__device__ __forceinline__ float q8_deq(unsigned int q, float s, float b) { return __fadd_rn(__fmul_rn(s, (float)q), b); }
+
+// Greedy head over the int8 embedding: one row per warp and step, 16 codes (one 16-byte load, inside one
+// group) per lane and step, f32 accumulation in a fixed order, argmax with the lowest row on ties.
+// wq: [rows, hidden] u8, hidden % 16 == 0; scales / biases: [rows, hidden / 64] f16 (hidden % 64 == 0).
+__global__ void __launch_bounds__(kHeadThreads)
+lm_head_argmax_q8_kernel(const unsigned char* __restrict__ wq, const __half* __restrict__ scales,
+                         const __half* __restrict__ biases, const __half* __restrict__ h, int rows, int hidden,
+                         HeadBest* __restrict__ partial) {
+    __shared__ __align__(16) float hs[kHeadMaxHidden];
+    __shared__ HeadBest red[kHeadThreads / 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < hidden; i += kHeadThreads) hs[i] = __half2float(h[i]);
+    __syncthreads();
+    const int vec = hidden / 16, gpr = hidden / 64;
+    float best = -INFINITY;
+    int best_row = 0x7fffffff;
+    for (int r = blockIdx.x * (kHeadThreads / 32) + warp; r < rows; r += gridDim.x * (kHeadThreads / 32)) {
+        const uint4* src = reinterpret_cast<const uint4*>(wq + (size_t)r * hidden);
+        float acc = 0.0f;
+#pragma unroll 2
+        for (int i = lane; i < vec; i += 32) {
+            const uint4 e = __ldg(src + i);
+            const int g = i >> 2;  // 16 codes per step, 64 per group
+            const float s = __half2float(scales[(size_t)r * gpr + g]), b = __half2float(biases[(size_t)r * gpr + g]);
+            const unsigned int w4[4] = {e.x, e.y, e.z, e.w};
+            const float* hv = hs + 16 * i;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc = __fmaf_rn(q8_deq(w4[j] & 0xffu, s, b), hv[4 * j], acc);
+                acc = __fmaf_rn(q8_deq((w4[j] >> 8) & 0xffu, s, b), hv[4 * j + 1], acc);
+                acc = __fmaf_rn(q8_deq((w4[j] >> 16) & 0xffu, s, b), hv[4 * j + 2], acc);
+                acc = __fmaf_rn(q8_deq(w4[j] >> 24, s, b), hv[4 * j + 3], acc);
+            }
+        }
+        acc = warp_sum_f(acc);
+        if (head_better(acc, r, best, best_row)) {
+            best = acc;
+            best_row = r;
+        }
+    }
+    if (lane == 0) red[warp] = HeadBest{best, best_row};
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        HeadBest b = red[0];
+        for (int w = 1; w < kHeadThreads / 32; ++w)
+            if (head_better(red[w].val, red[w].row, b.val, b.row)) b = red[w];
+        partial[blockIdx.x] = b;
+    }
+}
+
+// Token ids -> dequantised f16 rows, one CTA per token (emb_q8_gather): y[t, c] = f16(scale * q + bias).
+__global__ void embed_gather_q8_kernel(const unsigned char* __restrict__ wq, const __half* __restrict__ scales,
+                                       const __half* __restrict__ biases, const long long* __restrict__ ids,
+                                       __half* __restrict__ y, int hidden, int rows) {
+    long long row = ids[blockIdx.x];
+    if (row < 0 || row >= rows) row = 0;  // a token outside the vocabulary reads row 0 instead of foreign memory
+    const int gpr = (hidden + 63) / 64;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const size_t g = (size_t)row * gpr + (c >> 6);
+        y[(size_t)blockIdx.x * hidden + c] =
+            __float2half_rn(q8_deq(wq[(size_t)row * hidden + c], __half2float(scales[g]), __half2float(biases[g])));
+    }
+}
+
 // One CTA: merge the partials; the row index is reported with `row_offset` added (a vocabulary shard).
 __global__ void __launch_bounds__(kHeadMaxGrid)
 lm_head_pick_kernel(const HeadBest* __restrict__ partial, int n, long long row_offset, float* __restrict__ val_out,

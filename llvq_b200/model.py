@@ -95,6 +95,86 @@ class Int8KvCache:
         return 2 * (self.q[0][0].numel() + 2 * 2 * self.s[0][0].numel())
 
 
+class F16Embedding:
+    """The tied f16 embedding: row gather for the input, `head(E, h, row_offset)` for the greedy pick."""
+
+    def __init__(self, w, head: Callable):
+        self.w, self.head, self.device, self.rows = w, head, w.device, w.shape[0]
+
+    def lookup(self, tokens):
+        return self.w.index_select(0, tokens)
+
+    def shard(self, lo: int, hi: int) -> "F16Embedding":
+        return F16Embedding(self.w[lo:hi], self.head)
+
+    def pick(self, h, row_offset: int):
+        return self.head(self.w, h, row_offset)
+
+    def dense(self):
+        return self.w
+
+
+class Q8Embedding:
+    """The tied embedding carried as int8 g64 (w = scale * q + bias per 64 values of a row, f16 scale and bias:
+    the `embedq` payload of a sealed file, llvq-llm/src/embedquant.rs:22, kernels llvq-llm/kernels/emb_q8.cu)."""
+
+    def __init__(self, lib, wq, scales, biases):
+        import torch
+        if wq.dtype != torch.uint8 or scales.dtype != torch.float16 or biases.dtype != torch.float16 or wq.shape[1] % 64:
+            raise ValueError("Q8Embedding: u8 codes [V, H] with H % 64 == 0, f16 scales and biases [V, H / 64]")
+        self.lib, self.wq, self.scales, self.biases = lib, wq.contiguous(), scales.contiguous(), biases.contiguous()
+        self.device, self.rows, self.hidden = wq.device, wq.shape[0], wq.shape[1]
+        self._scratch = torch.zeros(8192, dtype=torch.uint8, device=self.device)
+        self._val = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._idx = torch.zeros(1, dtype=torch.long, device=self.device)
+
+    @staticmethod
+    def quantize(lib, w):
+        """f16 [V, H] -> Q8Embedding by the reference's quantize_affine (embedquant.rs:22-80): per group the
+        range over 255 through f16, constant groups ungraded (scale 1, q 0), round half away from zero."""
+        import torch
+        V, H = w.shape
+        g = w.float().reshape(V, H // 64, 64)
+        mn, mx = g.amin(-1, keepdim=True), g.amax(-1, keepdim=True)
+        s = ((mx - mn) / 255.0).half()
+        graded = s.float() > 0
+        s = torch.where(graded, s, torch.ones_like(s))
+        b = mn.half()
+        t = (g - b.float()) / s.float()
+        q = torch.where(graded, (torch.sign(t) * torch.floor(t.abs() + 0.5)).clamp(0, 255), torch.zeros_like(t))
+        return Q8Embedding(lib, q.to(torch.uint8).reshape(V, H), s.reshape(V, H // 64), b.reshape(V, H // 64))
+
+    def lookup(self, tokens):
+        import ctypes as C
+        import torch
+        from ._lib import check
+        tokens = tokens.to(torch.long).contiguous()
+        y = torch.empty(tokens.numel(), self.hidden, dtype=torch.float16, device=self.device)
+        p = lambda t: C.c_void_p(t.data_ptr())
+        check(self.lib.llvq_op_embed_gather_q8_h(p(self.wq), p(self.scales), p(self.biases), p(tokens), tokens.numel(), self.rows,
+                                                 self.hidden, p(y), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return y
+
+    def shard(self, lo: int, hi: int) -> "Q8Embedding":
+        return Q8Embedding(self.lib, self.wq[lo:hi], self.scales[lo:hi], self.biases[lo:hi])
+
+    def pick(self, h, row_offset: int):
+        import ctypes as C
+        import torch
+        from ._lib import check
+        p = lambda t: C.c_void_p(t.data_ptr())
+        check(self.lib.llvq_op_lm_head_argmax_q8_h(p(self.wq), p(self.scales), p(self.biases), p(h), self.rows, self.hidden, row_offset,
+                                                   p(self._scratch), p(self._val), p(self._idx),
+                                                   C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return self._val, self._idx
+
+    def dense(self):
+        """Dequantised f16 copy (diagnostics and tests): f16(scale * q + bias), f32 multiply then add."""
+        V, H = self.wq.shape
+        w = self.wq.float().reshape(V, H // 64, 64) * self.scales.float().unsqueeze(-1) + self.biases.float().unsqueeze(-1)
+        return w.reshape(V, H).half()
+
+
 class TpGroup:
     """Rank layout of a tensor-parallel model: rank r of `world` holds q heads [r H/world, (r+1) H/world),
     the matching kv heads, rows [r I/world, ...) of gate/up, rows [r D/world, ...) of o/down and rows
@@ -168,10 +248,12 @@ class FusedQwen3:
         self.h_loc, self.kv_loc, self.inter_loc = cfg.n_heads // self.world, cfg.n_kv // self.world, cfg.inter // self.world
         self.prefill_chunk = prefill_chunk
         self.sdpa_from = 1 << 28  # bytes of f32 scores above which the prompt attention is the library's fused kernel
-        dev = embed.device
+        # `embed`: the tied f16 embedding as a tensor, or an embedding object (F16Embedding, Q8Embedding)
+        self.emb = embed if hasattr(embed, "lookup") else F16Embedding(embed, head)
+        dev = self.emb.device
         self.device = dev
         v_loc = cfg.vocab // self.world
-        self.embed_head = embed[self.rank * v_loc:(self.rank + 1) * v_loc]
+        self.emb_head = self.emb.shard(self.rank * v_loc, (self.rank + 1) * v_loc)
         self.head_offset = self.rank * v_loc
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=dev, dtype=torch.float32) / cfg.head_dim))
         ang = torch.arange(capacity, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
@@ -288,7 +370,7 @@ class FusedQwen3:
         return x + self._all(self._proj(blk, "down", self._all(gated)))
 
     def hidden(self, tokens, pos, end: Optional[int] = None):
-        x = self.embed.index_select(0, tokens)
+        x = self.emb.lookup(tokens)
         for i in range(len(self.blocks)):
             x = self._block(i, x, pos, end)
         return x
@@ -306,7 +388,7 @@ class FusedQwen3:
 
     def pick(self, h):
         """Greedy token of the normalised hidden state h [hidden] -> int64 [1] (device)."""
-        val, idx = self.head(self.embed_head, h, self.head_offset)
+        val, idx = self.emb_head.pick(h, self.head_offset)
         if not self.tp:
             return idx
         self._best[0:1].view(val.dtype)[0:1].copy_(val)
@@ -319,7 +401,7 @@ class FusedQwen3:
     def logits_last(self, x):
         """Full logits of the last row (diagnostics; the loop itself uses `pick`)."""
         h = self._rms(x[-1:], self.final_norm)
-        return (h @ self.embed.t()).float()[0]
+        return (h @ self.emb.dense().t()).float()[0]
 
     # ---- the loop ----------------------------------------------------------------
     def generate(self, prompt: Sequence[int], max_new: int, use_graph: bool = False) -> List[int]:
@@ -369,7 +451,7 @@ class FusedQwen3:
         L, cfg, tp = self.ops, self.cfg, self.tp
         st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         p = lambda t: C.c_void_p(t.data_ptr())
-        self._x.copy_(self.embed.index_select(0, self._tok)[0])
+        self._x.copy_(self.emb.lookup(self._tok)[0])
         delta = None
 
         def norm_then(blk, name, ln, delta, out):
@@ -471,7 +553,7 @@ def tp_rows(cfg: Qwen3Config, world: int, rank: int) -> dict:
 
 def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: int = 0x51, layers: Optional[int] = None,
                     kv_int8: bool = True, fused_ops: bool = True, tp: Optional[TpGroup] = None, dense_prefill_from: int = 1024,
-                    keep_host: bool = True, device_codes: bool = False, rotations: bool = False):
+                    keep_host: bool = True, device_codes: bool = False, rotations: bool = False, embed_q8: bool = False):
     """Random-weight model of benchmark configurations 2 and 4: LLVQ codes for every projection, f16 N(0, 0.02)
     norms and tied embedding (norm weights are 1 + N(0, 0.02) so that activations keep their scale).
     With `tp` every rank draws and uploads only its own rows of each matrix (the same matrices for any
@@ -520,6 +602,8 @@ def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: i
     else:
         embed = f16(cfg.vocab * cfg.hidden).reshape(cfg.vocab, cfg.hidden)
     final_norm = f16(cfg.hidden, 1.0)
+    if embed_q8:  # carry the tied embedding as int8 g64, as a file sealed with the reference's embedq does
+        embed = Q8Embedding.quantize(rt.lib, embed)
 
     def gemm(proj, x):
         return rt.forward_batch_dense(proj, x) if x.shape[0] >= dense_prefill_from else rt.forward_batch(proj, x)
@@ -536,7 +620,8 @@ def load_archive_model(rt, ar, capacity: int, kv_int8: bool = True, fused_ops: b
     `model.layers.{i}.self_attn.{q,k,v,o}_proj.weight` / `mlp.{gate,up,down}_proj.weight` are uploaded straight
     from the file (q|k|v and gate|up as row groups), every group gets the rotation its records name (the records
     of a group must agree on it, as they consume one activation), the raw tensors give the tied f16 embedding and
-    the norms, and `config.json` the shape. Quantised embeddings (tag 1) are not served by this loader."""
+    the norms, and `config.json` the shape. An embedding stored group-affine quantised (tag 1) is served when it
+    is int8 with groups of 64 (the `embedq` payload); other quantised raw tensors are refused."""
     import ctypes as C
     import json
     import torch
@@ -554,9 +639,15 @@ def load_archive_model(rt, ar, capacity: int, kv_int8: bool = True, fused_ops: b
     raws = {}
     for i in range(ar.n_raw):
         t = ar.raw(i)
-        if t["tag"] != 0:
-            raise ValueError(f"{t['name']}: stored group-affine quantised; this loader takes f16 raw tensors")
-        raws[t["name"]] = torch.from_numpy(t["data"].astype(np.float16)).to(dev)
+        if t["tag"] == 0:
+            raws[t["name"]] = torch.from_numpy(t["data"].astype(np.float16)).to(dev)
+        elif t["name"] == "model.embed_tokens.weight" and t["bits"] == 8 and t["group"] == 64 and len(t["dims"]) == 2:
+            V, H = t["dims"]
+            raws[t["name"]] = Q8Embedding(rt.lib, torch.from_numpy(t["packed"].copy()).reshape(V, H).to(dev),
+                                          torch.from_numpy(t["scales"].astype(np.float16)).reshape(V, H // 64).to(dev),
+                                          torch.from_numpy(t["biases"].astype(np.float16)).reshape(V, H // 64).to(dev))
+        else:
+            raise ValueError(f"{t['name']}: group-affine {t['bits']}-bit g{t['group']}; only an int8 g64 embedding is served")
 
     def group(layer: int, names):
         ids = [index[f"model.layers.{layer}.{n}.weight"] for n in names]
@@ -586,6 +677,7 @@ def load_archive_model(rt, ar, capacity: int, kv_int8: bool = True, fused_ops: b
     def gemm(proj, x):
         return rt.forward_batch_dense(proj, x) if x.shape[0] >= dense_prefill_from else rt.forward_batch(proj, x)
 
-    return FusedQwen3(cfg, blocks, raws["model.embed_tokens.weight"].contiguous(), raws["model.norm.weight"], capacity,
+    emb = raws["model.embed_tokens.weight"]
+    return FusedQwen3(cfg, blocks, emb if isinstance(emb, Q8Embedding) else emb.contiguous(), raws["model.norm.weight"], capacity,
                       gemv=rt.forward, gemm=gemm, head=kernel_head(rt.lib), kv_int8=kv_int8, ops=rt.lib if fused_ops else None,
                       rotate=rt.rotate, gemv_rotated=rt.forward_rotated)

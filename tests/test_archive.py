@@ -187,3 +187,17 @@ def test_decode_loop_from_a_sealed_file_matches_the_loop_built_from_the_same_arr
                         ops=rt.lib, rotate=rt.rotate, gemv_rotated=rt.forward_rotated)
     want = direct.generate(prompt, 16)
     assert got == want and graphed == want and len(set(want)) >= 1
+    # the same file with the embedding carried as int8 g64 (tag 1): loaded, and equal to the loop built on the
+    # same quantised payload
+    from llvq_b200.model import Q8Embedding
+    q = Q8Embedding.quantize(rt.lib, t(emb))
+    raws_q = [W.raw_quant("model.embed_tokens.weight", [cfg.vocab, cfg.hidden], 8, 64, q.wq.cpu().numpy().tobytes(),
+                          q.scales.cpu().numpy().reshape(-1), q.biases.cpu().numpy().reshape(-1))] + raws[1:]
+    path_q = os.path.join(tmp_path, "tiny_q8.llvq")
+    with open(path_q, "wb") as f:
+        f.write(W.container(4, recs, raws_q, [W.blob("config.json", json.dumps(config).encode())]))
+    with LvqArchive(path=path_q) as ar:
+        got_q = load_archive_model(rt, ar, capacity=64).generate(prompt, 16)
+    direct_q = FusedQwen3(cfg, blocks, q, t(final), 64, gemv=rt.forward, gemm=rt.forward_batch, head=kernel_head(rt.lib),
+                          ops=rt.lib, rotate=rt.rotate, gemv_rotated=rt.forward_rotated)
+    assert got_q == direct_q.generate(prompt, 16)

@@ -33,14 +33,15 @@ def _dense_model(rt, oracle, cfg, mats, fused, capacity, kv_int8):
                       rotate=fused.rotate, gemv_rotated=lambda w, xr, out=None: lin(xr, w.float()).half())
 
 
-@pytest.mark.parametrize("kv_int8,rotations", [(True, False), (False, False), (True, True)])
-def test_greedy_tokens_match_the_dense_decoded_run(rt, oracle, kv_int8, rotations):
+@pytest.mark.parametrize("kv_int8,rotations,embed_q8", [(True, False, False), (False, False, False), (True, True, False),
+                                                        (True, False, True)])
+def test_greedy_tokens_match_the_dense_decoded_run(rt, oracle, kv_int8, rotations, embed_q8):
     import torch
     from llvq_b200.model import Qwen3Config, synthetic_model
     # widths 256 (power of two: no odd mix) and 496 = 16 * 31 (the largest odd factors the rotation serves)
     cfg = Qwen3Config(hidden=24 * 10 + 16, inter=24 * 20 + 16, n_heads=4, n_kv=2, head_dim=64, layers=2, vocab=512)
     capacity = 64
-    fused, mats = synthetic_model(rt, cfg, config_id=2, capacity=capacity, kv_int8=kv_int8, rotations=rotations)
+    fused, mats = synthetic_model(rt, cfg, config_id=2, capacity=capacity, kv_int8=kv_int8, rotations=rotations, embed_q8=embed_q8)
     dense = _dense_model(rt, oracle, cfg, mats, fused, capacity, kv_int8)
     g = np.random.default_rng(5)
     prompt = [int(t) for t in g.integers(0, cfg.vocab, 20)]  # 20 >= 16: the prefill takes the tensor-core GEMM
@@ -249,3 +250,32 @@ def test_tensor_parallel_model_on_two_gpus_picks_the_single_gpu_tokens():
                 p.terminate()  # the exact children started above
     for rank, phase, want, tokens in got:
         assert tokens == want, (rank, phase, want, tokens)
+
+
+def test_int8_embedding_kernels_follow_the_reference_arithmetic(rt):
+    """emb_q8_gather: f16(scale * q + bias) with an f32 multiply then an f32 add, bit for bit; the greedy head over
+    the same payload picks the argmax of the f32 logits of the dequantised rows (llvq-llm/kernels/emb_q8.cu:42-106);
+    the quantiser follows quantize_affine (embedquant.rs:22-80): constant groups ungraded, codes within one step."""
+    import torch
+    from llvq_b200.model import Q8Embedding
+    g = torch.Generator(device="cuda").manual_seed(6)
+    for V, H in ((1000, 256), (151936 // 8, 2560), (16, 64)):
+        w = (0.02 * torch.randn(V, H, device="cuda", generator=g)).half()
+        w[3 % V, :64] = 0.25  # a constant group
+        emb = Q8Embedding.quantize(rt.lib, w)
+        assert emb.scales[3 % V, 0] == 1.0 and int(emb.wq[3 % V, :64].max()) == 0 and emb.biases[3 % V, 0] == 0.25
+        deq = (emb.scales.float().unsqueeze(-1) * emb.wq.float().reshape(V, H // 64, 64) + emb.biases.float().unsqueeze(-1)).reshape(V, H)
+        step = emb.scales.float().unsqueeze(-1).expand(V, H // 64, 64).reshape(V, H)
+        assert ((deq - w.float()).abs() <= 0.51 * step + 1e-3).all()
+        toks = torch.tensor([0, V - 1, 3 % V, 7 % V], device="cuda")
+        assert torch.equal(emb.lookup(toks), deq.half().index_select(0, toks))
+        assert torch.equal(emb.dense(), deq.half())
+        h = torch.randn(H, device="cuda", generator=g).half()
+        logits = deq @ h.float()
+        val, idx = emb.pick(h, 100)
+        torch.cuda.synchronize()
+        assert int(idx) - 100 == int(logits.argmax()) and abs(float(val) - float(logits.max())) <= 1e-4 * max(1.0, float(logits.abs().max()))
+        lo = V // 2
+        v2, i2 = emb.shard(lo, V).pick(h, lo)
+        if int(logits.argmax()) >= lo:
+            assert int(i2) == int(logits.argmax())
