@@ -231,7 +231,7 @@ def run_reference(args):
     t = sum(times) / len(times)
     val = nbytes / t / 1e9
     sample = "each step = the 7 projections of one layer (4 185 600 blocks) on all host threads"
-    print(json.dumps({
+    emit(({
         "impl": "reference", "metric": "dequant_gemv_algorithmic_GBps", "value": val, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
@@ -314,7 +314,7 @@ def run_tp_decode(args):
     if rank == 0:
         gen = new_tokens - 1
         kv_bytes = 2 * layers * (prompt_len + new_tokens // 2) * cfg.n_kv * (cfg.head_dim + 2 * 2 * cfg.head_dim // 64)
-        print(json.dumps({
+        emit(({
             "metric": "decode_tok_per_s", "value": gen / (decode_ms * 1e-3), "unit": "tok/s", "n_gpus": world,
             "steps": gen, "warmup": max(args.warmup, 3), "ms_per_step": decode_ms / gen, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -374,13 +374,37 @@ def run_tp(args):
         per_layer.append(row)
     x_h = torch.from_numpy(synth.make_activation(5120, 0x4000, np.float16)).cuda()
     x_i = torch.from_numpy(synth.make_activation(17408, 0x4001, np.float16)).cuda()
+    # the gathers of one layer: q|k|v -> context, o, gate|up -> SwiGLU product, down (all needed whole by what follows);
+    # through peer memory by default (one site per gather of a layer), NCCL with --gather nccl
+    peer = None
+    if world > 1 and args.gather == "peer":
+        from llvq_b200.parallel import PeerExchange
+        peer = PeerExchange(rt.lib, local_rank, [row[gi][2].numel() * 2 for gi in range(4) for row in per_layer[:1]])
 
-    def step():
+    def pass_once():
         for row in per_layer:
             for gi, (proj, y_loc, y_all, _full) in enumerate(row):
                 rt.forward(proj, x_i if gi == 3 else x_h, out=y_loc)
-                if world > 1:  # q|k|v -> context, o, gate|up -> SwiGLU product, down: all needed whole next
+                if peer is not None:
+                    peer.exchange(gi, y_loc)
+                elif world > 1:
                     dist.all_gather_into_tensor(y_all, y_loc)
+
+    # one captured graph per rank, as the decode loop runs it: launch cost is not what is being measured
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        pass_once()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        pass_once()
+
+    def step():
+        graph.replay()
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -404,35 +428,58 @@ def run_tp(args):
     if rank == 0:
         peak, peak_kind, _ = measured_peaks()
         gbs = job_bytes / (ms * 1e-3) / 1e9
-        print(json.dumps({
+        emit(({
             "metric": "dequant_gemv_algorithmic_GBps", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "qwen3-14b-tp-layer-gemv", "layers_per_step": layers, "parallelism": f"tp{world}",
-                       "collective": "nccl all_gather_into_tensor x4 per layer" if world > 1 else "none",
+                       "collective": ("none" if world == 1 else "peer-memory exchange kernel x4 per layer" if peer is not None
+                                      else "nccl all_gather_into_tensor x4 per layer"),
                        "blocks_per_step": job_blocks, "algorithmic_bytes_per_step": job_bytes},
             "token_equiv_per_s": (layers / 40.0) / (ms * 1e-3), "gblocks_per_s": job_blocks / (ms * 1e-3) / 1e9,
             "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
-                         "traffic": None, "peak_kind": f"of {peak_kind}"}}))
+                         "traffic": None, "peak_kind": f"of {peak_kind}"},
+            "peer_errors": peer.poll_error() if peer is not None else None, "graph": True}))
     if world > 1:
-        dist.destroy_process_group()
+        # as in run_tp_decode: every collective has completed and been read; the ranks leave without tearing
+        # the process group down under a captured graph
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
-def _quiet_nccl():
-    """NCCL prints a version banner on stdout at the VERSION and WARN debug levels, ahead of the one JSON line a
-    rank-0 run must print: send whatever NCCL logs to stderr instead (the level itself is left alone)."""
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+_RESULT_FD = None
+
+
+def _own_stdout():
+    """The contract is ONE JSON line on stdout. Libraries write there too (NCCL prints a version banner at its
+    VERSION and WARN debug levels), so the process keeps a private duplicate of stdout for the result and points
+    file descriptor 1 at stderr for everything else."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(obj) -> None:
+    line = (json.dumps(obj) + "\n").encode()
+    sys.stdout.flush()
+    if _RESULT_FD is None:
+        os.write(1, line)
+    else:
+        os.write(_RESULT_FD, line)
 
 
 def main():
-    _quiet_nccl()
+    _own_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--tp", action="store_true",
                     help="tensor-parallel mode: Qwen3-14B projections row-sharded over the ranks with all-gathers")
     ap.add_argument("--tp-decode", action="store_true",
                     help="config 4: Qwen3-14B tensor-parallel greedy decode over the ranks (prompt --prompt, --new-tokens)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
-                    help="--tp-decode: token-step all-gathers through peer memory (llvq_tp_exchange) or NCCL")
+                    help="--tp / --tp-decode: all-gathers of the row shards through peer memory (llvq_tp_exchange) or NCCL")
     ap.add_argument("--no-graph", action="store_true", help="--tp-decode: launch every token step eagerly")
     ap.add_argument("--prompt", type=int, default=32768)
     ap.add_argument("--new-tokens", type=int, default=128)
@@ -593,7 +640,7 @@ def main():
     if not args.no_cpu_baseline and world == 1:
         cb, _ = cpu_baseline()
         out["cpu_baseline"] = cb
-    print(json.dumps(out))
+    emit(out)
     if world > 1:
         dist.destroy_process_group()
 
