@@ -16,11 +16,16 @@ namespace llvq {
 
 constexpr int kRotThreads = 1024;
 
+// Coordinate i of the vector lives at word i + i / 8 of shared memory: the radix-8 passes touch eight
+// coordinates 1, 8, 64... apart per thread, and the skew keeps the 32 lanes of a warp on 32 different banks
+// in the first two passes (without it they are 8-way and 4-way conflicts).
+__host__ __device__ inline int rot_at(int i) { return i + (i >> 3); }
+
 template <int R>
 __device__ __forceinline__ void wht_radix(float* s, int base, int stride) {
     float v[R];
 #pragma unroll
-    for (int j = 0; j < R; ++j) v[j] = s[base + j * stride];
+    for (int j = 0; j < R; ++j) v[j] = s[rot_at(base + j * stride)];
 #pragma unroll
     for (int len = 1; len < R; len <<= 1) {
 #pragma unroll
@@ -33,7 +38,7 @@ __device__ __forceinline__ void wht_radix(float* s, int base, int stride) {
         }
     }
 #pragma unroll
-    for (int j = 0; j < R; ++j) s[base + j * stride] = v[j];
+    for (int j = 0; j < R; ++j) s[rot_at(base + j * stride)] = v[j];
 }
 
 // Row stride of Q_odd in shared memory: k rounded up to the compile-time bound of rot_mix (zero padded).
@@ -48,7 +53,7 @@ __device__ __forceinline__ void rot_mix(const float* s, const float* q, float* _
     for (int j = tid; j < m; j += kRotThreads) {
         float col[KB];
 #pragma unroll
-        for (int t = 0; t < KB; ++t) col[t] = t < k ? s[t * m + j] * inv : 0.0f;
+        for (int t = 0; t < KB; ++t) col[t] = t < k ? s[rot_at(t * m + j)] * inv : 0.0f;
         for (int g = 0; g < k; ++g) {
             float acc = 0.0f;
 #pragma unroll
@@ -84,7 +89,7 @@ __device__ __forceinline__ void rot_transform(float* s, const float* q, float* _
         stride *= r;
     }
     if (k == 1) {
-        for (int i = tid; i < n; i += kRotThreads) out[i] = s[i] * inv;
+        for (int i = tid; i < n; i += kRotThreads) out[i] = s[rot_at(i)] * inv;
         return;
     }
     if (k <= 4) rot_mix<4>(s, q, out, m, k, inv, tid);
@@ -104,7 +109,8 @@ __device__ __forceinline__ void rot_stage_q(float* q, const float* __restrict__ 
 
 // Floats of dynamic shared memory a rotation of width n needs: the vector (rounded up to a multiple of 4 so
 // that Q_odd starts 16-byte aligned) and the padded Q_odd.
-__host__ __device__ inline size_t rot_smem_floats(int n, int k) { return (size_t)((n + 3) & ~3) + (size_t)k * rot_qstride(k); }
+__host__ __device__ inline int rot_vec_words(int n) { return (rot_at(n) + 4) & ~3; }
+__host__ __device__ inline size_t rot_smem_floats(int n, int k) { return (size_t)rot_vec_words(n) + (size_t)k * rot_qstride(k); }
 
 __device__ __forceinline__ float rot_signed(const unsigned int* __restrict__ signbits, int i, float v) {
     return ((signbits[i >> 5] >> (i & 31)) & 1u) ? -v : v;
@@ -117,11 +123,11 @@ rot_apply_kernel(const __half* __restrict__ x, const unsigned int* __restrict__ 
                  float* __restrict__ out, int n, int m, int k, float inv) {
     extern __shared__ float rot_s[];
     float* s = rot_s;
-    float* q = rot_s + ((n + 3) & ~3);
+    float* q = rot_s + rot_vec_words(n);
     const int tid = threadIdx.x;
     x += (size_t)blockIdx.x * n;
     out += (size_t)blockIdx.x * n;
-    for (int i = tid; i < n; i += kRotThreads) s[i] = rot_signed(signbits, i, __half2float(x[i]));
+    for (int i = tid; i < n; i += kRotThreads) s[rot_at(i)] = rot_signed(signbits, i, __half2float(x[i]));
     rot_stage_q(q, small, k, tid);
     __syncthreads();
     rot_transform(s, q, out, n, m, k, inv, tid);
@@ -137,7 +143,7 @@ add_rmsnorm_rotate_kernel(__half* __restrict__ x, const __half* __restrict__ del
     extern __shared__ float rot_s[];
     __shared__ float red[32];
     float* s = rot_s;
-    float* q = rot_s + ((n + 3) & ~3);
+    float* q = rot_s + rot_vec_words(n);
     const int tid = threadIdx.x;
     constexpr int kMaxPairs = 8;  // up to 16 384 elements
     const int pairs = n >> 1;
@@ -173,8 +179,8 @@ add_rmsnorm_rotate_kernel(__half* __restrict__ x, const __half* __restrict__ del
         if (i < pairs) {
             const float2 wf = __half22float2(reinterpret_cast<const __half2*>(w)[i]);
             const float2 y = __half22float2(__floats2half2_rn(v[j].x * r * wf.x, v[j].y * r * wf.y));
-            s[2 * i] = rot_signed(signbits, 2 * i, y.x);
-            s[2 * i + 1] = rot_signed(signbits, 2 * i + 1, y.y);
+            s[rot_at(2 * i)] = rot_signed(signbits, 2 * i, y.x);
+            s[rot_at(2 * i + 1)] = rot_signed(signbits, 2 * i + 1, y.y);
         }
     }
     __syncthreads();
@@ -187,11 +193,11 @@ silu_mul_rotate_kernel(const __half* __restrict__ gu, const unsigned int* __rest
                        const float* __restrict__ small, float* __restrict__ out, int n, int m, int k, float inv) {
     extern __shared__ float rot_s[];
     float* s = rot_s;
-    float* q = rot_s + ((n + 3) & ~3);
+    float* q = rot_s + rot_vec_words(n);
     const int tid = threadIdx.x;
     for (int i = tid; i < n; i += kRotThreads) {
         const float g = __half2float(gu[i]), u = __half2float(gu[n + i]);
-        s[i] = rot_signed(signbits, i, __half2float(__float2half_rn(g / (1.0f + __expf(-g)) * u)));
+        s[rot_at(i)] = rot_signed(signbits, i, __half2float(__float2half_rn(g / (1.0f + __expf(-g)) * u)));
     }
     rot_stage_q(q, small, k, tid);
     __syncthreads();
