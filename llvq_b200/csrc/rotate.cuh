@@ -10,6 +10,7 @@
 // k x k odd mix come last, one output per thread and step: out[g m + j] = sum_t Q_odd[g][t] *
 // (s[t m + j] * inv), t ascending, fused multiply-adds (llvq_rot.cuh:213-235).
 #pragma once
+#include <cstdint>
 #include <cuda_fp16.h>
 
 namespace llvq {
@@ -74,8 +75,8 @@ __device__ __forceinline__ void rot_mix(const float* s, const float* q, float* _
 // after both were written is the caller's): Hadamard
 // passes, then scale and odd mix into out.
 __device__ __forceinline__ void rot_transform(float* s, const float* q, float* __restrict__ out, int n, int m, int k,
-                                              float inv, int tid) {
-    for (int stride = 1; stride < m;) {
+                                              float inv, int tid, int first_stride = 1) {
+    for (int stride = first_stride; stride < m;) {
         const int r = min(8, m / stride);  // 8, or what is left of m: 4 or 2
         const int groups = n / r;
         for (int gi = tid; gi < groups; gi += kRotThreads) {
@@ -116,6 +117,28 @@ __device__ __forceinline__ float rot_signed(const unsigned int* __restrict__ sig
     return ((signbits[i >> 5] >> (i & 31)) & 1u) ? -v : v;
 }
 
+// Eight consecutive coordinates in registers: signs from one byte of the bitmap, then the first three butterfly
+// stages (len 1, 2, 4: the stride-1 radix-8 pass) before the values ever reach shared memory. i % 8 == 0.
+__device__ __forceinline__ void rot_first_pass_store(float* s, const unsigned int* __restrict__ signbits, int i, float (&v)[8]) {
+    const unsigned int bits = (signbits[i >> 5] >> (i & 31)) & 0xffu;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = ((bits >> j) & 1u) ? -v[j] : v[j];
+#pragma unroll
+    for (int len = 1; len < 8; len <<= 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if ((j & len) == 0) {
+                const float a = v[j], b = v[j + len];
+                v[j] = a + b;
+                v[j + len] = a - b;
+            }
+        }
+    }
+    const int w = rot_at(i);  // i + j stays inside one skew step: eight consecutive words
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[w + j] = v[j];
+}
+
 // grid = rows of the batch (one CTA rotates one activation). Dynamic shared memory: n floats of the
 // vector, then k * k floats of Q_odd.
 __global__ void __launch_bounds__(kRotThreads)
@@ -127,10 +150,27 @@ rot_apply_kernel(const __half* __restrict__ x, const unsigned int* __restrict__ 
     const int tid = threadIdx.x;
     x += (size_t)blockIdx.x * n;
     out += (size_t)blockIdx.x * n;
-    for (int i = tid; i < n; i += kRotThreads) s[rot_at(i)] = rot_signed(signbits, i, __half2float(x[i]));
+    // 16-byte loads and the first pass in registers when the group width allows (every model width does)
+    const bool fast = m >= 8 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    if (fast) {
+        for (int i = tid * 8; i < n; i += kRotThreads * 8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(x + i);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h2[j]);
+                v[2 * j] = f.x;
+                v[2 * j + 1] = f.y;
+            }
+            rot_first_pass_store(s, signbits, i, v);
+        }
+    } else {
+        for (int i = tid; i < n; i += kRotThreads) s[rot_at(i)] = rot_signed(signbits, i, __half2float(x[i]));
+    }
     rot_stage_q(q, small, k, tid);
     __syncthreads();
-    rot_transform(s, q, out, n, m, k, inv, tid);
+    rot_transform(s, q, out, n, m, k, inv, tid, fast ? 8 : 1);
 }
 
 // add + RMSNorm of the residual stream (as add_rmsnorm_kernel: x += delta in f16, y = f16(x / rms * w)) with
@@ -195,13 +235,30 @@ silu_mul_rotate_kernel(const __half* __restrict__ gu, const unsigned int* __rest
     float* s = rot_s;
     float* q = rot_s + rot_vec_words(n);
     const int tid = threadIdx.x;
-    for (int i = tid; i < n; i += kRotThreads) {
-        const float g = __half2float(gu[i]), u = __half2float(gu[n + i]);
-        s[rot_at(i)] = rot_signed(signbits, i, __half2float(__float2half_rn(g / (1.0f + __expf(-g)) * u)));
+    const bool fast = m >= 8 && (reinterpret_cast<uintptr_t>(gu) & 15u) == 0;  // then n % 8 == 0 and gu + n is aligned too
+    if (fast) {
+        for (int i = tid * 8; i < n; i += kRotThreads * 8) {
+            const uint4 gr = *reinterpret_cast<const uint4*>(gu + i), ur = *reinterpret_cast<const uint4*>(gu + n + i);
+            const __half2* g2 = reinterpret_cast<const __half2*>(&gr);
+            const __half2* u2 = reinterpret_cast<const __half2*>(&ur);
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 g = __half22float2(g2[j]), u = __half22float2(u2[j]);
+                v[2 * j] = __half2float(__float2half_rn(g.x / (1.0f + __expf(-g.x)) * u.x));
+                v[2 * j + 1] = __half2float(__float2half_rn(g.y / (1.0f + __expf(-g.y)) * u.y));
+            }
+            rot_first_pass_store(s, signbits, i, v);
+        }
+    } else {
+        for (int i = tid; i < n; i += kRotThreads) {
+            const float g = __half2float(gu[i]), u = __half2float(gu[n + i]);
+            s[rot_at(i)] = rot_signed(signbits, i, __half2float(__float2half_rn(g / (1.0f + __expf(-g)) * u)));
+        }
     }
     rot_stage_q(q, small, k, tid);
     __syncthreads();
-    rot_transform(s, q, out, n, m, k, inv, tid);
+    rot_transform(s, q, out, n, m, k, inv, tid, fast ? 8 : 1);
 }
 
 }  // namespace llvq
