@@ -365,6 +365,26 @@ int llvq_tp_exchange_emulated(llvq_tp_ctx* const* ctxs, int32_t n, int32_t site,
 /* Read and clear the error word (synchronises the device). */
 int llvq_tp_poll_error(llvq_tp_ctx* ctx, int32_t* out);
 
+/* ---- attribution probes ---------------------------------------------------- */
+
+/* llvq_gemv_h with parts of the kernel left out, for timing what the rest costs: the reference's
+ * "floor" kernels (llvq-cuda/kernels/nullk.cu:61: same grid, staging and reduction, no weights;
+ * llvq-cuda/kernels/llvq_floor.cuh:133-135: stream only / + table / + shared-memory reads).
+ * mode 0 = the full kernel; 1 = no decoders (records are read and classified, activations staged,
+ * rows summed and stored); 2 = no class search (records are only read); 3 = neither. y is NOT the
+ * product for mode > 0. */
+int llvq_gemv_probe_h(llvq_matrix* m, const uint16_t* x_dev, uint16_t* y_dev, int32_t mode, llvq_stream_t stream);
+
+/* One launch of the f16 GEMV kernel (mode as in llvq_gemv_probe_h) with time stamps: for each of
+ * the first max_ctas CTAs, 64 uint64 nanosecond readings of the GPU's global timer: [0] kernel
+ * entry, [1] tables and first codes landed, [2 + 2 i] end of pipeline interval i (after its barrier),
+ * [3 + 2 i] arrival of one warp at that barrier; 0 where an event did not occur. The per-phase timing
+ * the reference prints for a token (generate_phased, llvq-llm/src/model.rs:1116-1163), at the scale
+ * of one kernel. Allocates and frees a device buffer; synchronises the stream. */
+#define LLVQ_TRACE_EVENTS 64
+int llvq_gemv_trace_h(llvq_matrix* m, const uint16_t* x_dev, uint16_t* y_dev, int32_t mode, uint64_t* trace_host,
+                      int32_t max_ctas, int32_t* n_ctas, llvq_stream_t stream);
+
 /* ---- decode probes --------------------------------------------------------- */
 
 /* Decode n packed 6-byte records on the GPU to their lattice points: 24 int8
@@ -374,6 +394,14 @@ int llvq_tp_poll_error(llvq_tp_ctx* ctx, int32_t* out);
  * (llvq-cuda/kernels/preflight.cu:28-60). All pointers are device memory. */
 int llvq_decode_blocks(llvq_runtime* rt, const uint8_t* codes_dev, size_t n, int8_t* points_dev,
                        uint8_t* shell_dev, uint8_t* gain_dev, llvq_stream_t stream);
+
+/* The same dump through the decoders the fused GEMV and GEMM kernels run (class search and
+ * the state-table / arrangement-table family decoders, tables in shared memory), so that
+ * their integer output can be diffed block by block on the device
+ * (llvq-cuda/kernels/preflight.cu:39-60, decode_probe). Cap-12 ball only; points_dev
+ * must be 8-byte aligned. */
+int llvq_decode_blocks_fast(llvq_runtime* rt, const uint8_t* codes_dev, size_t n, int8_t* points_dev,
+                            uint8_t* shell_dev, uint8_t* gain_dev, llvq_stream_t stream);
 
 /* Decode n raw indices (up to the cap-13 ball, 48 bits) on the GPU:
  * Indexer::decode, llvq-search/src/index.rs:334-435. shell_dev as above. */

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libllvq_b200.so")
 
-SOURCES = ["api.cu", "codebook.cpp", "rotation.cpp", "archive.cpp"]
+SOURCES = ["api.cu", "codebook.cpp", "tab_tables.cpp", "rotation.cpp", "archive.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--extended-lambda",

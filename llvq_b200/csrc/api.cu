@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <cmath>
 #include <cstring>
+#include <map>
 #include <memory>
 #include <string>
 #include <vector>
@@ -23,6 +24,8 @@
 #include "tp_exchange.cuh"
 #include "gemm_tc.cuh"
 #include "gemv_sorted.cuh"
+#include "gemv_pipe.cuh"
+#include "tab_tables.h"
 #include "kernels_generic.cuh"
 
 using namespace llvq;
@@ -80,10 +83,19 @@ struct llvq_runtime {
     void* d_fcls = nullptr;
     void* d_lut_on = nullptr;
     void* d_lut_off = nullptr;
+    // state-table decoders: the blob the GEMV copies into shared memory, the off-support table
+    TabLayout TL{};
+    void* d_tab_blob = nullptr;
+    void* d_tab_off = nullptr;
+    void* d_tab_on3 = nullptr;
+    // largest dynamic shared-memory size configured so far, per kernel, ON THIS DEVICE (the
+    // attribute is per device: a second runtime on another GPU must raise it again)
+    std::map<const void*, size_t> smem_configured;
     uint64_t fingerprint = 0;
     int max_smem_optin = 0;
     int sm_count = 0;
-    int gemv_ctas_per_sm = 5;      // resident CTAs of the GEMV kernel per SM (its launch bounds)
+    int gemv_ctas_per_sm = 5;      // resident CTAs of the class-sorted GEMV kernel per SM (its launch bounds)
+    int use_sorted_gemv = 0;       // 1: serve GEMVs with the class-sorted kernel instead of the pipelined one
     // split-K partials of the batched GEMM; grown on demand, shared by all matrices of the runtime
     float* gemm_ws = nullptr;
     size_t gemm_ws_bytes = 0;
@@ -121,6 +133,17 @@ struct llvq_matrix {
 };
 
 namespace {
+
+// Raises a kernel's dynamic shared-memory limit on the runtime's device when `bytes` exceeds what
+// was configured there before.
+int ensure_dyn_smem(llvq_runtime* rt, const void* func, size_t bytes) {
+    size_t& have = rt->smem_configured[func];
+    if (bytes > have) {
+        CUDA_TRY(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        have = bytes;
+    }
+    return LLVQ_OK;
+}
 
 size_t generic_smem_bytes(int nb) { return ((size_t)kDim * nb + 32 + (size_t)kGenRows * nb) * sizeof(float); }
 
@@ -160,11 +183,34 @@ int launch_sorted(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s, size_t sme
     return LLVQ_OK;
 }
 
+// The persistent pipelined kernel: one CTA per SM, rows split evenly over the CTAs.
+template <typename XT, typename YT>
+int launch_pipe(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s, PipePlan plan, int probe = 0,
+                unsigned long long* trace = nullptr) {
+    plan.probe = probe;
+    plan.trace = trace;
+    llvq_runtime* rt = m->rt;
+    auto kern = llvq_gemv_pipe_kernel<XT, YT>;
+    int st = ensure_dyn_smem(rt, (const void*)kern, plan.total);
+    if (st) return st;
+    const int grid = (m->d_out + plan.rows_per_cta - 1) / plan.rows_per_cta;
+    kern<<<grid, kPipeThreads, plan.total, s>>>((const unsigned char*)rt->d_tab_blob, (const OffEntry*)rt->d_tab_off,
+                                               (const unsigned long long*)rt->d_tab_on3, rt->TL, m->view(), x, y, plan,
+                                               rt->d_err);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
 template <typename XT, typename YT>
 int launch_gemv(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
     llvq_runtime* rt = m->rt;
-    // the sorted kernel reads the activation with 16-byte loads
+    // the fused kernels read the activation with 16-byte loads
     if ((uintptr_t)x & 15u) return launch_gemv_generic<XT, YT>(m, x, y, s);
+    if (m->nb > 0 && !rt->use_sorted_gemv) {
+        const PipePlan plan = pipe_plan<XT>(rt->TL, rt->max_smem_optin, m->d_out, rt->sm_count);
+        if (plan.tile_max >= kColsMax) return launch_pipe<XT, YT>(m, x, y, s, plan);
+    }
     // 8 rows per CTA: measured against 16, the larger grid wins on every Qwen3 shape.
     const size_t smem8 = sorted_smem_bytes<8>(m->splits > 1 ? 0 : m->nb);  // no code slab when the columns are split
     if (smem8 <= (size_t)rt->max_smem_optin) return launch_sorted<XT, YT, 8>(m, x, y, s, smem8);
@@ -396,6 +442,9 @@ void llvq_runtime_destroy(llvq_runtime* rt) {
     cudaFree(rt->d_fcls);
     cudaFree(rt->d_lut_on);
     cudaFree(rt->d_lut_off);
+    cudaFree(rt->d_tab_blob);
+    cudaFree(rt->d_tab_off);
+    cudaFree(rt->d_tab_on3);
     delete rt;
 }
 
@@ -463,6 +512,19 @@ int llvq_runtime_create(int device, llvq_runtime** out) {
     rt->F.lut_on = (const unsigned int*)rt->d_lut_on;
     rt->F.lut_off = (const unsigned int*)rt->d_lut_off;
     rt->F.lut_shift = kLutShift;
+
+    {
+        TabTablesHost th;
+        build_tab_tables(cb, th);
+        rt->TL = th.layout;
+        RT_TRY(cudaMalloc(&rt->d_tab_blob, th.blob.size()));
+        RT_TRY(cudaMemcpy(rt->d_tab_blob, th.blob.data(), th.blob.size(), cudaMemcpyHostToDevice));
+        RT_TRY(cudaMalloc(&rt->d_tab_off, th.lut_off.size() * sizeof(OffEntry)));
+        RT_TRY(cudaMemcpy(rt->d_tab_off, th.lut_off.data(), th.lut_off.size() * sizeof(OffEntry), cudaMemcpyHostToDevice));
+        RT_TRY(cudaMalloc(&rt->d_tab_on3, th.lut_on3.size() * sizeof(unsigned long long)));
+        RT_TRY(cudaMemcpy(rt->d_tab_on3, th.lut_on3.data(), th.lut_on3.size() * sizeof(unsigned long long), cudaMemcpyHostToDevice));
+        if (th.slow_mass != 0.0) return bail(fail(LLVQ_ERR_CODEBOOK, "decoder tables leave %.3g of the ball unserved", th.slow_mass));
+    }
 
     // Verify the device tables against the published fingerprint: decode the probe
     // indices on the GPU and fold them into the reference's digest.
@@ -588,6 +650,43 @@ int llvq_gemv_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, llvq_stream_t s)
 }
 int llvq_gemv_f32x_h(llvq_matrix* m, const float* x, uint16_t* y, llvq_stream_t s) {
     return gemv_entry<float, __half>(m, x, (__half*)y, s);
+}
+
+int llvq_gemv_probe_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t mode, llvq_stream_t s) {
+    if (!m || !x || !y) return fail(LLVQ_ERR_INVALID, "gemv_probe: null argument");
+    if (mode < 0 || mode > 7) return fail(LLVQ_ERR_INVALID, "gemv_probe: mode %d (0 to 7)", mode);
+    if (((uintptr_t)x & 15u) || ((uintptr_t)y & 1u)) return fail(LLVQ_ERR_INVALID, "gemv_probe: x must be 16-byte aligned");
+    llvq_runtime* rt = m->rt;
+    DeviceGuard g(rt->device);
+    const PipePlan plan = pipe_plan<__half>(rt->TL, rt->max_smem_optin, m->d_out, rt->sm_count);
+    if (m->nb == 0 || plan.tile_max < kColsMax) return fail(LLVQ_ERR_UNSUPPORTED, "gemv_probe: matrix not served by the pipelined kernel");
+    return launch_pipe<__half, __half>(m, (const __half*)x, (__half*)y, (cudaStream_t)s, plan, mode);
+}
+
+int llvq_gemv_trace_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t mode, uint64_t* trace_host, int32_t max_ctas,
+                      int32_t* n_ctas, llvq_stream_t s) {
+    if (!m || !x || !y || !trace_host || !n_ctas || max_ctas <= 0) return fail(LLVQ_ERR_INVALID, "gemv_trace: bad argument");
+    if (mode < 0 || mode > 7) return fail(LLVQ_ERR_INVALID, "gemv_trace: mode %d (0 to 7)", mode);
+    if (((uintptr_t)x & 15u) || ((uintptr_t)y & 1u)) return fail(LLVQ_ERR_INVALID, "gemv_trace: x must be 16-byte aligned");
+    llvq_runtime* rt = m->rt;
+    DeviceGuard g(rt->device);
+    const PipePlan plan = pipe_plan<__half>(rt->TL, rt->max_smem_optin, m->d_out, rt->sm_count);
+    if (m->nb == 0 || plan.tile_max < kColsMax) return fail(LLVQ_ERR_UNSUPPORTED, "gemv_trace: matrix not served by the pipelined kernel");
+    const int grid = (m->d_out + plan.rows_per_cta - 1) / plan.rows_per_cta;
+    unsigned long long* d_trace = nullptr;
+    const size_t bytes = (size_t)grid * kTraceEvents * sizeof(unsigned long long);
+    CUDA_TRY(cudaMalloc((void**)&d_trace, bytes));
+    cudaMemsetAsync(d_trace, 0, bytes, (cudaStream_t)s);
+    int st = launch_pipe<__half, __half>(m, (const __half*)x, (__half*)y, (cudaStream_t)s, plan, mode, d_trace);
+    if (!st) {
+        cudaError_t e = cudaStreamSynchronize((cudaStream_t)s);
+        const int n = grid < max_ctas ? grid : max_ctas;
+        if (e == cudaSuccess) e = cudaMemcpy(trace_host, d_trace, (size_t)n * kTraceEvents * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) st = fail(LLVQ_ERR_CUDA, "gemv_trace: %s", cudaGetErrorString(e));
+        *n_ctas = n;
+    }
+    cudaFree(d_trace);
+    return st;
 }
 
 int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, llvq_stream_t stream) {
@@ -1245,6 +1344,28 @@ int llvq_decode_blocks(llvq_runtime* rt, const uint8_t* codes, size_t n, int8_t*
     DeviceGuard g(rt->device);
     decode_blocks_kernel<<<(unsigned)((n + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
         rt->T, codes, n, (signed char*)points, shell, gain, kN12);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return LLVQ_OK;
+}
+
+int llvq_decode_blocks_fast(llvq_runtime* rt, const uint8_t* codes, size_t n, int8_t* points, uint8_t* shell, uint8_t* gain,
+                            llvq_stream_t stream) {
+    if (!rt) return fail(LLVQ_ERR_INVALID, "decode_blocks_fast: null runtime");
+    if (n == 0) return LLVQ_OK;
+    if (!codes || !points || !shell) return fail(LLVQ_ERR_INVALID, "decode_blocks_fast: null argument");
+    if (n > (size_t)1 << 36) return fail(LLVQ_ERR_INVALID, "decode_blocks_fast: n too large");
+    if ((uintptr_t)points & 7u) return fail(LLVQ_ERR_INVALID, "decode_blocks_fast: points must be 8-byte aligned");
+    DeviceGuard g(rt->device);
+    const size_t smem = rt->TL.total_bytes;
+    int st = ensure_dyn_smem(rt, (const void*)llvq_decode_tab_kernel, smem);
+    if (st) return st;
+    // two CTAs per SM hold the tables; each walks a stride of the blocks
+    const size_t want = (n + kProbeThreads - 1) / kProbeThreads;
+    const unsigned grid = (unsigned)(want < (size_t)2 * rt->sm_count ? want : (size_t)2 * rt->sm_count);
+    llvq_decode_tab_kernel<<<grid, kProbeThreads, smem, (cudaStream_t)stream>>>(
+        (const unsigned char*)rt->d_tab_blob, (const OffEntry*)rt->d_tab_off, (const unsigned long long*)rt->d_tab_on3, rt->TL,
+        codes, n, (signed char*)points, shell, gain);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;

@@ -244,6 +244,36 @@ class FusedRuntime:
                                           gain.data_ptr(), self._stream()))
         return pts, shell, gain
 
+    def forward_probe(self, proj: FusedProj, x, mode: int, out=None):
+        """The f16 GEMV kernel with parts left out (mode 1: no decoders, 2: no class search, 3: neither)."""
+        import torch
+        self._check_x(proj, x, torch.float16)
+        y = out if out is not None else torch.empty(proj.d_out, dtype=torch.float16, device=x.device)
+        check(self.lib.llvq_gemv_probe_h(proj._h, x.data_ptr(), y.data_ptr(), mode, self._stream()))
+        return y
+
+    def forward_trace(self, proj: FusedProj, x, mode: int = 0, max_ctas: int = 256):
+        """One traced launch of the f16 GEMV kernel: (y, stamps[n_ctas, 64] in ns; 0 = event absent)."""
+        import torch
+        self._check_x(proj, x, torch.float16)
+        y = torch.empty(proj.d_out, dtype=torch.float16, device=x.device)
+        stamps = np.zeros((max_ctas, 64), np.uint64)
+        n = C.c_int32(0)
+        check(self.lib.llvq_gemv_trace_h(proj._h, x.data_ptr(), y.data_ptr(), mode, stamps.ctypes.data, max_ctas,
+                                         C.byref(n), self._stream()))
+        return y, stamps[:n.value]
+
+    def decode_blocks_fast(self, codes_dev):
+        """decode_blocks through the decoders the fused kernels run (cap-12 ball)."""
+        import torch
+        n = codes_dev.numel() // 6
+        pts = torch.empty((n, 24), dtype=torch.int8, device=codes_dev.device)
+        shell = torch.empty(n, dtype=torch.uint8, device=codes_dev.device)
+        gain = torch.empty(n, dtype=torch.uint8, device=codes_dev.device)
+        check(self.lib.llvq_decode_blocks_fast(self._h, codes_dev.data_ptr(), n, pts.data_ptr(), shell.data_ptr(),
+                                               gain.data_ptr(), self._stream()))
+        return pts, shell, gain
+
     def decode_indices(self, idx_dev):
         """int64/uint64 CUDA tensor of indices (cap-13 ball) -> (points int8 [n,24], shell u8 [n])."""
         import torch

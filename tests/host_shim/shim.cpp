@@ -9,6 +9,8 @@
 #include "../../llvq_b200/csrc/codebook.cpp"
 #include "../../llvq_b200/csrc/decode_generic.cuh"
 #include "../../llvq_b200/csrc/decode_fast.cuh"
+#include "../../llvq_b200/csrc/tab_tables.cpp"
+#include "../../llvq_b200/csrc/decode_tab.cuh"
 
 using namespace llvq;
 
@@ -104,6 +106,43 @@ void shim_fast_table_sizes(int64_t* out) {
     out[0] = (int64_t)fh.lut_on.size();
     out[1] = (int64_t)fh.lut_off.size();
     out[2] = (int64_t)(fh.slow_mass * 1e12);
+}
+
+// The state-table decoders the fused GEMV and GEMM run: per index the 24 coordinates and the family
+// (0 rare classes, 1 odd/state table, 2 odd/four kinds, 3 even; -1 origin, -2 refused).
+void shim_decode_tab(const uint64_t* idx, int64_t n, int8_t* points, int8_t* fam, float* scale) {
+    static TabTablesHost th;
+    static TabView V;
+    static bool ready = false;
+    HostTables& t = tables();
+    if (!ready) {
+        build_tab_tables(t.cb, th);
+        V.base = th.blob.data();
+        V.lut_off = th.lut_off.data();
+        V.lut_on3 = th.lut_on3.data();
+        V.L = th.layout;
+        ready = true;
+    }
+    for (int64_t b = 0; b < n; ++b) {
+        unsigned int v[6];
+        float s;
+        fam[b] = (int8_t)tab_decode_any(V, idx[b], v, &s);
+        std::memcpy(points + b * kDim, v, kDim);
+        if (scale) scale[b] = s;
+    }
+}
+
+// out: blob bytes, bytes classification needs, off-support entries, mass of the four families * 1e12,
+// mass no decoder serves * 1e15, entries of the three-kind on-support table
+void shim_tab_table_sizes(int64_t* out) {
+    TabTablesHost th;
+    build_tab_tables(tables().cb, th);
+    out[0] = (int64_t)th.layout.total_bytes;
+    out[1] = (int64_t)th.layout.classify_bytes;
+    out[2] = (int64_t)th.lut_off.size();
+    for (int f = 0; f < 4; ++f) out[3 + f] = (int64_t)(th.family_mass[f] * 1e12);
+    out[7] = (int64_t)(th.slow_mass * 1e15);
+    out[8] = (int64_t)th.lut_on3.size();
 }
 
 }  // extern "C"

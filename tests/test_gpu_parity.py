@@ -90,6 +90,42 @@ def test_decode_blocks_edge_records(rt, oracle):
     assert e_pts.shape == (0, 24)
 
 
+def test_fused_kernel_decoders_bit_exact_on_every_class(rt, oracle):
+    """The decoders the GEMV and GEMM kernels run (class search + family decoders, tables in shared memory),
+    dumped on the device: both ends of all 301 classes, their neighbours, 200 draws inside each class."""
+    torch = _torch()
+    from llvq_b200 import synth
+    idx = np.concatenate([probe_indices(oracle, per_class_random=200, cap=12),
+                          np.array([oracle.N12 + 1, (1 << 47) - 1], np.uint64)])
+    gain = (np.arange(idx.size) & 1).astype(np.uint64)
+    codes = synth.pack_codes(idx, gain)
+    pts, shell, gn = rt.decode_blocks_fast(torch.from_numpy(codes).cuda())
+    ref_pts, ref_shell, ref_gain, bad = oracle.decode_codes(codes, use_ref=True)
+    assert bad == 2
+    assert np.array_equal(pts.cpu().numpy(), ref_pts)
+    assert np.array_equal(shell.cpu().numpy(), ref_shell) and shell[-1].item() == 255
+    assert np.array_equal(gn.cpu().numpy(), ref_gain)
+    e_pts, _, _ = rt.decode_blocks_fast(torch.empty(0, dtype=torch.uint8, device="cuda"))
+    assert e_pts.shape == (0, 24)
+
+
+def test_fused_kernel_decoders_bit_exact_on_ten_million_draws(rt, oracle):
+    torch = _torch()
+    from llvq_b200 import synth
+    g = synth.SplitMix64(0xFA57B10C)
+    n = 10_000_000
+    idx = g.take(n) % np.uint64(oracle.N12 + 1)
+    gain = g.take(n) & np.uint64(1)
+    codes = synth.pack_codes(idx, gain)
+    pts, shell, gn = rt.decode_blocks_fast(torch.from_numpy(codes).cuda())
+    # the generic device decoder is pinned to the oracle by the tests above; the oracle itself checks a slice
+    ref_pts, ref_shell, ref_gn = rt.decode_blocks(torch.from_numpy(codes).cuda())
+    assert torch.equal(pts, ref_pts) and torch.equal(shell, ref_shell) and torch.equal(gn, ref_gn)
+    k = 500_000
+    o_pts, o_shell, o_gain, bad = oracle.decode_codes(codes[:6 * k])
+    assert bad == 0 and np.array_equal(pts[:k].cpu().numpy(), o_pts) and np.array_equal(shell[:k].cpu().numpy(), o_shell)
+
+
 @pytest.mark.parametrize("d_out,d_in", [(8, 24), (16, 127), (9, 24 * 7 + 3), (1, 48), (40, 23), (64, 2560), (24, 9728)])
 def test_gemv_f32_small_and_ragged(rt, oracle, d_out, d_in):
     from llvq_b200 import synth

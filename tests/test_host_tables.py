@@ -186,3 +186,50 @@ def test_fast_tables_are_small_and_cover_the_ball(shim):
     shim.shim_fast_table_sizes(out)
     assert out[0] < 10_000 and out[1] < 400_000   # entries of the on / off arrangement tables
     assert out[2] / 1e12 < 1e-3                    # mass left to the generic decoder
+
+
+def _shim_decode_tab(shim, idx):
+    idx = np.ascontiguousarray(idx, np.uint64)
+    pts = np.zeros((idx.size, 24), np.int8)
+    fam = np.zeros(idx.size, np.int8)
+    scale = np.zeros(idx.size, np.float32)
+    shim.shim_decode_tab(idx.ctypes.data_as(C.c_void_p), C.c_int64(idx.size), pts.ctypes.data_as(C.c_void_p),
+                         fam.ctypes.data_as(C.c_void_p), scale.ctypes.data_as(C.c_void_p))
+    return pts, fam, scale
+
+
+def test_state_table_decoders_match_oracle_on_every_class(shim, oracle):
+    """The decoders the fused kernels run (decode_tab.cuh): both ends of all 301 classes, their
+    neighbours and 300 draws inside each; every family, the rare classes included."""
+    idx = probe_indices(oracle, per_class_random=300, cap=12)
+    pts, fam, scale = _shim_decode_tab(shim, idx)
+    ref_pts, ref_shell = _shim_decode(shim, idx, 12)  # generic decoder, itself pinned to the oracle above
+    assert np.array_equal(pts, ref_pts)
+    for k in range(0, idx.size, 41):
+        assert np.array_equal(pts[k], oracle.decode_index(int(idx[k])))
+    assert set(fam.tolist()) >= {-1, 0, 1, 2, 3}
+    ok = ref_shell > 0
+    assert np.allclose(scale[ok], 1.0 / np.sqrt(16.0 * ref_shell[ok]), rtol=1e-6)
+    pts, fam, _ = _shim_decode_tab(shim, np.array([0, oracle.N12 + 1, (1 << 47) - 1, 1 << 47, (1 << 63) + 5], np.uint64))
+    assert fam.tolist() == [-1, -2, -2, -2, -2] and not pts.any()
+
+
+def test_state_table_decoders_match_oracle_on_uniform_draws(shim, oracle):
+    from llvq_b200 import synth
+    g = synth.SplitMix64(0x7AB1E)
+    idx = g.take(600_000) % np.uint64(oracle.N12 + 1)
+    pts, fam, _ = _shim_decode_tab(shim, idx)
+    ref_pts, _, _, bad = oracle.decode_codes(synth.pack_codes(idx, np.zeros_like(idx)))
+    assert bad == 0 and np.array_equal(pts, ref_pts)
+    frac = {f: float((fam == f).mean()) for f in (0, 1, 2, 3)}
+    assert frac[0] < 2e-3 and frac[3] > 0.45 and frac[1] > 0.2 and frac[2] > 0.2
+
+
+def test_state_tables_cover_the_ball_and_fit_shared_memory(shim):
+    out = (C.c_int64 * 9)()
+    shim.shim_tab_table_sizes(out)
+    assert out[0] < 120_000            # bytes of the blob the kernels keep in shared memory
+    assert out[1] < out[0] // 2         # what classification needs lands first
+    assert out[2] < 400_000             # entries of the off-support arrangement table (global memory)
+    assert out[7] == 0                  # no class is left without a decoder
+    assert abs(sum(out[3:7]) / 1e12 - 1.0) < 1e-9
