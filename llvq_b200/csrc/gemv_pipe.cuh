@@ -514,52 +514,66 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
             const unsigned int a0 = pipe_row_shift(mv.codes, tc, mv.nb, sg.contiguous, 0);
             const unsigned int pitch = ((unsigned int)mv.nb * 6u) & 15u;
             const unsigned int probe = (unsigned int)plan.probe;
+            // two groups of 32 blocks per iteration: their table look-ups are independent, so the scheduler can
+            // overlap the shared-memory latency of one with the arithmetic of the other
 #pragma unroll 1
-            for (unsigned int f0 = 32u * warp; f0 < blocks; f0 += 32u * kPipeWarps) {
-                const unsigned int f = f0 + lane;
-                unsigned int fam = 4u;  // 4: nothing to decode
-                if (f < blocks) {
-                    unsigned int ca;  // shared-window address of the record, 2-byte aligned
-                    if (sg.contiguous) {
-                        ca = slab + a0 + 6u * f;
-                    } else {
-                        const unsigned int lr = mdiv ? __umulhi(f, mdiv) : f, lc = f - lr * cols;
-                        ca = slab + lr * sg.row_stride + ((a0 + lr * pitch) & 15u) + 6u * lc;
-                    }
-                    unsigned int h0, h1, h2;
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(h0) : "r"(ca));
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(h1) : "r"(ca + 2u));
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(h2) : "r"(ca + 4u));
-                    const unsigned int hi = __byte_perm(h0, 0, 0x4401);   // bytes 0,1 -> big-endian 16 bits
-                    const unsigned int lo = __byte_perm(h1, h2, 0x0145);  // bytes 2..5 -> big-endian 32 bits
-                    uint2 it = make_uint2(0u, 0u);  // origin or refused index: a block sum of zero
-                    if (probe & 2u) {
-                        // stream probe: the codes are read, nothing is searched or decoded
-                        it.y = lo & hi & 0x80000000u & (lo >> 1);  // keeps the loads alive
-                    } else {
-                        const TabClassified c = tab_classify(T, ((unsigned long long)hi << 32) | lo);
-                        if (c.fam >= 0) {
-                            fam = (unsigned int)c.fam;
-                            it.x = (unsigned int)c.local2;
-                            it.y = (unsigned int)(c.local2 >> 32) | (unsigned int)c.ci << 13;
-                        } else if (c.fam == -2) {
-                            C.error = 1;
+            for (unsigned int f0 = 32u * warp; f0 < blocks; f0 += 64u * kPipeWarps) {
+                unsigned int fams[2], fs[2];
+                uint2 its[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const unsigned int f = f0 + 32u * kPipeWarps * u + lane;
+                    fs[u] = f;
+                    fams[u] = 4u;  // 4: nothing to decode
+                    its[u] = make_uint2(0u, 0u);  // origin or refused index: a block sum of zero
+                    if (f < blocks) {
+                        unsigned int ca;  // shared-window address of the record, 2-byte aligned
+                        if (sg.contiguous) {
+                            ca = slab + a0 + 6u * f;
+                        } else {
+                            const unsigned int lr = mdiv ? __umulhi(f, mdiv) : f, lc = f - lr * cols;
+                            ca = slab + lr * sg.row_stride + ((a0 + lr * pitch) & 15u) + 6u * lc;
+                        }
+                        // the slab is not written during this phase: plain (movable) loads
+                        unsigned int h0, h1, h2;
+                        asm("ld.shared.u16 %0, [%1];" : "=r"(h0) : "r"(ca));
+                        asm("ld.shared.u16 %0, [%1];" : "=r"(h1) : "r"(ca + 2u));
+                        asm("ld.shared.u16 %0, [%1];" : "=r"(h2) : "r"(ca + 4u));
+                        const unsigned int hi = __byte_perm(h0, 0, 0x4401);   // bytes 0,1 -> big-endian 16 bits
+                        const unsigned int lo = __byte_perm(h1, h2, 0x0145);  // bytes 2..5 -> big-endian 32 bits
+                        if (probe & 2u) {
+                            // stream probe: the codes are read, nothing is searched or decoded
+                            its[u].y = lo & hi & 0x80000000u & (lo >> 1);  // keeps the loads alive
+                        } else {
+                            const TabClassified c = tab_classify(T, ((unsigned long long)hi << 32) | lo);
+                            if (c.fam >= 0) {
+                                fams[u] = (unsigned int)c.fam;
+                                its[u].x = (unsigned int)c.local2;
+                                its[u].y = (unsigned int)(c.local2 >> 32) | (unsigned int)c.ci << 13;
+                            } else if (c.fam == -2) {
+                                C.error = 1;
+                            }
                         }
                     }
-                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(items + 8u * f), "r"(it.x), "r"(it.y) : "memory");
                 }
-                // lanes of the same family find each other; the lowest one reserves their list slots
-                const unsigned int v0 = __ballot_sync(0xffffffffu, fam == 0u), v1 = __ballot_sync(0xffffffffu, fam == 1u),
-                                   v2 = __ballot_sync(0xffffffffu, fam == 2u), v3 = __ballot_sync(0xffffffffu, fam == 3u);
-                const unsigned int peers = fam == 0u ? v0 : fam == 1u ? v1 : fam == 2u ? v2 : fam == 3u ? v3 : 1u << lane;
-                const int leader = __ffs(peers) - 1;
-                int slot = 0;
-                if (fam < 4u && lane == leader) slot = atomicAdd(&C.count[fam], __popc(peers));
-                slot = __shfl_sync(0xffffffffu, slot, leader);
-                if (fam < 4u) {
-                    const int2 lg = C.list_lut[fam];
-                    const unsigned int a = (unsigned int)(lg.x + lg.y * (slot + __popc(peers & ((1u << lane) - 1u))));
-                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "h"((unsigned short)f) : "memory");
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const unsigned int f = fs[u], fam = fams[u];
+                    if (f < blocks)
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(items + 8u * f), "r"(its[u].x), "r"(its[u].y) : "memory");
+                    // lanes of the same family find each other; the lowest one reserves their list slots
+                    const unsigned int v0 = __ballot_sync(0xffffffffu, fam == 0u), v1 = __ballot_sync(0xffffffffu, fam == 1u),
+                                       v2 = __ballot_sync(0xffffffffu, fam == 2u), v3 = __ballot_sync(0xffffffffu, fam == 3u);
+                    const unsigned int peers = fam == 0u ? v0 : fam == 1u ? v1 : fam == 2u ? v2 : fam == 3u ? v3 : 1u << lane;
+                    const int leader = __ffs(peers) - 1;
+                    int slot = 0;
+                    if (fam < 4u && lane == leader) slot = atomicAdd(&C.count[fam], __popc(peers));
+                    slot = __shfl_sync(0xffffffffu, slot, leader);
+                    if (fam < 4u) {
+                        const int2 lg = C.list_lut[fam];
+                        const unsigned int a = (unsigned int)(lg.x + lg.y * (slot + __popc(peers & ((1u << lane) - 1u))));
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "h"((unsigned short)f) : "memory");
+                    }
                 }
             }
         }
