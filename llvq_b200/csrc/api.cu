@@ -208,8 +208,8 @@ int launch_gemv(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
     // the fused kernels read the activation with 16-byte loads
     if ((uintptr_t)x & 15u) return launch_gemv_generic<XT, YT>(m, x, y, s);
     if (m->nb > 0 && !rt->use_sorted_gemv) {
-        const PipePlan plan = pipe_plan<XT>(rt->TL, rt->max_smem_optin, m->d_out, rt->sm_count);
-        if (plan.tile_max >= kColsMax) return launch_pipe<XT, YT>(m, x, y, s, plan);
+        const PipePlan plan = pipe_plan<XT>(rt->TL, rt->max_smem_optin, m->d_out, m->nb, rt->sm_count);
+        if (plan.tile_max > 0) return launch_pipe<XT, YT>(m, x, y, s, plan);
     }
     // 8 rows per CTA: measured against 16, the larger grid wins on every Qwen3 shape.
     const size_t smem8 = sorted_smem_bytes<8>(m->splits > 1 ? 0 : m->nb);  // no code slab when the columns are split
@@ -658,8 +658,8 @@ int llvq_gemv_probe_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t mo
     if (((uintptr_t)x & 15u) || ((uintptr_t)y & 1u)) return fail(LLVQ_ERR_INVALID, "gemv_probe: x must be 16-byte aligned");
     llvq_runtime* rt = m->rt;
     DeviceGuard g(rt->device);
-    const PipePlan plan = pipe_plan<__half>(rt->TL, rt->max_smem_optin, m->d_out, rt->sm_count);
-    if (m->nb == 0 || plan.tile_max < kColsMax) return fail(LLVQ_ERR_UNSUPPORTED, "gemv_probe: matrix not served by the pipelined kernel");
+    const PipePlan plan = pipe_plan<__half>(rt->TL, rt->max_smem_optin, m->d_out, m->nb, rt->sm_count);
+    if (m->nb == 0 || plan.tile_max == 0) return fail(LLVQ_ERR_UNSUPPORTED, "gemv_probe: matrix not served by the pipelined kernel");
     return launch_pipe<__half, __half>(m, (const __half*)x, (__half*)y, (cudaStream_t)s, plan, mode);
 }
 
@@ -670,8 +670,8 @@ int llvq_gemv_trace_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t mo
     if (((uintptr_t)x & 15u) || ((uintptr_t)y & 1u)) return fail(LLVQ_ERR_INVALID, "gemv_trace: x must be 16-byte aligned");
     llvq_runtime* rt = m->rt;
     DeviceGuard g(rt->device);
-    const PipePlan plan = pipe_plan<__half>(rt->TL, rt->max_smem_optin, m->d_out, rt->sm_count);
-    if (m->nb == 0 || plan.tile_max < kColsMax) return fail(LLVQ_ERR_UNSUPPORTED, "gemv_trace: matrix not served by the pipelined kernel");
+    const PipePlan plan = pipe_plan<__half>(rt->TL, rt->max_smem_optin, m->d_out, m->nb, rt->sm_count);
+    if (m->nb == 0 || plan.tile_max == 0) return fail(LLVQ_ERR_UNSUPPORTED, "gemv_trace: matrix not served by the pipelined kernel");
     const int grid = (m->d_out + plan.rows_per_cta - 1) / plan.rows_per_cta;
     unsigned long long* d_trace = nullptr;
     const size_t bytes = (size_t)grid * kTraceEvents * sizeof(unsigned long long);

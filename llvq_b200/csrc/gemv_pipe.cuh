@@ -2,7 +2,8 @@
 //
 // One CTA of 1024 threads per SM owns a contiguous range of output rows and keeps
 // the decoder tables (tab_tables.h, 111 KB) in shared memory. Its rows are cut into
-// tiles of at most tile_max blocks (rows x at most kColsMax column blocks, as many
+// tiles of at most tile_max blocks (rows x a chunk of the columns, the whole row where its activation
+// digits fit the digit buffer; as many blocks
 // as the rest of shared memory holds: about 5 000). A tile goes through three
 // phases separated by CTA-wide barriers:
 //
@@ -36,7 +37,7 @@ namespace llvq {
 
 constexpr int kPipeThreads = 1024;
 constexpr int kPipeWarps = kPipeThreads / 32;
-constexpr int kColsMax = 128;         // column blocks per tile
+constexpr int kDigitBytes = 24576;    // shared memory given to the activation digits
 constexpr int kTileRowsMax = 256;     // rows per tile
 constexpr int kStageWarps = 4;        // warps that stage the next tile's digits and row data
 constexpr unsigned int kPipeSpinLimit = 1u << 22;
@@ -60,7 +61,7 @@ struct XDigits<float> {
 // Shared-memory plan of one launch (byte offsets from the start of dynamic shared memory).
 struct PipePlan {
     unsigned int blob;        // decoder tables
-    unsigned int xbuf;        // 2 x kColsMax x (column bytes + 4)
+    unsigned int xbuf;        // one or two digit buffers of cols_max columns (column bytes, then one float each)
     unsigned int ctrl;        // PipeCtrl
     unsigned int items;       // tile_max x 8
     unsigned int lists;       // 2 x tile_max x 2
@@ -68,6 +69,7 @@ struct PipePlan {
     unsigned int slab_bytes;
     unsigned int total;
     int tile_max;             // blocks per tile
+    int cols_max, ncc;        // columns per chunk, column chunks (two digit buffers when ncc > 1)
     int rows_per_cta;
     int probe;                // attribution probes: bit 0 = leave the decoders out, bit 1 = leave the class search out
     unsigned long long* trace;  // per CTA kTraceEvents time stamps (ns), or null
@@ -415,16 +417,17 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
     // ---- rows of this CTA and their tiling ----
     const int cta_r0 = blockIdx.x * plan.rows_per_cta;
     const int cta_nr = min(plan.rows_per_cta, mv.d_out - cta_r0);
-    const int ncc = (mv.nb + kColsMax - 1) / kColsMax;
+    const int ncc = plan.ncc;
     const int tcn = (mv.nb + ncc - 1) / ncc;
     const int fit = max(1, min(kTileRowsMax, tile_max / tcn));
     const int nrg = (cta_nr + fit - 1) / fit;
     const int nt = cta_nr > 0 ? nrg * ncc : 0;
-    // activation digits: two buffers of kColsMax columns (digits, then one float per column); a matrix with a
-    // single column chunk stages its digits once, into the first
-    constexpr unsigned int xbuf_bytes = (unsigned int)kColsMax * (kColBytes + 4);
+    // activation digits: buffers of cols_max columns (digits, then one float per column); a matrix with a
+    // single column chunk stages its digits once, into the only buffer, else the tiles alternate between two
+    const unsigned int xdig_bytes = (unsigned int)plan.cols_max * kColBytes;
+    const unsigned int xbuf_bytes = ((unsigned int)plan.cols_max * (kColBytes + 4) + 15u) & ~15u;  // 16-byte loads
     const unsigned int items = sbase + plan.items, lists = sbase + plan.lists, xbuf = sbase + plan.xbuf,
-                       xscl = xbuf + (unsigned int)kColsMax * kColBytes, slab = sbase + plan.slab;
+                       xscl = xbuf + xdig_bytes, slab = sbase + plan.slab;
     const unsigned int bar_slab = pipe_smem_addr(&C.slab_bar);
 
     // ---- prologue: start the table and code copies, stage the tail activations ----
@@ -648,7 +651,7 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
                         scale = tab_decode_odd4(T, ci, local, V);
                     else
                         scale = tab_decode_rare(T, ci, local, V);
-                    const float dot = pipe_dot<XT>(V, xcur + lc * kColBytes, xcur + (unsigned int)kColsMax * kColBytes + 4u * lc);
+                    const float dot = pipe_dot<XT>(V, xcur + lc * kColBytes, xcur + xdig_bytes + 4u * lc);
                     const float2 cg = C.cent[i & 1][lr];
                     const float part = dot * (scale * (gain ? cg.y : cg.x));
                     asm volatile("st.shared.u32 [%0], %1;" ::"r"(items + 8u * f), "r"(__float_as_uint(part)) : "memory");
@@ -690,16 +693,22 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
     if (tid == 0 && C.error) atomicOr(err_flag, 1);
 }
 
-// Shared-memory plan for a device with `smem_optin` bytes per CTA; tile_max = 0 when the tables
-// leave no room for tiles.
+// Shared-memory plan for a matrix of nb column blocks on a device with `smem_optin` bytes per CTA;
+// tile_max = 0 when the tables leave no room for a tile.
 template <typename XT>
-inline PipePlan pipe_plan(const TabLayout& L, int smem_optin, int d_out, int sm_count) {
+inline PipePlan pipe_plan(const TabLayout& L, int smem_optin, int d_out, int nb, int sm_count) {
     PipePlan p{};
+    constexpr int kPerCol = XDigits<XT>::kColBytes + 4;
+    // the whole row in one chunk when its digits fit, else the fewest equal chunks whose two buffers fit
+    p.ncc = 1;
+    if (nb * kPerCol > kDigitBytes)
+        while (2 * ((nb + p.ncc - 1) / p.ncc) * kPerCol > kDigitBytes) ++p.ncc;
+    p.cols_max = nb > 0 ? (nb + p.ncc - 1) / p.ncc : 1;
     unsigned int at = 0;
     p.blob = at;
     at += (L.total_bytes + 127u) & ~127u;
     p.xbuf = at;
-    at += 2u * (unsigned int)kColsMax * (XDigits<XT>::kColBytes + 4);  // two buffers of digits + one float per column
+    at += (unsigned int)(p.ncc > 1 ? 2 : 1) * (((unsigned int)p.cols_max * kPerCol + 15u) & ~15u);
     p.ctrl = at;
     at += (unsigned int)((sizeof(PipeCtrl) + 15) & ~(size_t)15);
     // per block of a tile: 8 bytes of item, 2 x 2 bytes of lists, 7 bytes of code slab (6 bytes of
@@ -708,6 +717,7 @@ inline PipePlan pipe_plan(const TabLayout& L, int smem_optin, int d_out, int sm_
     int tile_max = room / 19;
     tile_max &= ~31;
     if (tile_max > 65536 - 32) tile_max = 65536 - 32;  // list entries are 16 bits
+    if (tile_max < p.cols_max) tile_max = 0;           // not even one row fits
     p.tile_max = tile_max > 0 ? tile_max : 0;
     p.items = at;
     at += (unsigned int)p.tile_max * 8u;
