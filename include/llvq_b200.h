@@ -107,6 +107,13 @@ int llvq_codebook_golay(uint32_t* out);
  * since the last poll met an index outside the ball (the reference surfaces this
  * as Error::IndexOutOfRange at load, llvq-artifact/src/format.rs:389-392).
  * Synchronises the device. */
+/* Registers per thread, local-memory bytes per thread (0: no spill), static shared memory and binary
+ * version of hot kernel `index` (0 .. until LLVQ_ERR_INVALID), read back with cudaFuncGetAttributes when
+ * the runtime was created. llvq_runtime_create refuses to start if one of them spills, as the reference
+ * does when it loads its kernels (llvq-cuda/src/gpu.rs:413-436, llvq-llm/src/fused_cuda.rs:229-239). */
+int llvq_runtime_kernel_info(llvq_runtime* rt, int32_t index, const char** name, int32_t* regs, int32_t* local_bytes,
+                             int32_t* static_smem_bytes, int32_t* binary_version);
+
 int llvq_runtime_poll_error(llvq_runtime* rt, int32_t* flag);
 
 /* ---- matrices ------------------------------------------------------------ */

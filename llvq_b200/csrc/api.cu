@@ -11,6 +11,7 @@
 #include <cstring>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -68,6 +69,23 @@ struct DeviceGuard {
 
 constexpr int kLutShift = 35;
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device setting: remember, per (device, kernel),
+// the largest size configured so far, so that a second runtime on another GPU raises it again.
+std::mutex g_smem_mu;
+std::map<std::pair<int, const void*>, size_t> g_smem_configured;
+
+int ensure_dyn_smem(const void* func, size_t bytes) {
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_smem_mu);
+    size_t& have = g_smem_configured[{dev, func}];
+    if (bytes > have) {
+        CUDA_TRY(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        have = bytes;
+    }
+    return LLVQ_OK;
+}
+
 }  // namespace
 
 struct llvq_runtime {
@@ -88,9 +106,11 @@ struct llvq_runtime {
     void* d_tab_blob = nullptr;
     void* d_tab_off = nullptr;
     void* d_tab_on3 = nullptr;
-    // largest dynamic shared-memory size configured so far, per kernel, ON THIS DEVICE (the
-    // attribute is per device: a second runtime on another GPU must raise it again)
-    std::map<const void*, size_t> smem_configured;
+    struct KernelInfo {
+        const char* name;
+        int regs, local_bytes, static_smem, binary_version;
+    };
+    std::vector<KernelInfo> kernel_info;  // read back at start-up
     uint64_t fingerprint = 0;
     int max_smem_optin = 0;
     int sm_count = 0;
@@ -134,17 +154,6 @@ struct llvq_matrix {
 
 namespace {
 
-// Raises a kernel's dynamic shared-memory limit on the runtime's device when `bytes` exceeds what
-// was configured there before.
-int ensure_dyn_smem(llvq_runtime* rt, const void* func, size_t bytes) {
-    size_t& have = rt->smem_configured[func];
-    if (bytes > have) {
-        CUDA_TRY(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
-        have = bytes;
-    }
-    return LLVQ_OK;
-}
-
 size_t generic_smem_bytes(int nb) { return ((size_t)kDim * nb + 32 + (size_t)kGenRows * nb) * sizeof(float); }
 
 template <typename XT, typename YT>
@@ -155,7 +164,10 @@ int launch_gemv_generic(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
         return fail(LLVQ_ERR_UNSUPPORTED, "d_in %d needs %zu bytes of shared memory (limit %d)", m->d_in, smem,
                     rt->max_smem_optin);
     auto kern = gemv_generic_kernel<XT, YT>;
-    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    {
+        int st = ensure_dyn_smem((const void*)kern, smem);
+        if (st) return st;
+    }
     const int grid = (m->d_out + kGenRows - 1) / kGenRows;
     kern<<<grid, kGenThreads, smem, s>>>(rt->T, m->view(), x, y, kN12, rt->d_err);
     g_launches++;
@@ -170,10 +182,9 @@ template <typename XT, typename YT, int ROWS>
 int launch_sorted(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s, size_t smem) {
     llvq_runtime* rt = m->rt;
     auto kern = gemv_sorted_kernel<XT, YT, ROWS>;
-    static size_t configured = 0;  // raise the kernel's shared-memory limit only when a larger tile shows up
-    if (smem > configured) {
-        CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
+    {
+        int st = ensure_dyn_smem((const void*)kern, smem);
+        if (st) return st;
     }
     const dim3 grid((m->d_out + ROWS - 1) / ROWS, m->splits);
     kern<<<grid, kThreads, smem, s>>>(rt->F, rt->T, m->view(), x, y, rt->d_err, m->split_range, m->split_ws,
@@ -191,7 +202,7 @@ int launch_pipe(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s, PipePlan pla
     plan.trace = trace;
     llvq_runtime* rt = m->rt;
     auto kern = llvq_gemv_pipe_kernel<XT, YT>;
-    int st = ensure_dyn_smem(rt, (const void*)kern, plan.total);
+    int st = ensure_dyn_smem((const void*)kern, plan.total);
     if (st) return st;
     const int grid = (m->d_out + plan.rows_per_cta - 1) / plan.rows_per_cta;
     kern<<<grid, kPipeThreads, plan.total, s>>>((const unsigned char*)rt->d_tab_blob, (const OffEntry*)rt->d_tab_off,
@@ -395,11 +406,10 @@ struct llvq_tp_ctx {
 template <int HD, int G>
 static int launch_attn(const __half* q, const KvCacheView& kc, const KvCacheView& vc, const long long* pos, __half* out,
                        float* scratch, int n_kv, int splits, cudaStream_t s) {
-    static bool configured = false;  // per instantiation
     const int smem = (int)sizeof(AttnSmem<HD, G>);
-    if (!configured) {
-        CUDA_TRY(cudaFuncSetAttribute(attn_splitkv_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        configured = true;
+    {
+        int st = ensure_dyn_smem((const void*)attn_splitkv_kernel<HD, G>, (size_t)smem);
+        if (st) return st;
     }
     attn_splitkv_kernel<HD, G><<<dim3(n_kv, splits), kAttnThreads, smem, s>>>(q, kc, vc, pos, out, scratch, n_kv);
     if (splits > 1) attn_combine_kernel<HD><<<n_kv * G, HD, splits * sizeof(float), s>>>(scratch, out, splits);
@@ -526,6 +536,25 @@ int llvq_runtime_create(int device, llvq_runtime** out) {
         if (th.slow_mass != 0.0) return bail(fail(LLVQ_ERR_CODEBOOK, "decoder tables leave %.3g of the ball unserved", th.slow_mass));
     }
 
+    // The hot kernels must run out of registers only: a spill to local memory is refused, as the reference
+    // refuses it when it loads its kernels (llvq-cuda/src/gpu.rs:413-436, llvq-llm/src/fused_cuda.rs:229-239).
+    {
+        const struct { const char* name; const void* fn; } hot[] = {
+            {"llvq_gemv_pipe_kernel<f16,f16>", (const void*)llvq_gemv_pipe_kernel<__half, __half>},
+            {"llvq_gemv_pipe_kernel<f32,f16>", (const void*)llvq_gemv_pipe_kernel<float, __half>},
+            {"llvq_gemv_pipe_kernel<f32,f32>", (const void*)llvq_gemv_pipe_kernel<float, float>},
+            {"llvq_decode_tab_kernel", (const void*)llvq_decode_tab_kernel},
+        };
+        for (const auto& k : hot) {
+            cudaFuncAttributes fa;
+            RT_TRY(cudaFuncGetAttributes(&fa, k.fn));
+            rt->kernel_info.push_back({k.name, fa.numRegs, (int)fa.localSizeBytes, (int)fa.sharedSizeBytes, fa.binaryVersion});
+            if (fa.localSizeBytes != 0)
+                return bail(fail(LLVQ_ERR_UNSUPPORTED, "%s uses %zu bytes of local memory per thread (register spill): refused",
+                                 k.name, (size_t)fa.localSizeBytes));
+        }
+    }
+
     // Verify the device tables against the published fingerprint: decode the probe
     // indices on the GPU and fold them into the reference's digest.
     std::vector<uint64_t> probes;
@@ -588,6 +617,19 @@ int llvq_codebook_golay(uint32_t* out) {
     static const Codebook cb;
     if (!out) return fail(LLVQ_ERR_INVALID, "codebook_golay: null out");
     std::memcpy(out, cb.golay, sizeof cb.golay);
+    return LLVQ_OK;
+}
+
+int llvq_runtime_kernel_info(llvq_runtime* rt, int32_t index, const char** name, int32_t* regs, int32_t* local_bytes,
+                             int32_t* static_smem_bytes, int32_t* binary_version) {
+    if (!rt) return fail(LLVQ_ERR_INVALID, "kernel_info: null runtime");
+    if (index < 0 || index >= (int)rt->kernel_info.size()) return fail(LLVQ_ERR_INVALID, "kernel_info: index %d of %zu", index, rt->kernel_info.size());
+    const auto& k = rt->kernel_info[index];
+    if (name) *name = k.name;
+    if (regs) *regs = k.regs;
+    if (local_bytes) *local_bytes = k.local_bytes;
+    if (static_smem_bytes) *static_smem_bytes = k.static_smem;
+    if (binary_version) *binary_version = k.binary_version;
     return LLVQ_OK;
 }
 
@@ -721,10 +763,9 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
         CUDA_TRY(cudaMalloc((void**)&rt->gemm_ws, need));
         rt->gemm_ws_bytes = need;
     }
-    static bool attr_set = false;
-    if (!attr_set) {
-        CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes()));
-        attr_set = true;
+    {
+        int st = ensure_dyn_smem((const void*)gemm_tc_kernel, gemm_smem_bytes());
+        if (st) return st;
     }
     const MatrixView mv = m->view();
     for (int b0 = 0; b0 < batch; b0 += kGMaxN) {
@@ -1021,11 +1062,7 @@ static int rotation_upload(llvq_runtime* rt, RotationTables&& t, llvq_rotation**
     if (e == cudaSuccess)
         e = cudaMemcpy(r->d_signbits, r->t.signbits.data(), r->t.signbits.size() * sizeof(unsigned int), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(r->d_small, r->t.small.data(), r->t.small.size() * sizeof(float), cudaMemcpyHostToDevice);
-    static size_t configured = 0;
-    if (e == cudaSuccess && smem > configured) {
-        e = cudaFuncSetAttribute(rot_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess) configured = smem;
-    }
+    if (e == cudaSuccess && ensure_dyn_smem((const void*)rot_apply_kernel, smem) != LLVQ_OK) e = cudaErrorInvalidValue;
     if (e != cudaSuccess) {
         cudaFree(r->d_signbits);
         cudaFree(r->d_small);
@@ -1103,16 +1140,9 @@ int llvq_rotate_h(llvq_rotation* r, const uint16_t* x, float* xr, int32_t batch,
 
 static int rot_fused_prepare(llvq_rotation* r, int n, const char* who) {
     if (r->t.n != n) return fail(LLVQ_ERR_INVALID, "%s: the rotation is %d wide, the activation %d", who, r->t.n, n);
-    static size_t configured_norm = 0, configured_silu = 0;  // raise each kernel's shared-memory limit once per size
-    if (r->smem > configured_norm) {
-        CUDA_TRY(cudaFuncSetAttribute(add_rmsnorm_rotate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)r->smem));
-        configured_norm = r->smem;
-    }
-    if (r->smem > configured_silu) {
-        CUDA_TRY(cudaFuncSetAttribute(silu_mul_rotate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)r->smem));
-        configured_silu = r->smem;
-    }
-    return LLVQ_OK;
+    int st = ensure_dyn_smem((const void*)add_rmsnorm_rotate_kernel, r->smem);
+    if (!st) st = ensure_dyn_smem((const void*)silu_mul_rotate_kernel, r->smem);
+    return st;
 }
 
 int llvq_op_add_rmsnorm_rotate_h(uint16_t* x, const uint16_t* delta, const uint16_t* w, llvq_rotation* r, float* xr, int32_t n,
@@ -1239,6 +1269,7 @@ int llvq_tp_exchange(llvq_tp_ctx* c, int32_t site, size_t buf_offset, const void
     TpCalls calls{};
     int st = tp_fill_call(calls.c[0], c, site, buf_offset, src, shard_bytes);
     if (st) return st;
+    DeviceGuard g(c->device);
     tp_exchange_kernel<<<1, 32 * kTpMaxWorld, 0, (cudaStream_t)stream>>>(calls);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
@@ -1303,6 +1334,8 @@ static __device__ __align__(256) float g_static_stage[LLVQ_STATIC_MAX_D_IN + LLV
 namespace {
 // In host code `g_static_stage` is only a handle; the device address has to be
 // asked for, once per device, while that device is current.
+// The slots are written without a lock: two threads making the first call on one device both
+// store the same address, so the race is benign.
 constexpr int kMaxDevices = 64;
 float* g_static_ptr[kMaxDevices] = {nullptr};
 }  // namespace
@@ -1358,7 +1391,7 @@ int llvq_decode_blocks_fast(llvq_runtime* rt, const uint8_t* codes, size_t n, in
     if ((uintptr_t)points & 7u) return fail(LLVQ_ERR_INVALID, "decode_blocks_fast: points must be 8-byte aligned");
     DeviceGuard g(rt->device);
     const size_t smem = rt->TL.total_bytes;
-    int st = ensure_dyn_smem(rt, (const void*)llvq_decode_tab_kernel, smem);
+    int st = ensure_dyn_smem((const void*)llvq_decode_tab_kernel, smem);
     if (st) return st;
     // two CTAs per SM hold the tables; each walks a stride of the blocks
     const size_t want = (n + kProbeThreads - 1) / kProbeThreads;

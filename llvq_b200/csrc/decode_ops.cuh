@@ -80,7 +80,8 @@ add_rmsnorm_kernel(__half* __restrict__ x, const __half* __restrict__ delta, con
 
 // Quantise the head_dim values of one head held by a warp (V values per lane, dims lane + 32 j) into
 // groups of 64: group g covers j in {2g, 2g + 1}. u8 affine, scale = range / 255 through f16, bias = min
-// through f16, round to nearest; a group whose scale rounds to zero stores code 0 (kvq.rs:133-160).
+// through f16, round half away from zero (candle's round(), kvq.rs:149-152); a group whose scale rounds to
+// zero stores code 0 (kvq.rs:133-160).
 template <int V>
 __device__ __forceinline__ void quantize_head(const float (&v)[V], unsigned char* q, __half* s, __half* b, int lane) {
 #pragma unroll
@@ -90,8 +91,8 @@ __device__ __forceinline__ void quantize_head(const float (&v)[V], unsigned char
         const __half sh = __float2half_rn((mx - mn) / 255.0f), bh = __float2half_rn(mn);
         const float sf = __half2float(sh), bf = __half2float(bh);
         const float safe = sf > 0.0f ? sf : 1.0f;
-        const float c0 = sf > 0.0f ? fminf(fmaxf(rintf((a0 - bf) / safe), 0.0f), 255.0f) : 0.0f;
-        const float c1 = sf > 0.0f ? fminf(fmaxf(rintf((a1 - bf) / safe), 0.0f), 255.0f) : 0.0f;
+        const float c0 = sf > 0.0f ? fminf(fmaxf(roundf((a0 - bf) / safe), 0.0f), 255.0f) : 0.0f;
+        const float c1 = sf > 0.0f ? fminf(fmaxf(roundf((a1 - bf) / safe), 0.0f), 255.0f) : 0.0f;
         q[lane + 64 * g] = (unsigned char)c0;
         q[lane + 32 + 64 * g] = (unsigned char)c1;
         if (lane == 0) {

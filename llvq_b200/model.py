@@ -56,7 +56,9 @@ def kv_quantize(x):
     mn = mn.half()
     sf = s.float()
     safe = torch.where(sf > 0, sf, torch.ones_like(sf))
-    q = ((g - mn.float()) / safe).round().clamp_(0, 255)
+    t = (g - mn.float()) / safe
+    # candle's round() rounds halves away from zero (kvq.rs:149-152); torch.round would round them to even
+    q = torch.where(t >= 0, torch.floor(t + 0.5), -torch.floor(0.5 - t)).clamp_(0, 255)
     q = torch.where(sf > 0, q, torch.zeros_like(q)).to(torch.uint8)
     return q.flatten(-2), s.squeeze(-1), mn.squeeze(-1)
 
@@ -553,13 +555,17 @@ def tp_rows(cfg: Qwen3Config, world: int, rank: int) -> dict:
 
 def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: int = 0x51, layers: Optional[int] = None,
                     kv_int8: bool = True, fused_ops: bool = True, tp: Optional[TpGroup] = None, dense_prefill_from: int = 1024,
-                    keep_host: bool = True, device_codes: bool = False, rotations: bool = False, embed_q8: bool = False):
+                    keep_host: bool = True, device_codes: bool = False, rotations: bool = False, embed_q8: bool = False,
+                    row_scale_gain: float = 1.0):
     """Random-weight model of benchmark configurations 2 and 4: LLVQ codes for every projection, f16 N(0, 0.02)
     norms and tied embedding (norm weights are 1 + N(0, 0.02) so that activations keep their scale).
     With `tp` every rank draws and uploads only its own rows of each matrix (the same matrices for any
     world size; `device_codes` draws the codes on the GPU, for models too large to draw on the host in
     reasonable time). `rotations` gives every group its incoherence rotation (one per shared activation, seeded
-    per layer and group), as every real artifact has; the benchmark configurationurations are drawn without. Prompts of `dense_prefill_from` rows or more go through a transient dense copy of each
+    per layer and group), as every real artifact has; the benchmark configurations are drawn without.
+    `row_scale_gain` multiplies every row scale (host-drawn matrices only): with the configurations' |N(0, 0.02)| scales
+    a random model's residual stream stays close to the embedding of its input token and greedy decoding repeats one
+    token, which makes a weak test; a gain of some tens lets the blocks dominate and the tokens vary. Prompts of `dense_prefill_from` rows or more go through a transient dense copy of each
     projection and a library GEMM. Returns (model, host matrices per layer or [] when keep_host is off)."""
     import torch
     from . import synth
@@ -585,6 +591,11 @@ def synthetic_model(rt, cfg: Qwen3Config, config_id: int, capacity: int, seed: i
         else:
             m = {n: synth.make_matrix_rows(do, di, synth.matrix_seed(config_id, l, synth.PROJ_IDS[n]), *rows[n], name=f"l{l}.{n}")
                  for n, (do, di) in shp.items()}
+        if row_scale_gain != 1.0:
+            if device_codes:
+                raise ValueError("row_scale_gain applies to host-drawn matrices only")
+            for mat in m.values():
+                mat.row_scales = mat.row_scales * row_scale_gain
         if keep_host:
             mats.append(m)
         blocks.append({"qkv": rt.upload_group([m["q"], m["k"], m["v"]], tail_f16=True), "o": rt.upload(m["o"], tail_f16=True),

@@ -106,6 +106,18 @@ class FusedRuntime:
         check(self.lib.llvq_codebook_info(self._h, shell_cap, C.byref(n), C.byref(size)))
         return n.value, size.value
 
+    def kernel_info(self):
+        """[(name, registers, local bytes, static shared bytes, binary version)] of the hot kernels, as read back
+        from the loaded module when the runtime was created (local bytes are always 0: a spill is refused)."""
+        out, i = [], 0
+        while True:
+            name, regs, loc, smem, ver = C.c_char_p(), C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32()
+            if self.lib.llvq_runtime_kernel_info(self._h, i, C.byref(name), C.byref(regs), C.byref(loc), C.byref(smem),
+                                                 C.byref(ver)) != 0:
+                return out
+            out.append((name.value.decode(), regs.value, loc.value, smem.value, ver.value))
+            i += 1
+
     def poll_range_error(self) -> bool:
         flag = C.c_int32()
         check(self.lib.llvq_runtime_poll_error(self._h, C.byref(flag)))

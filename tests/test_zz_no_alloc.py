@@ -31,6 +31,16 @@ def test_static_staging_matches_the_allocating_entry_point(rt):
         assert L.llvq_gemv_f32_host(proj._h, x.ctypes.data, want.ctypes.data, None) == 0
         assert L.llvq_gemv_f32_host_static(proj._h, x.ctypes.data, got.ctypes.data, None) == 0
         assert np.isfinite(want).all() and np.array_equal(got, want)
+    # the property the entry point exists for: once the first call has resolved the array's address, a call
+    # takes no device memory (cudaMemGetInfo before and after; the allocating entry would not show either, its
+    # buffers being the matrix's own, but a regression that allocates on this path would)
+    import torch
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    x = synth.make_activation(m.d_in, 0x1FF)
+    assert L.llvq_gemv_f32_host_static(proj._h, x.ctypes.data, got.ctypes.data, None) == 0
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
     # a second, smaller matrix right after: nothing stale from the larger one leaks into it
     m2 = synth.make_matrix(16, 48, 0x57A71D)
     p2 = rt.upload(m2)
@@ -39,6 +49,19 @@ def test_static_staging_matches_the_allocating_entry_point(rt):
     assert L.llvq_gemv_f32_host(p2._h, x.ctypes.data, want.ctypes.data, None) == 0
     assert L.llvq_gemv_f32_host_static(p2._h, x.ctypes.data, got.ctypes.data, None) == 0
     assert np.array_equal(got, want)
+
+
+def test_static_staging_at_the_documented_limit(rt):
+    """d_in == LLVQ_STATIC_MAX_D_IN: the activation fills its part of the array up to the first float of y."""
+    from llvq_b200 import _lib, synth
+    L = _lib.load()
+    m = synth.make_matrix(16, 65536, 0x57A71E)
+    proj = rt.upload(m)
+    x = synth.make_activation(m.d_in, 0x300)
+    want, got = np.full(16, np.nan, np.float32), np.full(16, np.nan, np.float32)
+    assert L.llvq_gemv_f32_host(proj._h, x.ctypes.data, want.ctypes.data, None) == 0
+    assert L.llvq_gemv_f32_host_static(proj._h, x.ctypes.data, got.ctypes.data, None) == 0
+    assert np.isfinite(want).all() and np.array_equal(got, want)
 
 
 def test_static_staging_refuses_what_does_not_fit(rt):
