@@ -35,9 +35,17 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# DRAM bytes (read + write) the GEMV kernel moved for the four grouped launches of one layer in the
-# ncu capture summarised in profiles/gemv_sorted_kernel_qwen3_4b_layer.md (5.16 + 3.62 + 14.31 + 7.34 MB).
-NCU_DRAM_BYTES_PER_LAYER = 30.43e6
+def ncu_dram_bytes_per_launch():
+    """DRAM bytes (read + write) per GEMV launch of one Qwen3-4B layer, from the tracked summary of the ncu
+    capture of this kernel (profiles/*.json, written when the profile is refreshed); None when it is missing."""
+    path = os.path.join(ROOT, "profiles", "gemv_dram_traffic.json")
+    try:
+        d = json.load(open(path))
+        return float(d["dram_bytes_per_layer"]) / float(d["launches_per_layer"])
+    except (OSError, KeyError, ValueError):
+        return None
+
+
 MODEL = "qwen3-4b"
 PROJS = ["q", "k", "v", "o", "gate", "up", "down"]
 CONFIG_ID = 1
@@ -197,7 +205,9 @@ def decode_section(rt, torch, prompt_len=128, new_tokens=256, rotations=False, e
 
     held = [{k: blk.pop(k) for k in list(blk) if k.startswith("rot_")} for blk in model.blocks]
     res = {"workload": "qwen3-4b-greedy-decode", "prompt_tokens": prompt_len, "new_tokens": new_tokens, "kv_cache": "int8 g64",
-           "graph": True, "setup_s": setup}
+           "graph": True, "setup_s": setup,
+           "deviations": "norm weights are 1 + N(0, 0.02) (the configuration says N(0, 0.02)) so that activations keep their "
+                         "scale; with random weights the greedy loop settles on very few distinct tokens (see distinct_tokens)"}
     res.update(timed())
     if embed_q8:  # the same model with the tied embedding carried as int8 g64 (the reference's embedq payload)
         from llvq_b200.model import Q8Embedding
@@ -211,6 +221,28 @@ def decode_section(rt, torch, prompt_len=128, new_tokens=256, rotations=False, e
             blk.update(rots)
         res["with_rotations"] = timed()
     return res
+
+
+def verify_before_timing(rt, torch, synth, rank):
+    """Every row of one projection group per shape is checked against the f64 CPU reference before the clock
+    starts, as the reference's kernel bench does (llvq-cuda/src/bin/matvec.rs:582-602): the four grouped launches
+    of layer `rank * 1000` (the first one timed), f16 activations, relative L2 against the 1e-3 of the f16 path."""
+    from oracle import ref
+    layer = synth.make_layer(MODEL, CONFIG_ID, rank * 1000)
+    worst = 0.0
+    for gi, names in enumerate((["q", "k", "v"], ["o"], ["gate", "up"], ["down"])):
+        ms = [layer[n] for n in names]
+        proj = rt.upload_group(ms, tail_f16=True) if len(ms) > 1 else rt.upload(ms[0], tail_f16=True)
+        x = synth.make_activation(ms[0].d_in, 0x2000 + gi, np.float16)
+        y = rt.forward(proj, torch.from_numpy(x).cuda()).float().cpu().numpy().astype(np.float64)
+        want = np.concatenate([ref.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales,
+                                            m.tail.astype(np.float16).astype(np.float32), x.astype(np.float64)) for m in ms])
+        rel = float(np.linalg.norm(y - want) / max(np.linalg.norm(want), 1e-300))
+        proj.free()
+        if not rel <= 1e-3:
+            raise SystemExit(f"bench: group {'|'.join(names)} differs from the CPU reference (relative L2 {rel:.3g}); not timing")
+        worst = max(worst, rel)
+    return {"groups": 4, "rows": int(sum(layer[n].d_out for n in PROJS)), "worst_rel_l2": worst, "tolerance": 1e-3}
 
 
 def run_reference(args):
@@ -231,11 +263,16 @@ def run_reference(args):
     t = sum(times) / len(times)
     val = nbytes / t / 1e9
     sample = "each step = the 7 projections of one layer (4 185 600 blocks) on all host threads"
+    blocks = sum(m.n_blocks for m in mats)
     emit(({
         "impl": "reference", "metric": "dequant_gemv_algorithmic_GBps", "value": val, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": "qwen3-4b-layer-gemv", "sample": sample},
+        # the keys of the GPU arm's config, with this arm's bounded sample (one layer per step instead of 36)
+        "config": {"workload": "qwen3-4b-layer-gemv", "layers_per_step": 1, "projections_per_step": 7,
+                   "launches_per_step": 0, "grouping": "none", "blocks_per_step": blocks,
+                   "algorithmic_bytes_per_step": nbytes, "activations": "f16",
+                   "l2": "host caches; each step decodes 25 MB of codes", "parallelism": "single", "sample": sample},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -448,6 +485,188 @@ def run_tp(args):
         os._exit(0)
 
 
+def tp_block(args, rt, torch, dist, world, rank, local_rank):
+    """benchmark configuration 4 inside the line the driver runs: the Qwen3-14B-architecture model with its output rows
+    sharded over the `world` ranks of this run (q/k/v by heads, the other projections and the tied head by rows; the
+    same matrices at every N), measured twice: `gemv` = one pass over the 4 x 40 projection groups with the gather
+    that follows each of them in a token step (captured in one CUDA graph per rank), `decode` = a 32 768-token
+    prompt into the int8 KV cache, then 128 greedy tokens replayed from a graph. Strong scaling: the job does not
+    change with N, so the N = 1 run of this same function gives the tp1 figures. Before any timing, every rank
+    checks 64 rows of each of its shards against the CPU reference, and rank 0 checks rows it received through the
+    gather against its own unsharded computation of the same rows, bit for bit."""
+    from oracle import ref
+    from llvq_b200 import synth
+    from llvq_b200.model import Qwen3Config, TpGroup, synthetic_model, tp_rows
+    cfg = Qwen3Config.named("qwen3-14b")
+    layers = cfg.layers
+    prompt_len, new_tokens = args.prompt, args.new_tokens
+    t0 = time.perf_counter()
+    model, _ = synthetic_model(rt, cfg, config_id=4, capacity=prompt_len + new_tokens, layers=layers,
+                               tp=TpGroup(peer_lib=rt.lib if args.gather == "peer" else None) if world > 1 else None,
+                               keep_host=False, device_codes=True)
+    torch.cuda.synchronize()
+    setup = time.perf_counter() - t0
+    tp = model.tp
+    hd = cfg.head_dim
+    x_h = torch.from_numpy(synth.make_activation(cfg.hidden, 0x4000, np.float16)).cuda()
+    x_i = torch.from_numpy(synth.make_activation(cfg.inter, 0x4001, np.float16)).cuda()
+    shapes = {"q": (cfg.n_heads * hd, cfg.hidden), "k": (cfg.n_kv * hd, cfg.hidden), "v": (cfg.n_kv * hd, cfg.hidden),
+              "o": (cfg.hidden, cfg.n_heads * hd), "gate": (cfg.inter, cfg.hidden), "up": (cfg.inter, cfg.hidden),
+              "down": (cfg.hidden, cfg.inter)}
+    rows = tp_rows(cfg, world, rank)
+
+    # ---- verification, layer 0 ----
+    def tile_rows(name, lo, n):
+        """rows [lo, lo + n) of layer 0's projection `name`, as the model drew them (tiles of d_out / 8 rows)."""
+        do, di = shapes[name]
+        per = do // 8
+        t = lo // per
+        m = synth.make_matrix_rows_cuda(do, di, synth.matrix_seed(4, 0, synth.PROJ_IDS[name]), t * per, (t + 1) * per,
+                                        device=torch.device("cuda", local_rank))
+        return m.rows(lo - t * per, lo - t * per + n)
+
+    blk0 = model.blocks[0]
+    groups = (("qkv", ["q", "k", "v"], x_h), ("o", ["o"], x_h), ("gate_up", ["gate", "up"], x_h), ("down", ["down"], x_i))
+    worst = 0.0
+    for gname, names, x in groups:
+        y = rt.forward(blk0[gname], x).float().cpu().numpy().astype(np.float64)
+        at = 0
+        for n in names:
+            lo, hi = rows[n]
+            m = tile_rows(n, lo, 64)
+            want = ref.gemv_f64(m.codes, 64, m.d_in, m.centroids, m.row_scales, m.tail.astype(np.float16).astype(np.float32),
+                                x.cpu().numpy().astype(np.float64))
+            rel = float(np.linalg.norm(y[at:at + 64] - want) / max(np.linalg.norm(want), 1e-300))
+            if not rel <= 1e-3:
+                raise SystemExit(f"bench: rank {rank} shard of {n} differs from the CPU reference (relative L2 {rel:.3g})")
+            worst = max(worst, rel)
+            at += hi - lo
+    gathered_ok = None
+    if tp is not None:
+        # rows of the LAST rank's o shard, as they arrive in this rank's gathered buffer, against a local GEMV
+        # of the same rows: rows do not interact, so the bits must agree
+        o_loc = rt.forward(blk0["o"], x_h, out=model._o_loc)
+        tp.gather_into(1, model._o, o_loc)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        lo_last = tp_rows(cfg, world, world - 1)["o"][0]
+        m = tile_rows("o", lo_last, 64)
+        p64 = rt.upload(m, tail_f16=True)
+        mine = rt.forward(p64, x_h)
+        gathered_ok = bool(torch.equal(mine, model._o[lo_last:lo_last + 64]))
+        p64.free()
+        if not gathered_ok:
+            raise SystemExit(f"bench: rank {rank}: gathered rows of the o projection differ from the unsharded GEMV")
+
+    # ---- the GEMV pass: 4 projection groups + 4 gathers per layer, as a token step issues them ----
+    q_loc, i_loc = model.h_loc * hd, model.inter_loc
+
+    def pass_once():
+        for blk in model.blocks:
+            rt.forward(blk["qkv"], x_h, out=model._qkv)
+            if tp is not None:
+                tp.gather_into(0, model._ctx, model._qkv[:q_loc])
+            rt.forward(blk["o"], x_h, out=model._o_loc)
+            if tp is not None:
+                tp.gather_into(1, model._o, model._o_loc)
+            rt.forward(blk["gate_up"], x_h, out=model._gu)
+            if tp is not None:
+                tp.gather_into(2, model._act, model._gu[:i_loc])
+            rt.forward(blk["down"], x_i, out=model._down_loc)
+            if tp is not None:
+                tp.gather_into(3, model._down, model._down_loc)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        pass_once()
+    torch.cuda.current_stream().wait_stream(side)
+    sync_all()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        pass_once()
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    sync_all()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_pass = t.item()
+    job_bytes = job_blocks = 0
+    for names, d_in in ((["q", "k", "v"], cfg.hidden), (["o"], cfg.n_heads * hd), (["gate", "up"], cfg.hidden), (["down"], cfg.inter)):
+        job_bytes += d_in * 2
+        for n in names:
+            do, di = shapes[n]
+            job_bytes += do * (di // 24) * 6 + do * (di % 24) * 4 + do * 8 + do * 2
+            job_blocks += do * (di // 24)
+    job_bytes *= layers
+    job_blocks *= layers
+    collective = ("none" if world == 1 else "peer-memory exchange kernel (stores + flags), 4 per layer" if args.gather == "peer"
+                  else "nccl all_gather_into_tensor, 4 per layer")
+    gemv = {"workload": "qwen3-14b-tp-layer-gemv", "layers_per_pass": layers, "ms_per_pass": ms_pass,
+            "value": job_bytes / (ms_pass * 1e-3) / 1e9, "unit": "GB/s (whole job, algorithmic)",
+            "gblocks_per_s": job_blocks / (ms_pass * 1e-3) / 1e9, "blocks_per_pass": job_blocks,
+            "algorithmic_bytes_per_pass": job_bytes, "collective": collective, "graph": True, "steps": args.steps}
+
+    # ---- the greedy decode ----
+    rng = np.random.default_rng(0x4C0DE)
+    prompt = [int(tk) for tk in rng.integers(0, cfg.vocab, prompt_len)]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    sync_all()
+    ev[0].record()
+    nxt = model.pick(model._rms(model.prefill(prompt), model.final_norm)[0])
+    ev[1].record()
+    torch.cuda.synchronize()
+    model.start_decode(nxt, prompt_len)
+    for _ in range(3):  # the first call captures the graph; the position moves on, as in a real run
+        model._graph_step()
+    model.start_decode(nxt, prompt_len)
+    sync_all()
+    out = [int(nxt)]
+    ev[2].record()
+    while len(out) < new_tokens:
+        model._graph_step()
+        out.append(int(model._tok))  # the per-token read-back of the reference's loop
+    ev[3].record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ev[2].elapsed_time(ev[3]), ev[0].elapsed_time(ev[1])], device="cuda")
+    ranks_agree = True
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        toks = torch.tensor(out, device="cuda")
+        first = toks.clone()
+        dist.broadcast(first, 0)
+        same = torch.tensor([int(torch.equal(first, toks))], device="cuda")
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        ranks_agree = bool(same.item())
+    decode_ms, prefill_ms = t[0].item(), t[1].item()
+    gen = new_tokens - 1
+    decode = {"workload": "qwen3-14b-tp-greedy-decode", "prompt_tokens": prompt_len, "new_tokens": new_tokens,
+              "tok_per_s": gen / (decode_ms * 1e-3), "ms_per_token": decode_ms / gen, "prefill_ms": prefill_ms,
+              "kv_cache": "int8 g64, split-KV attention", "attn_splits": model.attn_splits, "graph": True,
+              "collective": collective + (", 1 per token" if world > 1 else ""), "ranks_agree": ranks_agree,
+              "distinct_tokens": len(set(out)),
+              "token_checksum": int(sum((i + 1) * tk for i, tk in enumerate(out)) % (1 << 31))}
+    peer_errors = tp.peer.poll_error() if tp is not None and tp.peer is not None else None
+    return {"parallelism": f"tp{world}", "scaling": "strong", "setup_s": setup, "gemv": gemv, "decode": decode,
+            "peer_errors": peer_errors,
+            "verified_before_timing": {"shard_rows_vs_cpu_reference": 64 * 7, "worst_rel_l2": worst, "tolerance": 1e-3,
+                                       "gathered_rows_bit_exact": gathered_ok}}
+
+
 _RESULT_FD = None
 
 
@@ -495,6 +714,8 @@ def main():
                     help="time the config-2 decode a second time with the tied embedding / head carried as int8 g64")
     ap.add_argument("--rotations", action="store_true",
                     help="time the config-2 decode a second time with an activation rotation per projection group")
+    ap.add_argument("--no-tp", action="store_true",
+                    help="skip the tensor-parallel block (configuration 4: Qwen3-14B sharded over the ranks of this run)")
     ap.add_argument("--no-groups", action="store_true",
                     help="launch q, k, v and gate, up separately instead of row-concatenated")
     args = ap.parse_args()
@@ -516,6 +737,11 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the measured path")
     torch.cuda.set_device(local_rank)
     if world > 1:
+        # NVLS off for the peer-memory gathers (plain peer stores); the communicator-init lines of NCCL's INFO log
+        # show how many ranks joined
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("NCCL_DEBUG", "INFO")
+        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
         # a rank that dies must end its peers' next collective with an error, not leave them waiting
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=300))
     rt = FusedRuntime(local_rank)
@@ -576,6 +802,8 @@ def main():
             ms = t.item()
         return ms
 
+    verified = verify_before_timing(rt, torch, synth, rank) if rank == 0 else None
+
     for _ in range(max(args.warmup, 3)):
         step_device()
     sampler = ClockSampler(local_rank)
@@ -592,9 +820,19 @@ def main():
     e2e_steps = max(1, min(args.steps, 5))
     ms_e2e = timed(step_e2e, e2e_steps)
 
+    for p in projs:
+        p.free()
+    projs_n = len(projs)
+    del xs_dev, ys_dev
+    torch.cuda.empty_cache()
+    # configuration 4 (tensor parallel over the ranks of this run; tp1 figures at N = 1): every rank takes part
+    tp_res = None if args.no_tp else tp_block(args, rt, torch, dist, world, rank, local_rank)
+
     if rank != 0:
         if world > 1:
-            dist.destroy_process_group()
+            sys.stdout.flush()
+            torch.cuda.synchronize()
+            os._exit(0)
         return
 
     ms_step = ms_total / args.steps
@@ -610,27 +848,27 @@ def main():
     out = {
         "metric": "dequant_gemv_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations in and out; int8 x int8 dot products (dp4a), f32 scaling",
+        "data": "synthetic",
         "config": {"workload": "qwen3-4b-layer-gemv", "layers_per_step": args.layers, "projections_per_step": 7 * args.layers,
-                   "launches_per_step": len(projs), "grouping": "none" if args.no_groups else "q|k|v, o, gate|up, down",
+                   "launches_per_step": projs_n, "grouping": "none" if args.no_groups else "q|k|v, o, gate|up, down",
                    "blocks_per_step": step_blocks, "algorithmic_bytes_per_step": step_bytes, "activations": "f16",
                    "l2": "every step streams %.0f MB of distinct codes (> 126 MB L2)" % (codes_bytes / 1e6),
                    "parallelism": f"replicas x{world}" if world > 1 else "single"},
         "token_equiv_per_s": world * (args.layers / 36.0) / (ms_step * 1e-3),
         "gblocks_per_s": world * step_blocks / (ms_step * 1e-3) / 1e9,
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
-                     "traffic": (NCU_DRAM_BYTES_PER_LAYER * args.layers / len(projs)) if not args.no_groups else None,
-                     "algorithmic_bytes_per_launch": step_bytes / len(projs), "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBps": per_gpu_gbs / 8000.0,
+                     "traffic": ncu_dram_bytes_per_launch() if not args.no_groups else None,
+                     "algorithmic_bytes_per_launch": step_bytes / projs_n, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBps": per_gpu_gbs / 8000.0,
                      "kernel": "gemv", "launches": launches, "avg_launch_us": ms_total * 1e3 / max(launches, 1),
                      "two_term": {"t_bytes_ms": t_bytes * 1e3, "t_alu_ms": t_alu * 1e3,
                                   "frac": max(t_bytes, t_alu) * 1e3 / ms_step, "ops_per_block": 184}},
         "e2e": {"value": e2e_value, "unit": "GB/s",
                 "h2d_bytes_per_step": sum(di * 2 for _, _, _, di in mats_meta),
                 "d2h_bytes_per_step": sum(do * 2 for _, _, do, _ in mats_meta), "ms_per_step": ms_e2e / e2e_steps},
-        "gpu_launches": int(launches), "clocks": clocks, "setup_s": gen_s,
+        "gpu_launches": int(launches), "clocks": clocks, "setup_s": gen_s, "verified_before_timing": verified,
+        "kernels": [{"name": n, "registers": r, "local_bytes": lb} for n, r, lb, _, _ in rt.kernel_info()],
     }
-    for p in projs:
-        p.free()
     # side measurements of the single-GPU configurations (3: batched GEMM, 2: greedy decode) and the CPU baseline
     # belong to the N = 1 line; a multi-rank run reports the replicated GEMV pass only
     if not args.no_gemm and world == 1:
@@ -640,9 +878,15 @@ def main():
     if not args.no_cpu_baseline and world == 1:
         cb, _ = cpu_baseline()
         out["cpu_baseline"] = cb
+    if not args.no_tp:
+        out["tp"] = tp_res
     emit(out)
     if world > 1:
-        dist.destroy_process_group()
+        # every collective has completed and been read on the host; the ranks leave without tearing the process
+        # group down under captured graphs (see run_tp_decode)
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 if __name__ == "__main__":
