@@ -114,6 +114,16 @@ int llvq_codebook_golay(uint32_t* out);
 int llvq_runtime_kernel_info(llvq_runtime* rt, int32_t index, const char** name, int32_t* regs, int32_t* local_bytes,
                              int32_t* static_smem_bytes, int32_t* binary_version);
 
+/* Overlap of consecutive GEMV launches (on by default). The fused GEMV is launched with programmatic stream
+ * serialisation: when the kernel before it in the stream is another fused GEMV, its CTAs take each SM as the
+ * previous launch leaves it and bring the decoder tables and their first codes into shared memory before the
+ * previous launch has finished; they wait for its completion before reading x or writing y. The code stream
+ * and the tables of a matrix must therefore not be written by a kernel still running when a GEMV on it is
+ * launched (llvq_matrix_upload and llvq_runtime_create synchronise, so this holds for everything this library
+ * uploads). on = 0 gives ordinary launches. The reference has no counterpart: it pays 3.6 us per launch
+ * (docs/mesures/a3-graph-2026-08-06.txt:6) or captures the token in a CUDA graph. */
+int llvq_runtime_set_overlap(llvq_runtime* rt, int32_t on);
+
 int llvq_runtime_poll_error(llvq_runtime* rt, int32_t* flag);
 
 /* ---- matrices ------------------------------------------------------------ */

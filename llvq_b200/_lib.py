@@ -111,6 +111,7 @@ _SIGNATURES = {
     "llvq_gemv_h_host_many": (C.c_int, [C.POINTER(HostCall), C.c_int32, C.c_void_p]),
     "llvq_gemv_f32_host_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "llvq_decode_blocks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llvq_runtime_set_overlap": (C.c_int, [C.c_void_p, C.c_int32]),
     "llvq_runtime_kernel_info": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "llvq_gemv_probe_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "llvq_gemv_trace_h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),

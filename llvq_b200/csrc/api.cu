@@ -24,6 +24,7 @@
 #include "rotation.h"
 #include "tp_exchange.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_tab.cuh"
 #include "gemv_sorted.cuh"
 #include "gemv_pipe.cuh"
 #include "tab_tables.h"
@@ -116,6 +117,7 @@ struct llvq_runtime {
     int sm_count = 0;
     int gemv_ctas_per_sm = 5;      // resident CTAs of the class-sorted GEMV kernel per SM (its launch bounds)
     int use_sorted_gemv = 0;       // 1: serve GEMVs with the class-sorted kernel instead of the pipelined one
+    int overlap_launches = 1;      // GEMV launches carry the programmatic-serialisation attribute
     // split-K partials of the batched GEMM; grown on demand, shared by all matrices of the runtime
     float* gemm_ws = nullptr;
     size_t gemm_ws_bytes = 0;
@@ -205,11 +207,23 @@ int launch_pipe(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s, PipePlan pla
     int st = ensure_dyn_smem((const void*)kern, plan.total);
     if (st) return st;
     const int grid = (m->d_out + plan.rows_per_cta - 1) / plan.rows_per_cta;
-    kern<<<grid, kPipeThreads, plan.total, s>>>((const unsigned char*)rt->d_tab_blob, (const OffEntry*)rt->d_tab_off,
-                                               (const unsigned long long*)rt->d_tab_on3, rt->TL, m->view(), x, y, plan,
-                                               rt->d_err);
+    // Launched with programmatic stream serialisation: when the previous kernel of the stream is another launch of
+    // this kernel, the prologue of this one (tables and first codes into shared memory) runs on every SM the previous
+    // launch has left, instead of after its last CTA; the kernel orders itself behind the previous launch with
+    // griddepcontrol.wait before it touches x or y. After any other kernel the attribute changes nothing.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kPipeThreads);
+    cfg.dynamicSmemBytes = plan.total;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = rt->overlap_launches ? 1 : 0;
+    CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, (const unsigned char*)rt->d_tab_blob, (const OffEntry*)rt->d_tab_off,
+                                (const unsigned long long*)rt->d_tab_on3, rt->TL, m->view(), x, y, plan, rt->d_err));
     g_launches++;
-    CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
 }
 
@@ -544,6 +558,7 @@ int llvq_runtime_create(int device, llvq_runtime** out) {
             {"llvq_gemv_pipe_kernel<f32,f16>", (const void*)llvq_gemv_pipe_kernel<float, __half>},
             {"llvq_gemv_pipe_kernel<f32,f32>", (const void*)llvq_gemv_pipe_kernel<float, float>},
             {"llvq_decode_tab_kernel", (const void*)llvq_decode_tab_kernel},
+            {"llvq_gemm_tab_kernel", (const void*)llvq_gemm_tab_kernel},
         };
         for (const auto& k : hot) {
             cudaFuncAttributes fa;
@@ -617,6 +632,12 @@ int llvq_codebook_golay(uint32_t* out) {
     static const Codebook cb;
     if (!out) return fail(LLVQ_ERR_INVALID, "codebook_golay: null out");
     std::memcpy(out, cb.golay, sizeof cb.golay);
+    return LLVQ_OK;
+}
+
+int llvq_runtime_set_overlap(llvq_runtime* rt, int32_t on) {
+    if (!rt) return fail(LLVQ_ERR_INVALID, "set_overlap: null runtime");
+    rt->overlap_launches = on ? 1 : 0;
     return LLVQ_OK;
 }
 
@@ -747,13 +768,16 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
         }
         return LLVQ_OK;
     }
-    const int tiles = (m->d_out + kGM - 1) / kGM;
-    const int chunks = (m->nb + kGKB - 1) / kGKB;
-    // enough CTAs for two per SM: split the column chunks when the row tiles alone are too few
-    int splits = chunks > 0 ? (2 * rt->sm_count + tiles - 1) / tiles : 0;
-    if (splits > chunks) splits = chunks;
-    const int cps = splits > 0 ? (chunks + splits - 1) / splits : 1;
-    splits = chunks > 0 ? (chunks + cps - 1) / cps : 0;
+    // one persistent CTA per SM walks (row tile, column split) units; the plan picks the split
+    GemmTabPlan plan = gemm_tab_plan(rt->TL, m->d_out, m->nb, rt->sm_count);
+    static unsigned long long* dbg_trace = nullptr;  // DEBUG
+    if (getenv("LLVQ_GEMM_TRACE")) {
+        if (!dbg_trace) cudaMalloc((void**)&dbg_trace, 128 * 8);
+        cudaMemset(dbg_trace, 0, 128 * 8);
+    }
+    plan.trace = getenv("LLVQ_GEMM_TRACE") ? dbg_trace : nullptr;
+    const int splits = plan.splits;
+    if ((int)plan.total > rt->max_smem_optin) return fail(LLVQ_ERR_UNSUPPORTED, "gemm_h: %u bytes of shared memory", plan.total);
     const size_t need = (size_t)(splits > 0 ? splits : 1) * kGMaxN * m->d_out * sizeof(float);
     if (need > rt->gemm_ws_bytes) {  // first use or a larger matrix: (re)allocate the workspace
         CUDA_TRY(cudaStreamSynchronize(s));
@@ -764,10 +788,11 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
         rt->gemm_ws_bytes = need;
     }
     {
-        int st = ensure_dyn_smem((const void*)gemm_tc_kernel, gemm_smem_bytes());
+        int st = ensure_dyn_smem((const void*)llvq_gemm_tab_kernel, plan.total);
         if (st) return st;
     }
     const MatrixView mv = m->view();
+    const int grid = plan.units < rt->sm_count ? plan.units : rt->sm_count;
     for (int b0 = 0; b0 < batch; b0 += kGMaxN) {
         const int nb_rows = batch - b0 < kGMaxN ? batch - b0 : kGMaxN;
         GemmArgs ga;
@@ -775,10 +800,12 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
         ga.ws = rt->gemm_ws;
         ga.batch = nb_rows;
         ga.n_pad = (nb_rows + 15) & ~15;
-        ga.chunks_per_split = cps;
+        ga.chunks_per_split = plan.chunks_per_split;
         ga.x_vec_ok = ((m->d_in & 7) == 0 && ((uintptr_t)ga.x & 15u) == 0) ? 1 : 0;
         if (splits > 0) {
-            gemm_tc_kernel<<<dim3(tiles, splits), kGThreads, gemm_smem_bytes(), s>>>(rt->F, rt->T, mv, ga, rt->d_err);
+            llvq_gemm_tab_kernel<<<grid, kTGThreads, plan.total, s>>>((const unsigned char*)rt->d_tab_blob, (const OffEntry*)rt->d_tab_off,
+                                                                      (const unsigned long long*)rt->d_tab_on3, rt->TL, mv, ga, plan,
+                                                                      rt->d_err);
             g_launches++;
             CUDA_TRY(cudaGetLastError());
         }
@@ -786,6 +813,17 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
             mv, ga.x, rt->gemm_ws, (__half*)y + (size_t)b0 * m->d_out, nb_rows, ga.n_pad, splits);
         g_launches++;
         CUDA_TRY(cudaGetLastError());
+    }
+    if (plan.trace) {  // DEBUG
+        unsigned long long h[128];
+        cudaDeviceSynchronize();
+        cudaMemcpy(h, dbg_trace, sizeof h, cudaMemcpyDeviceToHost);
+        fprintf(stderr, "gemm trace splits=%d cps=%d units=%d\n", plan.splits, plan.chunks_per_split, plan.units);
+        for (int w = 0; w < 2; ++w) {
+            fprintf(stderr, " t%d:", w ? 1023 : 0);
+            for (int i = 1; i < 64 && h[64 * w + i]; ++i) fprintf(stderr, " %llu", h[64 * w + i] - h[64 * w]);
+            fprintf(stderr, "\n");
+        }
     }
     return LLVQ_OK;
 }

@@ -51,14 +51,17 @@ struct alignas(1024) GemmSmem {
 };
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ unsigned long long umma_desc_k128(const void* smem_ptr) {
-    const unsigned long long addr = smem_addr(smem_ptr);
+__device__ __forceinline__ unsigned long long umma_desc_k128_at(unsigned long long addr) {
     unsigned long long d = (addr & 0x3FFFFull) >> 4;  // start address, 16-byte units
     d |= 1ull << 16;                                   // leading byte offset (unused with swizzle)
     d |= (1024ull >> 4) << 32;                         // stride byte offset between 8-row groups
     d |= 1ull << 46;                                   // descriptor version of sm_100
     d |= 2ull << 61;                                   // SWIZZLE_128B
     return d;
+}
+
+__device__ __forceinline__ unsigned long long umma_desc_k128(const void* smem_ptr) {
+    return umma_desc_k128_at(smem_addr(smem_ptr));
 }
 
 // Byte offset of 16-byte chunk `gc` (0..23 over the three panels) of row `r` in a swizzled tile.

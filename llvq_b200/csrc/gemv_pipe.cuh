@@ -453,8 +453,11 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
         if (nt > 0) C.tile[0] = geo.next();
         C.geo = geo;
     }
-    if (tid < 32) C.xs_tail[tid] = tid < mv.tail_w ? to_f32<XT>(x[mv.nb * kDim + tid]) : 0.0f;
     __syncthreads();
+    // Programmatic dependent launch: the next launch of the stream may take this SM as soon as this CTA
+    // leaves it, and this launch has come this far while the previous one was still running. Nothing above
+    // or in the copies below reads what a previous kernel writes (tables and codes are constant).
+    asm volatile("griddepcontrol.launch_dependents;");
     if (warp == 0) {
         if (lane == 0) {
             // what classification reads comes first; the decode tables land while the first tile is classified
@@ -470,6 +473,15 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
             pipe_bulk_copy(T.base + L.classify_bytes, blob_g + L.classify_bytes, L.total_bytes - L.classify_bytes,
                            pipe_smem_addr(&C.mbar[1]));
         }
+    }
+    // the activation may be the previous kernel's output, and y may be its input: from here on the previous
+    // launch of the stream has completed and its writes are visible (no-op for an ordinary launch)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // the tail activations: every staging warp writes the same values and reads them back after its own
+    // warp barrier (no CTA barrier stands between here and the staging below)
+    if (warp >= kPipeWarps - kStageWarps) {
+        C.xs_tail[lane] = lane < mv.tail_w ? to_f32<XT>(x[mv.nb * kDim + lane]) : 0.0f;
+        __syncwarp();
     }
     // the first tile's digits and row data are staged while the tables travel
     if (nt > 0 && warp >= kPipeWarps - kStageWarps) {

@@ -118,6 +118,11 @@ class FusedRuntime:
             out.append((name.value.decode(), regs.value, loc.value, smem.value, ver.value))
             i += 1
 
+    def set_overlap(self, on: bool) -> None:
+        """Consecutive fused GEMV launches overlap the next launch's table and code prologue with the previous
+        launch's tail (programmatic dependent launch); on by default, off gives ordinary launches."""
+        check(self.lib.llvq_runtime_set_overlap(self._h, 1 if on else 0))
+
     def poll_range_error(self) -> bool:
         flag = C.c_int32()
         check(self.lib.llvq_runtime_poll_error(self._h, C.byref(flag)))

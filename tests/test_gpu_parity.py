@@ -498,3 +498,46 @@ def test_gemv_column_splits_agree_with_the_oracle(rt, oracle, d_out, d_in):
         assert rel_l2(y.cpu().numpy(), ref) <= TOL_F16, n
         assert torch.equal(rt.forward(proj, x), y)  # the arrival counters are re-armed by the launch itself
     assert not rt.poll_range_error()
+
+
+def test_overlapped_launches_keep_stream_order(rt):
+    """Back-to-back fused GEMVs are launched with programmatic stream serialisation: the next launch's prologue
+    runs while the previous launch drains. A chain in which every launch reads the previous launch's output
+    (and overwrites a buffer the one before it read) gives the bits of ordinary launches, a hundred times over."""
+    torch = _torch()
+    from llvq_b200 import synth
+    dims = [(2560, 4096), (4096, 2560), (2560, 4096), (1024, 2560)]
+    projs = [rt.upload(synth.make_matrix(do, di, 0xD0 + i), tail_f16=True) for i, (do, di) in enumerate(dims)]
+    x0 = torch.from_numpy(synth.make_activation(4096, 5, np.float16)).cuda()
+
+    def chain():
+        bufs = [x0, torch.empty(2560, dtype=torch.float16, device="cuda"), torch.empty(4096, dtype=torch.float16, device="cuda")]
+        a = rt.forward(projs[0], bufs[0], out=bufs[1])
+        b = rt.forward(projs[1], a, out=bufs[2])
+        b.mul_(0.01)  # an ordinary kernel between two launches
+        c = rt.forward(projs[2], b, out=bufs[1])   # overwrites what the second launch read
+        c.mul_(0.01)
+        return rt.forward(projs[3], c).clone()
+
+    try:
+        rt.set_overlap(False)
+        want = chain()
+        torch.cuda.synchronize()
+        rt.set_overlap(True)
+        for _ in range(100):
+            assert torch.equal(chain(), want)
+        # without the ordinary kernels in between: launch directly behind launch
+        ys = [torch.empty(1024, dtype=torch.float16, device="cuda") for _ in range(50)]
+        xin = torch.from_numpy(synth.make_activation(2560, 6, np.float16)).cuda()
+        rt.set_overlap(False)
+        ref = rt.forward(projs[3], xin).clone()
+        rt.set_overlap(True)
+        for y in ys:
+            rt.forward(projs[3], xin, out=y)
+        torch.cuda.synchronize()
+        assert all(torch.equal(y, ref) for y in ys)
+    finally:
+        rt.set_overlap(True)
+        for p in projs:
+            p.free()
+    assert not rt.poll_range_error()
