@@ -769,13 +769,7 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
         return LLVQ_OK;
     }
     // one persistent CTA per SM walks (row tile, column split) units; the plan picks the split
-    GemmTabPlan plan = gemm_tab_plan(rt->TL, m->d_out, m->nb, rt->sm_count);
-    static unsigned long long* dbg_trace = nullptr;  // DEBUG
-    if (getenv("LLVQ_GEMM_TRACE")) {
-        if (!dbg_trace) cudaMalloc((void**)&dbg_trace, 128 * 8);
-        cudaMemset(dbg_trace, 0, 128 * 8);
-    }
-    plan.trace = getenv("LLVQ_GEMM_TRACE") ? dbg_trace : nullptr;
+    const GemmTabPlan plan = gemm_tab_plan(rt->TL, m->d_out, m->nb, rt->sm_count);
     const int splits = plan.splits;
     if ((int)plan.total > rt->max_smem_optin) return fail(LLVQ_ERR_UNSUPPORTED, "gemm_h: %u bytes of shared memory", plan.total);
     const size_t need = (size_t)(splits > 0 ? splits : 1) * kGMaxN * m->d_out * sizeof(float);
@@ -813,17 +807,6 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
             mv, ga.x, rt->gemm_ws, (__half*)y + (size_t)b0 * m->d_out, nb_rows, ga.n_pad, splits);
         g_launches++;
         CUDA_TRY(cudaGetLastError());
-    }
-    if (plan.trace) {  // DEBUG
-        unsigned long long h[128];
-        cudaDeviceSynchronize();
-        cudaMemcpy(h, dbg_trace, sizeof h, cudaMemcpyDeviceToHost);
-        fprintf(stderr, "gemm trace splits=%d cps=%d units=%d\n", plan.splits, plan.chunks_per_split, plan.units);
-        for (int w = 0; w < 2; ++w) {
-            fprintf(stderr, " t%d:", w ? 1023 : 0);
-            for (int i = 1; i < 64 && h[64 * w + i]; ++i) fprintf(stderr, " %llu", h[64 * w + i] - h[64 * w]);
-            fprintf(stderr, "\n");
-        }
     }
     return LLVQ_OK;
 }

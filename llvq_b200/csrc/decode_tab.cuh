@@ -388,6 +388,29 @@ LLVQ_HD float tab_decode_rare(const TabView& T, int ci, unsigned long long local
     return 0.0f;
 }
 
+#if defined(__CUDACC__)
+// The rare classes (0.07 % of the blocks) out of line, for the kernels: inlined, the four rare decoders add
+// their registers and their code to the hot loop. Arguments and results travel by value (registers), not through a stack frame.
+struct TabRareBlock {
+    unsigned int v0, v1, v2, v3, v4, v5;
+    float scale;
+};
+__device__ __noinline__ TabRareBlock tab_decode_rare_call(unsigned int tab_base, const OffEntry* lut_off,
+                                                          const unsigned long long* lut_on3, TabLayout L, int ci,
+                                                          unsigned long long local) {
+    TabView T;
+    T.base = tab_base;
+    T.lut_off = lut_off;
+    T.lut_on3 = lut_on3;
+    T.L = L;
+    unsigned int V[6];
+    TabRareBlock r;
+    r.scale = tab_decode_rare(T, ci, local, V);
+    r.v0 = V[0]; r.v1 = V[1]; r.v2 = V[2]; r.v3 = V[3]; r.v4 = V[4]; r.v5 = V[5];
+    return r;
+}
+#endif
+
 // Decode one cap-12 index with whichever routine its class calls for. Returns the family
 // (TabFamily; -1 origin, -2 refused index).
 LLVQ_HD int tab_decode_any(const TabView& T, unsigned long long idx, unsigned int* V, float* scale) {

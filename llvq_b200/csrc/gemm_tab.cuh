@@ -50,7 +50,6 @@ struct GemmTabPlan {
     unsigned int ctrl;
     unsigned int total;
     int units, splits, chunks_per_split, row_tiles;
-    unsigned long long* trace;  // DEBUG
 };
 
 // Position of a CTA in its sequence of chunks: unit = row tile * splits + split.
@@ -100,27 +99,6 @@ __device__ __forceinline__ unsigned int gemm_tab_list_slot(unsigned int lists, u
     const unsigned int arr = lists + ((fam == kFamOdd3 || fam == kFamEven) ? 2u * kGItems : 0u);
     const bool front = fam == kFamOdd4 || fam == kFamEven;
     return arr + 2u * (unsigned int)(front ? i : kGItems - 1 - i);
-}
-
-// The rare classes (0.07 % of the blocks) stay out of line: inlined, their register needs add to the loop's
-// and the kernel spills. Arguments and results travel by value (registers), not through a stack frame.
-struct GemmTabBlock {
-    unsigned int v0, v1, v2, v3, v4, v5;
-    float scale;
-};
-__device__ __noinline__ GemmTabBlock gemm_tab_decode_rare(unsigned int tab_base, const OffEntry* lut_off,
-                                                          const unsigned long long* lut_on3, TabLayout L, int ci,
-                                                          unsigned long long local) {
-    TabView T;
-    T.base = tab_base;
-    T.lut_off = lut_off;
-    T.lut_on3 = lut_on3;
-    T.L = L;
-    unsigned int V[6];
-    GemmTabBlock r;
-    r.scale = tab_decode_rare(T, ci, local, V);
-    r.v0 = V[0]; r.v1 = V[1]; r.v2 = V[2]; r.v3 = V[3]; r.v4 = V[4]; r.v5 = V[5];
-    return r;
 }
 
 __global__ void __launch_bounds__(kTGThreads, 1)
@@ -321,8 +299,6 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
     }
     
 
-    int tn = 0; auto stamp = [&](){ if (P.trace && blockIdx.x == 0 && (tid == 0 || tid == 1023) && tn < 64) P.trace[(tid ? 64 : 0) + tn] = pipe_now_ns(); ++tn; };
-    stamp();
     int q = 0;  // chunks issued so far = groups of MMAs committed on mbar_mma
     for (; ok && C.it[q % 3].valid; ++q) {
         const GemmTabIt& cur = C.it[q % 3];
@@ -333,7 +309,6 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        stamp();
         if (tid == 0) {  // counters and position of the chunk after the next one
 #pragma unroll
             for (int k = 0; k < 4; ++k) C.count[(q + 2) % 3][k] = 0;
@@ -358,7 +333,6 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
         // the finished unit's accumulators are overwritten by this chunk's first MMA (after the next barrier)
         if (prev_last) store_unit();
 
-        stamp();
         // ---- decode: one family per batch of 32 blocks, into the A tile ----
         // (the family counts are re-read from shared memory for every batch: nothing but the ticket stays in
         // registers across a decoder)
@@ -398,7 +372,7 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
                     scale = tab_decode_odd4(T, ci, local, V);
                 else
                     {
-                    const GemmTabBlock r = gemm_tab_decode_rare(T.base, lut_off, lut_on3, L, ci, local);
+                    const TabRareBlock r = tab_decode_rare_call(T.base, lut_off, lut_on3, L, ci, local);
                     V[0] = r.v0; V[1] = r.v1; V[2] = r.v2; V[3] = r.v3; V[4] = r.v4; V[5] = r.v5;
                     scale = r.scale;
                 }
@@ -425,7 +399,6 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
             }
         }
 
-        stamp();
         // ---- classify the next chunk while the other warps finish their batches ----
         const GemmTabIt& nxt = C.it[(q + 1) % 3];
         bool landed = true;
@@ -434,7 +407,6 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
             landed = classify(nxt, q + 1);
         }
 
-        stamp();
         // generic-proxy writes must be visible to the tensor core's asynchronous reads
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         ok = __syncthreads_and(landed);
@@ -470,7 +442,6 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
                              pipe_smem_addr(&C.mbar_mma))
                          : "memory");
         }
-        stamp();
         prev_last = cur.last != 0;
     }
 

@@ -37,9 +37,19 @@ namespace llvq {
 
 constexpr int kPipeThreads = 1024;
 constexpr int kPipeWarps = kPipeThreads / 32;
+// The CTA runs as kPipeGroups independent groups of warps that share the decoder tables: each group owns a
+// part of the CTA's rows, its own tile buffers and its own named barrier, so the groups drift out of phase
+// and one group's decode phase fills the issue slots another leaves empty while it classifies, sums rows or
+// waits at a barrier (what two CTAs per SM would do, if two copies of the tables fitted).
+#ifndef LLVQ_PIPE_GROUPS
+#define LLVQ_PIPE_GROUPS 2
+#endif
+constexpr int kPipeGroups = LLVQ_PIPE_GROUPS;
+constexpr int kGroupThreads = kPipeThreads / kPipeGroups;
+constexpr int kGroupWarps = kGroupThreads / 32;
 constexpr int kDigitBytes = 24576;    // shared memory given to the activation digits
-constexpr int kTileRowsMax = 256;     // rows per tile
-constexpr int kStageWarps = 4;        // warps that stage the next tile's digits and row data
+constexpr int kTileRowsMax = 128;     // rows per tile
+constexpr int kStageWarps = 4 / kPipeGroups > 0 ? 4 / kPipeGroups : 1;  // warps of a group that stage the next tile's digits and row data
 constexpr unsigned int kPipeSpinLimit = 1u << 22;
 
 template <typename XT>
@@ -117,20 +127,39 @@ struct PipeGeom {
     }
 };
 
-struct alignas(16) PipeCtrl {
+struct alignas(16) PipeShared {
     unsigned long long mbar[2];       // decoder tables: classification part, decode part
+    int error;
+    float xs_tail[32];
+};
+struct alignas(16) PipeCtrl {         // one per group
     unsigned long long slab_bar;      // code slab
     int ticket;
     int count[4];                     // items per family in the tile
     int2 list_lut[4];                 // per family: shared-window address of list entry 0, byte step to the next entry
-    int error;
-    float xs_tail[32];
     float rowacc[kTileRowsMax];
     float2 cent[2][kTileRowsMax];     // gain centroids of the rows of tile k at cent[k & 1]
     float2 rowfix[2][kTileRowsMax];   // (row scale, tail-column product) of the rows of tile k at rowfix[k & 1]
-    PipeTile tile[2];                 // geometry of tile k at tile[k & 1], written by thread 0 one tile ahead
-    PipeGeom geo;                     // stepped by thread 0 only
+    PipeTile tile[2];                 // geometry of tile k at tile[k & 1], written by the group's thread 0 one tile ahead
+    PipeGeom geo;                     // stepped by the group's thread 0 only
 };
+
+// Barrier over the kGroupThreads threads of group g (named barrier g + 1; barrier 0 stays the CTA's).
+__device__ __forceinline__ void pipe_group_sync(int g) {
+    asm volatile("bar.sync %0, %1;" ::"r"(g + 1), "n"(kGroupThreads) : "memory");
+}
+__device__ __forceinline__ bool pipe_group_sync_and(int g, bool pred) {
+    unsigned int r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 p, %2, 0;\n\t"
+        "bar.red.and.pred q, %1, %3, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"(g + 1), "r"((unsigned int)pred), "n"(kGroupThreads)
+        : "memory");
+    return r != 0;
+}
 
 __device__ __forceinline__ unsigned long long pipe_now_ns() {
     unsigned long long t;
@@ -356,15 +385,14 @@ __device__ __forceinline__ int2 pipe_list_geom(unsigned int lists, int tile_max,
     return make_int2((int)(front ? arr : arr + 2u * (unsigned int)(tile_max - 1)), front ? 2 : -2);
 }
 
-// Staging of a tile's per-column and per-row data by the warps `first_warp` .. : activation digits of
-// its columns (only when the columns differ from the last tile's), centroids of its rows and, for the
-// last column chunk of a row, its row scale and tail-column product.
+// Staging of a tile's per-column and per-row data: activation digits of column c of the tile, and for row c
+// of the tile its centroids and, for the last column chunk of a row, its row scale and tail-column product.
 template <typename XT>
-__device__ __forceinline__ void pipe_stage_tile(const MatrixView& mv, const XT* __restrict__ x, const PipeTile& t, PipeCtrl& C,
-                                                int slot, unsigned int xbuf, unsigned int xscl, int c) {
+__device__ __forceinline__ void pipe_stage_col(const XT* __restrict__ x, const PipeTile& t, unsigned int xbuf, unsigned int xscl, int c) {
     constexpr int kColBytes = XDigits<XT>::kColBytes;
-    if (c < t.cols && (t.rg_first || !t.same_cols))
-        pipe_prep_column<XT>(x + (size_t)(t.col0 + c) * kDim, xbuf + c * kColBytes, xscl + 4u * c);
+    if (c < t.cols) pipe_prep_column<XT>(x + (size_t)(t.col0 + c) * kDim, xbuf + c * kColBytes, xscl + 4u * c);
+}
+__device__ __forceinline__ void pipe_stage_row(const MatrixView& mv, const PipeTile& t, PipeCtrl& C, const float* xs_tail, int slot, int c) {
     if (c < t.rows) {
         const int r = t.row0 + c;
         C.cent[slot][c] = __ldg(mv.cent + r);
@@ -381,7 +409,7 @@ __device__ __forceinline__ void pipe_stage_tile(const MatrixView& mv, const XT* 
             float tv = 0.0f;
 #pragma unroll
             for (int k = 0; k < kDim - 1; ++k)
-                if (k < mv.tail_w) tv = fmaf(w[k], C.xs_tail[k], tv);
+                if (k < mv.tail_w) tv = fmaf(w[k], xs_tail[k], tv);
             C.rowfix[slot][c] = make_float2(__ldg(mv.rscale + r), tv);
         }
     }
@@ -395,9 +423,12 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
                       int* __restrict__ err_flag) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const unsigned int sbase = pipe_smem_addr(smem_raw);
-    PipeCtrl& C = *reinterpret_cast<PipeCtrl*>(smem_raw + plan.ctrl);
     constexpr int kColBytes = XDigits<XT>::kColBytes;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
+    const int grp = tid / kGroupThreads;                      // this thread's group
+    const int gt = tid - grp * kGroupThreads, lane = gt & 31, warp = gt >> 5;  // position inside the group
+    PipeShared& S = *reinterpret_cast<PipeShared*>(smem_raw + plan.ctrl);
+    PipeCtrl& C = reinterpret_cast<PipeCtrl*>(smem_raw + plan.ctrl + sizeof(PipeShared))[grp];
     const int tile_max = plan.tile_max;
 
     TabView T;
@@ -405,7 +436,7 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
     T.lut_off = lut_off;
     T.lut_on3 = lut_on3;
     T.L = L;
-    // time stamps of thread 0: entry, tables landed, then the end of every phase
+    // time stamps of thread 0 (group 0): entry, tables landed, then the end of every phase
     unsigned long long* trace = plan.trace ? plan.trace + (size_t)blockIdx.x * kTraceEvents : nullptr;
     int trace_n = 0;
     auto stamp = [&]() {
@@ -414,38 +445,47 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
     };
     stamp();
 
-    // ---- rows of this CTA and their tiling ----
+    // ---- rows of this CTA, of this group, and their tiling ----
     const int cta_r0 = blockIdx.x * plan.rows_per_cta;
-    const int cta_nr = min(plan.rows_per_cta, mv.d_out - cta_r0);
+    const int cta_nr = max(0, min(plan.rows_per_cta, mv.d_out - cta_r0));
+    const int rpg = (cta_nr + kPipeGroups - 1) / kPipeGroups;
+    const int grp_r0 = cta_r0 + grp * rpg;
+    const int grp_nr = max(0, min(rpg, cta_r0 + cta_nr - grp_r0));
     const int ncc = plan.ncc;
     const int tcn = (mv.nb + ncc - 1) / ncc;
     const int fit = max(1, min(kTileRowsMax, tile_max / tcn));
-    const int nrg = (cta_nr + fit - 1) / fit;
-    const int nt = cta_nr > 0 ? nrg * ncc : 0;
-    // activation digits: buffers of cols_max columns (digits, then one float per column); a matrix with a
-    // single column chunk stages its digits once, into the only buffer, else the tiles alternate between two
+    const int nrg = (grp_nr + fit - 1) / fit;
+    const int nt = grp_nr > 0 ? nrg * ncc : 0;
+    // activation digits: buffers of cols_max columns (digits, then one float per column). A matrix with a single
+    // column chunk stages its digits once for the whole CTA; otherwise every group alternates between two
+    // buffers of its own.
     const unsigned int xdig_bytes = (unsigned int)plan.cols_max * kColBytes;
     const unsigned int xbuf_bytes = ((unsigned int)plan.cols_max * (kColBytes + 4) + 15u) & ~15u;  // 16-byte loads
-    const unsigned int items = sbase + plan.items, lists = sbase + plan.lists, xbuf = sbase + plan.xbuf,
-                       xscl = xbuf + xdig_bytes, slab = sbase + plan.slab;
+    const unsigned int items = sbase + plan.items + (unsigned int)grp * (unsigned int)tile_max * 8u,
+                       lists = sbase + plan.lists + (unsigned int)grp * (unsigned int)tile_max * 4u,
+                       xbuf = sbase + plan.xbuf + (ncc > 1 ? (unsigned int)grp * 2u * xbuf_bytes : 0u), xscl = xbuf + xdig_bytes,
+                       slab = sbase + plan.slab + (unsigned int)grp * plan.slab_bytes;
     const unsigned int bar_slab = pipe_smem_addr(&C.slab_bar);
+    bool failed = false;
 
     // ---- prologue: start the table and code copies, stage the tail activations ----
-    if (tid < 4) C.list_lut[tid] = pipe_list_geom(lists, tile_max, (unsigned int)tid);
+    if (gt < 4) C.list_lut[gt] = pipe_list_geom(lists, tile_max, (unsigned int)gt);
     if (tid == 0) {
-        C.error = 0;
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&C.mbar[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&C.mbar[1])));
+        S.error = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&S.mbar[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&S.mbar[1])));
+    }
+    if (gt == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_slab));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         PipeGeom geo;
         geo.nb = mv.nb;
-        geo.r0 = cta_r0;
-        geo.nr = cta_nr;
+        geo.r0 = grp_r0;
+        geo.nr = grp_nr;
         geo.ncc = ncc;
         geo.tcn = tcn;
         geo.nrg = nrg;
-        geo.rpt = (cta_nr + nrg - 1) / max(nrg, 1);
+        geo.rpt = (grp_nr + nrg - 1) / max(nrg, 1);
         geo.mdiv_full = PipeGeom::reciprocal(tcn);
         geo.mdiv_last = PipeGeom::reciprocal(mv.nb - (ncc - 1) * tcn);
         geo.rg = 0;
@@ -458,51 +498,61 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
     // leaves it, and this launch has come this far while the previous one was still running. Nothing above
     // or in the copies below reads what a previous kernel writes (tables and codes are constant).
     asm volatile("griddepcontrol.launch_dependents;");
-    if (warp == 0) {
+    if (tid < 32) {
         if (lane == 0) {
-            // what classification reads comes first; the decode tables land while the first tile is classified
-            pipe_expect_tx(pipe_smem_addr(&C.mbar[0]), L.classify_bytes);
-            pipe_bulk_copy(T.base, blob_g, L.classify_bytes, pipe_smem_addr(&C.mbar[0]));
+            // what classification reads comes first; the decode tables land while the first tiles are classified
+            pipe_expect_tx(pipe_smem_addr(&S.mbar[0]), L.classify_bytes);
+            pipe_bulk_copy(T.base, blob_g, L.classify_bytes, pipe_smem_addr(&S.mbar[0]));
         }
-        if (nt > 0) {
-            const PipeTile t0 = C.tile[0];
-            pipe_issue_slab(mv.codes, t0, mv.nb, slab, bar_slab, lane);
-        }
-        if (lane == 0) {
-            pipe_expect_tx(pipe_smem_addr(&C.mbar[1]), L.total_bytes - L.classify_bytes);
-            pipe_bulk_copy(T.base + L.classify_bytes, blob_g + L.classify_bytes, L.total_bytes - L.classify_bytes,
-                           pipe_smem_addr(&C.mbar[1]));
-        }
+    }
+    if (warp == 0 && nt > 0) {
+        const PipeTile t0 = C.tile[0];
+        pipe_issue_slab(mv.codes, t0, mv.nb, slab, bar_slab, lane);
+    }
+    if (tid == 0) {
+        pipe_expect_tx(pipe_smem_addr(&S.mbar[1]), L.total_bytes - L.classify_bytes);
+        pipe_bulk_copy(T.base + L.classify_bytes, blob_g + L.classify_bytes, L.total_bytes - L.classify_bytes,
+                       pipe_smem_addr(&S.mbar[1]));
     }
     // the activation may be the previous kernel's output, and y may be its input: from here on the previous
     // launch of the stream has completed and its writes are visible (no-op for an ordinary launch)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // the tail activations: every staging warp writes the same values and reads them back after its own
     // warp barrier (no CTA barrier stands between here and the staging below)
-    if (warp >= kPipeWarps - kStageWarps) {
-        C.xs_tail[lane] = lane < mv.tail_w ? to_f32<XT>(x[mv.nb * kDim + lane]) : 0.0f;
+    if (warp >= kGroupWarps - kStageWarps) {
+        S.xs_tail[lane] = lane < mv.tail_w ? to_f32<XT>(x[mv.nb * kDim + lane]) : 0.0f;
         __syncwarp();
     }
     // the first tile's digits and row data are staged while the tables travel
-    if (nt > 0 && warp >= kPipeWarps - kStageWarps) {
-        const PipeTile t0 = C.tile[0];
-        for (int c = 32 * (kPipeWarps - 1 - warp) + lane; c < max(t0.cols, t0.rows); c += 32 * kStageWarps)
-            pipe_stage_tile<XT>(mv, x, t0, C, 0, xbuf, xscl, c);
+    if (warp >= kGroupWarps - kStageWarps) {
+        const int sw = kGroupWarps - 1 - warp;  // 0 .. kStageWarps - 1
+        if (ncc == 1) {
+            // one column chunk: the digits of the whole row, once, by the staging warps of all groups together
+            PipeTile all;
+            all.col0 = 0;
+            all.cols = mv.nb;
+            for (int c = 32 * (grp * kStageWarps + sw) + lane; c < mv.nb; c += 32 * kStageWarps * kPipeGroups)
+                pipe_stage_col<XT>(x, all, xbuf, xscl, c);
+        }
+        if (nt > 0) {
+            const PipeTile t0 = C.tile[0];
+            for (int c = 32 * sw + lane; c < max(t0.cols, t0.rows); c += 32 * kStageWarps) {
+                if (ncc > 1) pipe_stage_col<XT>(x, t0, xbuf, xscl, c);
+                pipe_stage_row(mv, t0, C, S.xs_tail, 0, c);
+            }
+        }
     }
     {
-        const bool landed = tid != 0 || pipe_mbar_wait(pipe_smem_addr(&C.mbar[0]));
-        if (!__syncthreads_and(landed)) {
-            if (tid == 0) atomicOr(err_flag, 2);
-            return;
-        }
+        const bool landed = tid != 0 || pipe_mbar_wait(pipe_smem_addr(&S.mbar[0]));
+        if (!__syncthreads_and(landed)) failed = true;  // uniform over the CTA
     }
     stamp();
 
-    for (int i = 0; i < nt; ++i) {
+    for (int i = 0; i < nt && !failed; ++i) {
         const PipeTile& tc = C.tile[i & 1];
         const bool has_next = i + 1 < nt;
         // ================= phase 1: digits, row data, classification =================
-        if (tid == 0) {
+        if (gt == 0) {
             C.ticket = 0;
 #pragma unroll
             for (int k = 0; k < 4; ++k) C.count[k] = 0;
@@ -514,14 +564,14 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
         }
         {
             // the tile's codes: started a phase ago (or in the prologue)
-            const bool landed = tid != 0 || pipe_mbar_wait(bar_slab, (unsigned int)i & 1u);
-            if (!__syncthreads_and(landed)) {
-                if (tid == 0) atomicOr(err_flag, 2);
-                return;
+            const bool landed = gt != 0 || pipe_mbar_wait(bar_slab, (unsigned int)i & 1u);
+            if (!pipe_group_sync_and(grp, landed)) {
+                failed = true;
+                break;
             }
         }
         {
-            // ---- classification: warp w takes blocks 32 w .. 32 w + 31, then 32 (w + 32) .., ... ----
+            // ---- classification: warp w takes blocks 32 w .. 32 w + 31, then 32 (w + warps) .., ... ----
             // item: 2 * (rank inside the class) + gain (45 bits: the largest class holds 8.83e12 points), class << 45
             const PipeSlabGeom sg = pipe_slab_geom(tc, mv.nb);
             const unsigned int blocks = (unsigned int)tc.blocks, cols = (unsigned int)tc.cols, mdiv = tc.mdiv;
@@ -532,12 +582,12 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
             // two groups of 32 blocks per iteration: their table look-ups are independent, so the scheduler can
             // overlap the shared-memory latency of one with the arithmetic of the other
 #pragma unroll 1
-            for (unsigned int f0 = 32u * warp; f0 < blocks; f0 += 64u * kPipeWarps) {
+            for (unsigned int f0 = 32u * warp; f0 < blocks; f0 += 64u * kGroupWarps) {
                 unsigned int fams[2], fs[2];
                 uint2 its[2];
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    const unsigned int f = f0 + 32u * kPipeWarps * u + lane;
+                    const unsigned int f = f0 + 32u * kGroupWarps * u + lane;
                     fs[u] = f;
                     fams[u] = 4u;  // 4: nothing to decode
                     its[u] = make_uint2(0u, 0u);  // origin or refused index: a block sum of zero
@@ -566,7 +616,7 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
                                 its[u].x = (unsigned int)c.local2;
                                 its[u].y = (unsigned int)(c.local2 >> 32) | (unsigned int)c.ci << 13;
                             } else if (c.fam == -2) {
-                                C.error = 1;
+                                S.error = 1;
                             }
                         }
                     }
@@ -593,11 +643,11 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
             }
         }
         {
-            // the decode tables must have landed before the first decode phase
-            const bool landed = i > 0 || tid != 0 || pipe_mbar_wait(pipe_smem_addr(&C.mbar[1]));
-            if (!__syncthreads_and(landed)) {
-                if (tid == 0) atomicOr(err_flag, 2);
-                return;
+            // the decode tables must have landed before the group's first decode phase
+            const bool landed = i > 0 || gt != 0 || pipe_mbar_wait(pipe_smem_addr(&S.mbar[1]));
+            if (!pipe_group_sync_and(grp, landed)) {
+                failed = true;
+                break;
             }
         }
         stamp();
@@ -609,18 +659,20 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
             pipe_issue_slab(mv.codes, tn, mv.nb, slab, bar_slab, lane);
         }
         // ... and its digits and row data are staged by a few warps before they join the decoding
-        if (has_next && warp >= kPipeWarps - kStageWarps) {
+        if (has_next && warp >= kGroupWarps - kStageWarps) {
             const PipeTile tn = C.tile[(i + 1) & 1];
-            const unsigned int xo = tn.same_cols ? 0u : (unsigned int)((i + 1) & 1) * xbuf_bytes;
-            for (int c = 32 * (kPipeWarps - 1 - warp) + lane; c < max(tn.cols, tn.rows); c += 32 * kStageWarps)
-                pipe_stage_tile<XT>(mv, x, tn, C, (i + 1) & 1, xbuf + xo, xscl + xo, c);
+            const unsigned int xo = ncc > 1 ? (unsigned int)((i + 1) & 1) * xbuf_bytes : 0u;
+            for (int c = 32 * (kGroupWarps - 1 - warp) + lane; c < max(tn.cols, tn.rows); c += 32 * kStageWarps) {
+                if (ncc > 1) pipe_stage_col<XT>(x, tn, xbuf + xo, xscl + xo, c);
+                pipe_stage_row(mv, tn, C, S.xs_tail, (i + 1) & 1, c);
+            }
         }
         {
             const int n_rare = C.count[kFamRare], n_o4 = C.count[kFamOdd4], n_o3 = C.count[kFamOdd3], n_ev = C.count[kFamEven];
             const int b_rare = (n_rare + 31) >> 5, b_o4 = (n_o4 + 31) >> 5, b_o3 = (n_o3 + 31) >> 5, b_ev = (n_ev + 31) >> 5;
             const int n_dec = (plan.probe & 4) ? 0 : b_rare + b_o4 + b_o3 + b_ev;  // probe bit 2: no batches at all
             const unsigned int cols = (unsigned int)tc.cols, mdiv = tc.mdiv;
-            const unsigned int xcur = xbuf + (tc.same_cols ? 0u : (unsigned int)(i & 1) * xbuf_bytes);
+            const unsigned int xcur = xbuf + (ncc > 1 ? (unsigned int)(i & 1) * xbuf_bytes : 0u);
             for (;;) {
                 int t = 0;
                 if (lane == 0) t = atomicAdd(&C.ticket, 1);
@@ -661,8 +713,11 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
                         scale = tab_decode_odd3(T, ci, local, V);
                     else if (fam == kFamOdd4)
                         scale = tab_decode_odd4(T, ci, local, V);
-                    else
-                        scale = tab_decode_rare(T, ci, local, V);
+                    else {
+                        const TabRareBlock r = tab_decode_rare_call(T.base, lut_off, lut_on3, L, ci, local);
+                        V[0] = r.v0; V[1] = r.v1; V[2] = r.v2; V[3] = r.v3; V[4] = r.v4; V[5] = r.v5;
+                        scale = r.scale;
+                    }
                     const float dot = pipe_dot<XT>(V, xcur + lc * kColBytes, xcur + xdig_bytes + 4u * lc);
                     const float2 cg = C.cent[i & 1][lr];
                     const float part = dot * (scale * (gain ? cg.y : cg.x));
@@ -670,11 +725,11 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
                 }
             }
         }
-        __syncthreads();
+        pipe_group_sync(grp);
         stamp();
 
         // ================= phase 3: fixed-order row sums =================
-        for (int lr = warp; lr < tc.rows; lr += kPipeWarps) {
+        for (int lr = warp; lr < tc.rows; lr += kGroupWarps) {
             float s = 0.0f;
             for (int c = lane; c < tc.cols; c += 32) {
                 unsigned int u;
@@ -694,15 +749,16 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
                 }
             }
         }
-        __syncthreads();
+        pipe_group_sync(grp);
         stamp();
     }
-    if (nt == 0) {
-        // nothing to decode, but the table copy must not outlive the CTA
-        const bool landed = tid != 0 || pipe_mbar_wait(pipe_smem_addr(&C.mbar[1]));
-        __syncthreads_and(landed);
+    // the groups meet again: neither table copy may outlive the CTA, and the error words are complete
+    if (tid == 0) pipe_mbar_wait(pipe_smem_addr(&S.mbar[1]));
+    const bool any_failed = __syncthreads_or(failed);
+    if (tid == 0) {
+        if (any_failed) atomicOr(err_flag, 2);
+        if (S.error) atomicOr(err_flag, 1);
     }
-    if (tid == 0 && C.error) atomicOr(err_flag, 1);
 }
 
 // Shared-memory plan for a matrix of nb column blocks on a device with `smem_optin` bytes per CTA;
@@ -711,33 +767,34 @@ template <typename XT>
 inline PipePlan pipe_plan(const TabLayout& L, int smem_optin, int d_out, int nb, int sm_count) {
     PipePlan p{};
     constexpr int kPerCol = XDigits<XT>::kColBytes + 4;
-    // the whole row in one chunk when its digits fit, else the fewest equal chunks whose two buffers fit
+    // the whole row in one chunk (digits shared by the groups) when its digits fit, else the fewest equal
+    // chunks for which two buffers per group fit
     p.ncc = 1;
     if (nb * kPerCol > kDigitBytes)
-        while (2 * ((nb + p.ncc - 1) / p.ncc) * kPerCol > kDigitBytes) ++p.ncc;
+        while (2 * kPipeGroups * ((nb + p.ncc - 1) / p.ncc) * kPerCol > kDigitBytes) ++p.ncc;
     p.cols_max = nb > 0 ? (nb + p.ncc - 1) / p.ncc : 1;
     unsigned int at = 0;
     p.blob = at;
     at += (L.total_bytes + 127u) & ~127u;
     p.xbuf = at;
-    at += (unsigned int)(p.ncc > 1 ? 2 : 1) * (((unsigned int)p.cols_max * kPerCol + 15u) & ~15u);
+    at += (unsigned int)(p.ncc > 1 ? 2 * kPipeGroups : 1) * (((unsigned int)p.cols_max * kPerCol + 15u) & ~15u);
     p.ctrl = at;
-    at += (unsigned int)((sizeof(PipeCtrl) + 15) & ~(size_t)15);
-    // per block of a tile: 8 bytes of item, 2 x 2 bytes of lists, 7 bytes of code slab (6 bytes of
+    at += (unsigned int)((sizeof(PipeShared) + kPipeGroups * sizeof(PipeCtrl) + 15) & ~(size_t)15);
+    // per block of a group's tile: 8 bytes of item, 2 x 2 bytes of lists, 7 bytes of code slab (6 bytes of
     // record + the alignment slack of a column chunk's rows: at most 30 bytes per 65 blocks)
-    const int room = smem_optin - (int)at - 128;
-    int tile_max = room / 19;
+    const int room = smem_optin - (int)at - 128 - kPipeGroups * 96;
+    int tile_max = room / (19 * kPipeGroups);
     tile_max &= ~31;
     if (tile_max > 65536 - 32) tile_max = 65536 - 32;  // list entries are 16 bits
     if (tile_max < p.cols_max) tile_max = 0;           // not even one row fits
     p.tile_max = tile_max > 0 ? tile_max : 0;
     p.items = at;
-    at += (unsigned int)p.tile_max * 8u;
+    at += (unsigned int)kPipeGroups * (unsigned int)p.tile_max * 8u;
     p.lists = at;
-    at += (unsigned int)p.tile_max * 4u;
+    at += (unsigned int)kPipeGroups * (unsigned int)p.tile_max * 4u;
     p.slab_bytes = ((unsigned int)p.tile_max * 7u + 64u + 15u) & ~15u;
     p.slab = at;
-    at += p.slab_bytes;
+    at += (unsigned int)kPipeGroups * p.slab_bytes;
     p.total = at;
     p.rows_per_cta = (d_out + sm_count - 1) / sm_count;
     p.probe = 0;
