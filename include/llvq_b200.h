@@ -140,14 +140,6 @@ int llvq_matrix_upload_group(llvq_runtime* rt, const llvq_matrix_desc* descs, in
 void llvq_matrix_free(llvq_matrix* m);
 int llvq_matrix_dims(const llvq_matrix* m, int32_t* d_out, int32_t* d_in);
 
-/* Column split of the batch-1 GEMV: `splits` CTAs share every 8-row tile, each decoding its own range
- * of column blocks; partial row sums are added in split order, so the result does not depend on
- * scheduling (it does depend on the split count, in the last bits of the f32 sum). The upload takes
- * the fewest splits the 128-block chunk allows (ceil(nblocks / 128)), more for a matrix with so few
- * rows that its grid would leave most SMs idle. 0 restores that default. Tuning knob with no counterpart in the
- * reference. Synchronises the device and reallocates the workspace: not for use inside a capture. */
-int llvq_matrix_set_splits(llvq_matrix* m, int32_t splits);
-int llvq_matrix_get_splits(const llvq_matrix* m, int32_t* splits);
 
 /* Bytes one GEMV must move at minimum: codes + tail + row scales (as stored in
  * the archive: f64) + x + y. Used by the benchmark's roofline. */
@@ -186,8 +178,11 @@ int llvq_gemv_h_host(llvq_matrix* m, const uint16_t* x_host, uint16_t* y_host, l
 /* A whole list of host-buffer GEMVs (f16 in, f16 out) enqueued back to back with ONE
  * synchronisation at the end: what a layer or a token is for a plugin that holds host
  * tensors. The reference's loop also issues every launch of a token and synchronises once,
- * at the argmax read-back (llvq-llm/src/model.rs:1058-1072). Pinned host buffers let the
- * copies overlap the kernels of the neighbouring calls. */
+ * at the argmax read-back (llvq-llm/src/model.rs:1058-1072). The activations are packed into a
+ * pinned buffer of the runtime and go up in one copy, the GEMVs run launch behind launch, the
+ * results come back in one copy and are scattered into y_host before the call returns (the
+ * buffers are sized by the first call and grow on demand; calls on one runtime take turns). The
+ * calls of a list are independent: no call reads another call's result. */
 typedef struct llvq_host_call {
     llvq_matrix* m;
     const uint16_t* x_host; /* d_in halves */

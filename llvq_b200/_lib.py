@@ -69,8 +69,6 @@ _SIGNATURES = {
     "llvq_gemv_h_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "llvq_op_add_rmsnorm_h": (C.c_int, [C.c_void_p] * 4 + [C.c_int32, C.c_float, C.c_void_p]),
     "llvq_op_qkv_rope_cache_h": (C.c_int, [C.c_void_p] * 13 + [C.c_int32] * 3 + [C.c_float, C.c_void_p]),
-    "llvq_matrix_set_splits": (C.c_int, [C.c_void_p, C.c_int32]),
-    "llvq_matrix_get_splits": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
     "llvq_archive_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "llvq_archive_open_memory": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
     "llvq_archive_close": (None, [C.c_void_p]),

@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -23,9 +24,7 @@
 #include "rotate.cuh"
 #include "rotation.h"
 #include "tp_exchange.cuh"
-#include "gemm_tc.cuh"
 #include "gemm_tab.cuh"
-#include "gemv_sorted.cuh"
 #include "gemv_pipe.cuh"
 #include "tab_tables.h"
 #include "kernels_generic.cuh"
@@ -70,6 +69,25 @@ struct DeviceGuard {
 
 constexpr int kLutShift = 35;
 
+// Launch with programmatic stream serialisation (see llvq_runtime_set_overlap): the kernel may be scheduled
+// while the previous kernel of the stream is still running; it orders itself behind that kernel with
+// griddepcontrol.wait before it touches memory (llvq_dependent_enter, or the GEMV's own placement of the wait).
+std::atomic<int> g_overlap_ops{1};
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_overlap_ops.load(std::memory_order_relaxed) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
 // cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device setting: remember, per (device, kernel),
 // the largest size configured so far, so that a second runtime on another GPU raises it again.
 std::mutex g_smem_mu;
@@ -98,10 +116,6 @@ struct llvq_runtime {
     void* d_lut = nullptr;
     void* d_golay = nullptr;
     int* d_err = nullptr;  // sticky flag written by kernels: bit 0 index outside the ball, bit 1 copy timeout
-    FastTables F{};
-    void* d_fcls = nullptr;
-    void* d_lut_on = nullptr;
-    void* d_lut_off = nullptr;
     // state-table decoders: the blob the GEMV copies into shared memory, the off-support table
     TabLayout TL{};
     void* d_tab_blob = nullptr;
@@ -115,9 +129,12 @@ struct llvq_runtime {
     uint64_t fingerprint = 0;
     int max_smem_optin = 0;
     int sm_count = 0;
-    int gemv_ctas_per_sm = 5;      // resident CTAs of the class-sorted GEMV kernel per SM (its launch bounds)
-    int use_sorted_gemv = 0;       // 1: serve GEMVs with the class-sorted kernel instead of the pipelined one
     int overlap_launches = 1;      // GEMV launches carry the programmatic-serialisation attribute
+    // staging of llvq_gemv_h_host_many: one pinned host buffer and its device twin, grown on demand
+    std::mutex many_mu;
+    unsigned char* many_host = nullptr;
+    unsigned char* many_dev = nullptr;
+    size_t many_bytes = 0;
     // split-K partials of the batched GEMM; grown on demand, shared by all matrices of the runtime
     float* gemm_ws = nullptr;
     size_t gemm_ws_bytes = 0;
@@ -131,11 +148,6 @@ struct llvq_matrix {
     float* rscale = nullptr;
     void* tail = nullptr;
     size_t codes_bytes = 0;
-    // column split of the GEMV (matrices whose rows are longer than one 128-block chunk): every
-    // split owns split_range column blocks; partial row sums and one arrival counter per row tile
-    int splits = 1, split_range = 0;
-    float* split_ws = nullptr;
-    int* split_counter = nullptr;
     // staging for the host-buffer entry points
     void* x_stage = nullptr;
     void* y_stage = nullptr;
@@ -177,25 +189,6 @@ int launch_gemv_generic(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
     return LLVQ_OK;
 }
 
-// The class-sorted kernel serves every matrix whose 8-row code slab fits in shared
-// memory (d_in up to roughly 90 000) and whose activation pointer allows 16-byte
-// loads; anything else goes to the generic kernel.
-template <typename XT, typename YT, int ROWS>
-int launch_sorted(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s, size_t smem) {
-    llvq_runtime* rt = m->rt;
-    auto kern = gemv_sorted_kernel<XT, YT, ROWS>;
-    {
-        int st = ensure_dyn_smem((const void*)kern, smem);
-        if (st) return st;
-    }
-    const dim3 grid((m->d_out + ROWS - 1) / ROWS, m->splits);
-    kern<<<grid, kThreads, smem, s>>>(rt->F, rt->T, m->view(), x, y, rt->d_err, m->split_range, m->split_ws,
-                                      m->split_counter);
-    g_launches++;
-    CUDA_TRY(cudaGetLastError());
-    return LLVQ_OK;
-}
-
 // The persistent pipelined kernel: one CTA per SM, rows split evenly over the CTAs.
 template <typename XT, typename YT>
 int launch_pipe(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s, PipePlan plan, int probe = 0,
@@ -232,13 +225,11 @@ int launch_gemv(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
     llvq_runtime* rt = m->rt;
     // the fused kernels read the activation with 16-byte loads
     if ((uintptr_t)x & 15u) return launch_gemv_generic<XT, YT>(m, x, y, s);
-    if (m->nb > 0 && !rt->use_sorted_gemv) {
+    if (m->nb > 0) {
         const PipePlan plan = pipe_plan<XT>(rt->TL, rt->max_smem_optin, m->d_out, m->nb, rt->sm_count);
         if (plan.tile_max > 0) return launch_pipe<XT, YT>(m, x, y, s, plan);
     }
-    // 8 rows per CTA: measured against 16, the larger grid wins on every Qwen3 shape.
-    const size_t smem8 = sorted_smem_bytes<8>(m->splits > 1 ? 0 : m->nb);  // no code slab when the columns are split
-    if (smem8 <= (size_t)rt->max_smem_optin) return launch_sorted<XT, YT, 8>(m, x, y, s, smem8);
+    // a matrix of tail columns only
     return launch_gemv_generic<XT, YT>(m, x, y, s);
 }
 
@@ -268,43 +259,6 @@ void free_matrix_buffers(llvq_matrix* m) {
     cudaFree(m->tail);
     cudaFree(m->x_stage);
     cudaFree(m->y_stage);
-    cudaFree(m->split_ws);
-    cudaFree(m->split_counter);
-}
-
-// Column split of a matrix: `splits` CTAs share a row tile, each owning split_range column blocks.
-// At least ceil(nb / 128) (a CTA stages one 128-block chunk of the activation at a time and a split
-// never loops over more than its range); more splits spread a matrix with few rows over more SMs.
-// splits = 0 picks the default.
-// Frees and reallocates the partial-sum workspace: not while a launch on the matrix is in flight.
-int set_splits(llvq_matrix* m, int splits) {
-    const int min_splits = m->nb > kChunk ? (m->nb + kChunk - 1) / kChunk : 1;
-    if (splits == 0) {
-        // default: the fewest splits the chunk allows (every extra split repeats the per-CTA fixed work), except
-        // for matrices with so few row tiles that the grid would leave most SMs idle: those are cut until half
-        // of the resident CTA slots are taken, down to ranges of 16 column blocks (measured on row shards of
-        // 640 to 1792 rows: 5 to 10 % faster than the minimum, and flat beyond)
-        const long long tiles = ((long long)m->d_out + 7) / 8;
-        const long long half_slots = (long long)m->rt->sm_count * m->rt->gemv_ctas_per_sm / 2;
-        splits = min_splits;
-        while (tiles * splits < half_slots && (m->nb + splits) / (splits + 1) >= 16) ++splits;
-    }
-    if (splits < min_splits) splits = min_splits;
-    if (m->nb > 0 && splits > m->nb) splits = m->nb;
-    if (m->nb == 0) splits = 1;
-    cudaFree(m->split_ws);
-    cudaFree(m->split_counter);
-    m->split_ws = nullptr;
-    m->split_counter = nullptr;
-    m->split_range = m->nb > 0 ? (m->nb + splits - 1) / splits : 1;
-    m->splits = m->nb > 0 ? (m->nb + m->split_range - 1) / m->split_range : 1;  // no empty trailing split
-    if (m->splits > 1) {
-        const size_t tiles = ((size_t)m->d_out + 7) / 8;
-        CUDA_TRY(cudaMalloc((void**)&m->split_ws, (size_t)m->splits * m->d_out * sizeof(float)));
-        CUDA_TRY(cudaMalloc((void**)&m->split_counter, tiles * sizeof(int)));
-        CUDA_TRY(cudaMemset(m->split_counter, 0, tiles * sizeof(int)));
-    }
-    return LLVQ_OK;
 }
 
 int upload_impl(llvq_runtime* rt, const llvq_matrix_desc* descs, int n, llvq_matrix** out) {
@@ -374,10 +328,6 @@ int upload_impl(llvq_runtime* rt, const llvq_matrix_desc* descs, int n, llvq_mat
     } else {
         UP_TRY(cudaMalloc(&m->tail, 16));  // never read; keeps the pointer valid
     }
-    {
-        int st = set_splits(m.get(), 0);  // the fewest splits the chunk size allows
-        if (st) return bail(st);
-    }
     UP_TRY(cudaMalloc(&m->x_stage, (size_t)m->d_in * sizeof(float) + 16));
     UP_TRY(cudaMalloc(&m->y_stage, (size_t)m->d_out * sizeof(float) + 16));
 #undef UP_TRY
@@ -425,8 +375,8 @@ static int launch_attn(const __half* q, const KvCacheView& kc, const KvCacheView
         int st = ensure_dyn_smem((const void*)attn_splitkv_kernel<HD, G>, (size_t)smem);
         if (st) return st;
     }
-    attn_splitkv_kernel<HD, G><<<dim3(n_kv, splits), kAttnThreads, smem, s>>>(q, kc, vc, pos, out, scratch, n_kv);
-    if (splits > 1) attn_combine_kernel<HD><<<n_kv * G, HD, splits * sizeof(float), s>>>(scratch, out, splits);
+    CUDA_TRY(launch_dep(attn_splitkv_kernel<HD, G>, dim3(n_kv, splits), dim3(kAttnThreads), smem, s, q, kc, vc, pos, out, scratch, n_kv));
+    if (splits > 1) CUDA_TRY(launch_dep(attn_combine_kernel<HD>, dim3(n_kv * G), dim3(HD), splits * sizeof(float), s, scratch, out, splits));
     g_launches += splits > 1 ? 2 : 1;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
@@ -463,9 +413,8 @@ void llvq_runtime_destroy(llvq_runtime* rt) {
     cudaFree(rt->d_golay);
     cudaFree(rt->d_err);
     cudaFree(rt->gemm_ws);
-    cudaFree(rt->d_fcls);
-    cudaFree(rt->d_lut_on);
-    cudaFree(rt->d_lut_off);
+    cudaFreeHost(rt->many_host);
+    cudaFree(rt->many_dev);
     cudaFree(rt->d_tab_blob);
     cudaFree(rt->d_tab_off);
     cudaFree(rt->d_tab_on3);
@@ -520,22 +469,6 @@ int llvq_runtime_create(int device, llvq_runtime** out) {
     rt->T.lut = (const unsigned short*)rt->d_lut;
     rt->T.golay = (const unsigned int*)rt->d_golay;
     rt->T.lut_shift = kLutShift;
-
-    FastTablesHost fh;
-    build_fast_tables(cb, fh);
-    RT_TRY(cudaMalloc(&rt->d_fcls, fh.cls.size() * sizeof(FastClass)));
-    RT_TRY(cudaMemcpy(rt->d_fcls, fh.cls.data(), fh.cls.size() * sizeof(FastClass), cudaMemcpyHostToDevice));
-    RT_TRY(cudaMalloc(&rt->d_lut_on, fh.lut_on.size() * sizeof(unsigned int)));
-    RT_TRY(cudaMemcpy(rt->d_lut_on, fh.lut_on.data(), fh.lut_on.size() * sizeof(unsigned int), cudaMemcpyHostToDevice));
-    RT_TRY(cudaMalloc(&rt->d_lut_off, fh.lut_off.size() * sizeof(unsigned int)));
-    RT_TRY(cudaMemcpy(rt->d_lut_off, fh.lut_off.data(), fh.lut_off.size() * sizeof(unsigned int), cudaMemcpyHostToDevice));
-    rt->F.cls = (const FastClass*)rt->d_fcls;
-    rt->F.ends = rt->T.ends;
-    rt->F.lut = rt->T.lut;
-    rt->F.golay = rt->T.golay;
-    rt->F.lut_on = (const unsigned int*)rt->d_lut_on;
-    rt->F.lut_off = (const unsigned int*)rt->d_lut_off;
-    rt->F.lut_shift = kLutShift;
 
     {
         TabTablesHost th;
@@ -638,6 +571,7 @@ int llvq_codebook_golay(uint32_t* out) {
 int llvq_runtime_set_overlap(llvq_runtime* rt, int32_t on) {
     if (!rt) return fail(LLVQ_ERR_INVALID, "set_overlap: null runtime");
     rt->overlap_launches = on ? 1 : 0;
+    g_overlap_ops.store(on ? 1 : 0);  // the decode-step kernels take no runtime: one switch for the process
     return LLVQ_OK;
 }
 
@@ -678,19 +612,6 @@ void llvq_matrix_free(llvq_matrix* m) {
     DeviceGuard g(m->rt->device);
     free_matrix_buffers(m);
     delete m;
-}
-
-int llvq_matrix_set_splits(llvq_matrix* m, int32_t splits) {
-    if (!m || splits < 0) return fail(LLVQ_ERR_INVALID, "matrix_set_splits: bad argument");
-    DeviceGuard g(m->rt->device);
-    CUDA_TRY(cudaDeviceSynchronize());
-    return set_splits(m, splits);
-}
-
-int llvq_matrix_get_splits(const llvq_matrix* m, int32_t* splits) {
-    if (!m || !splits) return fail(LLVQ_ERR_INVALID, "matrix_get_splits: null argument");
-    *splits = m->splits;
-    return LLVQ_OK;
 }
 
 int llvq_matrix_dims(const llvq_matrix* m, int32_t* d_out, int32_t* d_in) {
@@ -794,7 +715,6 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
         ga.ws = rt->gemm_ws;
         ga.batch = nb_rows;
         ga.n_pad = (nb_rows + 15) & ~15;
-        ga.chunks_per_split = plan.chunks_per_split;
         ga.x_vec_ok = ((m->d_in & 7) == 0 && ((uintptr_t)ga.x & 15u) == 0) ? 1 : 0;
         if (splits > 0) {
             llvq_gemm_tab_kernel<<<grid, kTGThreads, plan.total, s>>>((const unsigned char*)rt->d_tab_blob, (const OffEntry*)rt->d_tab_off,
@@ -819,8 +739,8 @@ int llvq_gemv_h_host(llvq_matrix* m, const uint16_t* x, uint16_t* y, llvq_stream
 int llvq_op_add_rmsnorm_h(uint16_t* x, const uint16_t* delta, const uint16_t* w, uint16_t* y, int32_t n, float eps,
                           llvq_stream_t stream) {
     if (!x || !w || !y || n <= 0 || (n & 1) || n > 16384) return fail(LLVQ_ERR_INVALID, "op_add_rmsnorm: bad argument (n even, <= 16384)");
-    add_rmsnorm_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>((__half*)x, (const __half*)delta, (const __half*)w, (__half*)y, n,
-                                                            eps);
+    CUDA_TRY(launch_dep(add_rmsnorm_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, (__half*)x, (const __half*)delta, (const __half*)w, (__half*)y, n,
+                                                            eps));
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
@@ -837,11 +757,11 @@ int llvq_op_qkv_rope_cache_h(const uint16_t* qkv, const uint16_t* q_norm, const 
     const int grid = n_heads + 2 * n_kv;
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 128)
-        qkv_rope_cache_kernel<128><<<grid, 32, 0, s>>>((const __half*)qkv, (const __half*)q_norm, (const __half*)k_norm, cos_t,
-                                                       sin_t, (const long long*)pos, (__half*)q_out, kc, vc, n_heads, n_kv, eps);
+        CUDA_TRY(launch_dep(qkv_rope_cache_kernel<128>, dim3(grid), dim3(32), 0, s, (const __half*)qkv, (const __half*)q_norm, (const __half*)k_norm, cos_t,
+                                                       sin_t, (const long long*)pos, (__half*)q_out, kc, vc, n_heads, n_kv, eps));
     else if (head_dim == 64)
-        qkv_rope_cache_kernel<64><<<grid, 32, 0, s>>>((const __half*)qkv, (const __half*)q_norm, (const __half*)k_norm, cos_t,
-                                                      sin_t, (const long long*)pos, (__half*)q_out, kc, vc, n_heads, n_kv, eps);
+        CUDA_TRY(launch_dep(qkv_rope_cache_kernel<64>, dim3(grid), dim3(32), 0, s, (const __half*)qkv, (const __half*)q_norm, (const __half*)k_norm, cos_t,
+                                                      sin_t, (const long long*)pos, (__half*)q_out, kc, vc, n_heads, n_kv, eps));
     else
         return fail(LLVQ_ERR_UNSUPPORTED, "op_qkv_rope_cache: head_dim %d (64 or 128)", head_dim);
     g_launches++;
@@ -869,7 +789,7 @@ int llvq_op_attn_decode_int8_h(const uint16_t* q, const uint8_t* kq, const uint1
 
 int llvq_op_silu_mul_h(const uint16_t* gu, uint16_t* y, int32_t inter, llvq_stream_t stream) {
     if (!gu || !y || inter <= 0) return fail(LLVQ_ERR_INVALID, "op_silu_mul: bad argument");
-    silu_mul_kernel<<<(inter + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const __half*)gu, (__half*)y, inter);
+    CUDA_TRY(launch_dep(silu_mul_kernel, dim3((inter + 255) / 256), dim3(256), 0, (cudaStream_t)stream, (const __half*)gu, (__half*)y, inter));
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
@@ -889,8 +809,8 @@ int llvq_op_lm_head_argmax_h(const uint16_t* embed, const uint16_t* h, int32_t r
     if (grid > want) grid = want;
     if (grid > kHeadMaxGrid) grid = kHeadMaxGrid;
     cudaStream_t s = (cudaStream_t)stream;
-    lm_head_argmax_kernel<<<grid, kHeadThreads, 0, s>>>((const __half*)embed, (const __half*)h, rows, hidden, (HeadBest*)scratch);
-    lm_head_pick_kernel<<<1, kHeadMaxGrid, 0, s>>>((const HeadBest*)scratch, grid, (long long)row_offset, val_out, (long long*)idx_out);
+    CUDA_TRY(launch_dep(lm_head_argmax_kernel, dim3(grid), dim3(kHeadThreads), 0, s, (const __half*)embed, (const __half*)h, rows, hidden, (HeadBest*)scratch));
+    CUDA_TRY(launch_dep(lm_head_pick_kernel, dim3(1), dim3(kHeadMaxGrid), 0, s, (const HeadBest*)scratch, grid, (long long)row_offset, val_out, (long long*)idx_out));
     g_launches += 2;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
@@ -912,9 +832,9 @@ int llvq_op_lm_head_argmax_q8_h(const uint8_t* wq, const uint16_t* scales, const
     if (grid > want) grid = want;
     if (grid > kHeadMaxGrid) grid = kHeadMaxGrid;
     cudaStream_t s = (cudaStream_t)stream;
-    lm_head_argmax_q8_kernel<<<grid, kHeadThreads, 0, s>>>(wq, (const __half*)scales, (const __half*)biases, (const __half*)h, rows,
-                                                           hidden, (HeadBest*)scratch);
-    lm_head_pick_kernel<<<1, kHeadMaxGrid, 0, s>>>((const HeadBest*)scratch, grid, (long long)row_offset, val_out, (long long*)idx_out);
+    CUDA_TRY(launch_dep(lm_head_argmax_q8_kernel, dim3(grid), dim3(kHeadThreads), 0, s, wq, (const __half*)scales, (const __half*)biases, (const __half*)h, rows,
+                                                           hidden, (HeadBest*)scratch));
+    CUDA_TRY(launch_dep(lm_head_pick_kernel, dim3(1), dim3(kHeadMaxGrid), 0, s, (const HeadBest*)scratch, grid, (long long)row_offset, val_out, (long long*)idx_out));
     g_launches += 2;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
@@ -925,8 +845,8 @@ int llvq_op_embed_gather_q8_h(const uint8_t* wq, const uint16_t* scales, const u
     if (!wq || !scales || !biases || !ids || !y || n_tokens < 0 || rows <= 0 || hidden <= 0)
         return fail(LLVQ_ERR_INVALID, "op_embed_gather_q8: bad argument");
     if (n_tokens == 0) return LLVQ_OK;
-    embed_gather_q8_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>(wq, (const __half*)scales, (const __half*)biases,
-                                                                     (const long long*)ids, (__half*)y, hidden, rows);
+    CUDA_TRY(launch_dep(embed_gather_q8_kernel, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, wq, (const __half*)scales, (const __half*)biases,
+                                                                     (const long long*)ids, (__half*)y, hidden, rows));
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
@@ -939,7 +859,15 @@ int llvq_matrix_dequant_h(llvq_matrix* m, uint16_t* out, llvq_stream_t stream) {
     const MatrixView mv = m->view();
     const size_t items = (size_t)mv.d_out * (mv.nb + (mv.tail_w ? 1 : 0));
     if (items == 0) return LLVQ_OK;
-    dequant_dense_kernel<<<(unsigned int)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(rt->F, rt->T, mv, (__half*)out, rt->d_err);
+    {
+        int st = ensure_dyn_smem((const void*)dequant_dense_kernel, rt->TL.total_bytes);
+        if (st) return st;
+    }
+    const size_t want = (items + kDenseThreads - 1) / kDenseThreads;
+    const unsigned int grid = (unsigned int)(want < (size_t)(2 * rt->sm_count) ? want : (size_t)(2 * rt->sm_count));  // two CTAs per SM
+    dequant_dense_kernel<<<grid, kDenseThreads, rt->TL.total_bytes, (cudaStream_t)stream>>>(
+        (const unsigned char*)rt->d_tab_blob, (const OffEntry*)rt->d_tab_off, (const unsigned long long*)rt->d_tab_on3, rt->TL, mv,
+        (__half*)out, rt->d_err);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
@@ -1152,8 +1080,8 @@ int llvq_rotate_h(llvq_rotation* r, const uint16_t* x, float* xr, int32_t batch,
     if (batch == 0) return LLVQ_OK;
     if (((uintptr_t)x & 1u) || ((uintptr_t)xr & 3u)) return fail(LLVQ_ERR_INVALID, "rotate_h: misaligned buffer");
     DeviceGuard g(r->rt->device);
-    rot_apply_kernel<<<batch, kRotThreads, r->smem, (cudaStream_t)stream>>>((const __half*)x, r->d_signbits, r->d_small, xr, r->t.n,
-                                                                        r->t.m, r->t.k, r->t.inv);
+    CUDA_TRY(launch_dep(rot_apply_kernel, dim3(batch), dim3(kRotThreads), r->smem, (cudaStream_t)stream, (const __half*)x, r->d_signbits, r->d_small, xr, r->t.n,
+                                                                        r->t.m, r->t.k, r->t.inv));
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
@@ -1173,8 +1101,8 @@ int llvq_op_add_rmsnorm_rotate_h(uint16_t* x, const uint16_t* delta, const uint1
     DeviceGuard g(r->rt->device);
     int st = rot_fused_prepare(r, n, "op_add_rmsnorm_rotate");
     if (st) return st;
-    add_rmsnorm_rotate_kernel<<<1, kRotThreads, r->smem, (cudaStream_t)stream>>>(
-        (__half*)x, (const __half*)delta, (const __half*)w, r->d_signbits, r->d_small, xr, n, r->t.m, r->t.k, r->t.inv, eps);
+    CUDA_TRY(launch_dep(add_rmsnorm_rotate_kernel, dim3(1), dim3(kRotThreads), r->smem, (cudaStream_t)stream, 
+        (__half*)x, (const __half*)delta, (const __half*)w, r->d_signbits, r->d_small, xr, n, r->t.m, r->t.k, r->t.inv, eps));
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
@@ -1185,8 +1113,8 @@ int llvq_op_silu_mul_rotate_h(const uint16_t* gu, llvq_rotation* r, float* xr, i
     DeviceGuard g(r->rt->device);
     int st = rot_fused_prepare(r, inter, "op_silu_mul_rotate");
     if (st) return st;
-    silu_mul_rotate_kernel<<<1, kRotThreads, r->smem, (cudaStream_t)stream>>>((const __half*)gu, r->d_signbits, r->d_small, xr,
-                                                                              inter, r->t.m, r->t.k, r->t.inv);
+    CUDA_TRY(launch_dep(silu_mul_rotate_kernel, dim3(1), dim3(kRotThreads), r->smem, (cudaStream_t)stream, (const __half*)gu, r->d_signbits, r->d_small, xr,
+                                                                              inter, r->t.m, r->t.k, r->t.inv));
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
@@ -1333,14 +1261,44 @@ int llvq_gemv_h_host_many(const llvq_host_call* calls, int32_t n, llvq_stream_t 
             return fail(LLVQ_ERR_INVALID, "gemv_h_host_many: call %d has a null field or another runtime", i);
     DeviceGuard g(calls[0].m->rt->device);
     cudaStream_t s = (cudaStream_t)stream;
+    // One pinned host buffer and one device buffer of the runtime carry the whole list: the activations are
+    // packed on the host and go up in ONE copy, the GEMVs run launch behind launch (each one's prologue
+    // overlapping the previous one's tail), the results come back in ONE copy and are scattered on the host.
+    // (A copy per call costs about 2 us of stream time each way; a 252-projection token would spend more time in
+    // copies than in a fifth of its kernels.) The buffers grow on demand; calls on one runtime take turns.
+    llvq_runtime* rt = calls[0].m->rt;
+    std::lock_guard<std::mutex> lock(rt->many_mu);
+    std::vector<size_t> xo(n), yo(n);
+    size_t at = 0;
     for (int i = 0; i < n; ++i) {
-        llvq_matrix* m = calls[i].m;
-        CUDA_TRY(cudaMemcpyAsync(m->x_stage, calls[i].x_host, (size_t)m->d_in * sizeof(__half), cudaMemcpyHostToDevice, s));
-        int st = launch_gemv<__half, __half>(m, (const __half*)m->x_stage, (__half*)m->y_stage, s);
-        if (st) return st;
-        CUDA_TRY(cudaMemcpyAsync(calls[i].y_host, m->y_stage, (size_t)m->d_out * sizeof(__half), cudaMemcpyDeviceToHost, s));
+        xo[i] = at;
+        at += ((size_t)calls[i].m->d_in * sizeof(__half) + 15) & ~(size_t)15;  // the kernels read x with 16-byte loads
     }
+    const size_t x_bytes = at;
+    for (int i = 0; i < n; ++i) {
+        yo[i] = at;
+        at += ((size_t)calls[i].m->d_out * sizeof(__half) + 15) & ~(size_t)15;
+    }
+    if (at > rt->many_bytes) {
+        CUDA_TRY(cudaStreamSynchronize(s));
+        cudaFreeHost(rt->many_host);
+        cudaFree(rt->many_dev);
+        rt->many_host = nullptr;
+        rt->many_dev = nullptr;
+        rt->many_bytes = 0;
+        CUDA_TRY(cudaMallocHost((void**)&rt->many_host, at));
+        CUDA_TRY(cudaMalloc((void**)&rt->many_dev, at));
+        rt->many_bytes = at;
+    }
+    for (int i = 0; i < n; ++i) std::memcpy(rt->many_host + xo[i], calls[i].x_host, (size_t)calls[i].m->d_in * sizeof(__half));
+    CUDA_TRY(cudaMemcpyAsync(rt->many_dev, rt->many_host, x_bytes, cudaMemcpyHostToDevice, s));
+    for (int i = 0; i < n; ++i) {
+        int st = launch_gemv<__half, __half>(calls[i].m, (const __half*)(rt->many_dev + xo[i]), (__half*)(rt->many_dev + yo[i]), s);
+        if (st) return st;
+    }
+    CUDA_TRY(cudaMemcpyAsync(rt->many_host + x_bytes, rt->many_dev + x_bytes, at - x_bytes, cudaMemcpyDeviceToHost, s));
     CUDA_TRY(cudaStreamSynchronize(s));
+    for (int i = 0; i < n; ++i) std::memcpy(calls[i].y_host, rt->many_host + yo[i], (size_t)calls[i].m->d_out * sizeof(__half));
     return LLVQ_OK;
 }
 

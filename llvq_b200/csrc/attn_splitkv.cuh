@@ -23,6 +23,8 @@
 #pragma once
 #include <cuda_fp16.h>
 
+#include "portable.h"
+
 namespace llvq {
 
 struct KvCacheView {
@@ -76,6 +78,7 @@ template <int HD, int G>
 __global__ void __launch_bounds__(kAttnThreads)
 attn_splitkv_kernel(const __half* __restrict__ q, KvCacheView kc, KvCacheView vc, const long long* __restrict__ pos_ptr,
                     __half* __restrict__ out, float* __restrict__ partial, int n_kv) {
+    llvq_dependent_enter();
     constexpr int NG = HD / 64;
     constexpr int VB = HD / 32;       // value bytes (dims) per lane
     constexpr int KW = HD / 4;        // 32-bit words of a key row
@@ -264,6 +267,7 @@ attn_splitkv_kernel(const __half* __restrict__ q, KvCacheView kc, KvCacheView vc
 template <int HD>
 __global__ void __launch_bounds__(HD)
 attn_combine_kernel(const float* __restrict__ partial, __half* __restrict__ out, int splits) {
+    llvq_dependent_enter();
     extern __shared__ float f_s[];  // splits weights
     __shared__ float red[HD / 32];
     __shared__ float bcast[2];

@@ -307,9 +307,8 @@ uint64_t fingerprint_from_points(const Codebook& cb, const std::vector<uint64_t>
 }  // namespace llvq
 
 // ---------------------------------------------------------------------------
-// Fast-path tables
+// Magic division (tables of the even-coset decoder)
 // ---------------------------------------------------------------------------
-#include <map>
 
 namespace llvq {
 
@@ -319,124 +318,6 @@ void magic28(unsigned int d, unsigned int* m, unsigned int* s) {
     const unsigned long long pow = 1ull << (28 + l);
     *m = (unsigned int)((pow + d - 1) / d);  // ceil(2^(28+l) / d) <= 2^29 + 1
     *s = l;
-}
-
-namespace {
-
-// Lexicographic unranking of one multiset arrangement (kinds ordered by index),
-// the plain form of llvq-search/src/index.rs:101-118 with the M*c/n recurrence.
-void unrank_arrangement(uint64_t rank, const uint8_t* cnt_in, int k, int slots, uint64_t total, int* out) {
-    uint8_t cnt[8];
-    for (int j = 0; j < k; ++j) cnt[j] = cnt_in[j];
-    uint64_t m = total;
-    for (int s = 0, n = slots; s < slots; ++s, --n) {
-        for (int j = 0; j < k; ++j) {
-            if (!cnt[j]) continue;
-            const uint64_t mj = m * cnt[j] / (uint64_t)n;
-            if (rank < mj) {
-                out[s] = j;
-                cnt[j]--;
-                m = mj;
-                break;
-            }
-            rank -= mj;
-        }
-    }
-}
-
-unsigned int float_bits(float f) {
-    unsigned int u;
-    std::memcpy(&u, &f, 4);
-    return u;
-}
-
-}  // namespace
-
-void build_fast_tables(const Codebook& cb, FastTablesHost& out) {
-    out.cls.assign(cb.n_classes12, FastClass{});
-    out.lut_on.clear();
-    out.lut_off.clear();
-    std::map<std::vector<int>, unsigned int> on_base, off_base;
-    double slow = 0.0;
-    for (int ci = 0; ci < cb.n_classes12; ++ci) {
-        const ClassInfo& c = cb.classes[ci];
-        FastClass& f = out.cls[ci];
-        std::memset(&f, 0, sizeof f);
-        f.off_lo = (unsigned int)c.offset;
-        f.off_hi = (unsigned int)(c.offset >> 32);
-        const float scale = (float)(1.0 / std::sqrt(16.0 * c.shell));
-        unsigned int path = kPathSlow;
-        if (c.odd) {
-            f.arr = (unsigned int)c.arr_a;
-            if (c.n_a <= 4 && c.arr_a < (1ull << 31)) {
-                path = c.n_a <= 3 ? kPathOdd2 : kPathOdd3;
-                unsigned int cum = 0, sv = 0, run = 0;
-                for (int j = 0; j < 3; ++j) {
-                    run = j < c.n_a - 1 ? run + c.cnt_a[j] : 24;  // thresholds of absent kinds sit at the top
-                    cum |= run << (8 * j);
-                }
-                for (int j = 0; j < c.n_a; ++j) {
-                    const int v = c.val_a[j];
-                    const int a = (v & 3) == 3 ? v : -v;  // value where the codeword bit is 1
-                    sv |= (unsigned int)(uint8_t)(int8_t)a << (8 * j);
-                }
-                f.a0 = cum;
-                f.a1 = sv;
-                f.a2 = float_bits(scale);
-                f.a3 = float_bits((float)(1.0 / (double)c.arr_a));
-            }
-        } else {
-            f.arr = (unsigned int)c.arr_b;
-            const int slots_b = kDim - c.w;
-            const bool ok = (c.w == 8 || c.w == 12 || c.w == 16) && c.n_a >= 1 && c.n_a <= 2 && c.n_b <= 4 &&
-                            c.arr_b <= kOffLutCap;
-            if (ok) {
-                path = kPathEven;
-                std::vector<int> key_on = {c.w}, key_off = {slots_b};
-                for (int j = 0; j < c.n_a; ++j) key_on.push_back(c.cnt_a[j]);
-                for (int j = 0; j < c.n_b; ++j) key_off.push_back(c.cnt_b[j]);
-                if (!on_base.count(key_on)) {
-                    on_base[key_on] = (unsigned int)out.lut_on.size();
-                    int kinds[kDim];
-                    for (uint64_t r = 0; r < c.arr_a; ++r) {
-                        unrank_arrangement(r, c.cnt_a, c.n_a, c.w, c.arr_a, kinds);
-                        unsigned int e = 0;
-                        for (int s = 0; s < c.w; ++s) e |= (unsigned int)kinds[s] << (2 * s);
-                        out.lut_on.push_back(e);
-                    }
-                }
-                if (!off_base.count(key_off)) {
-                    off_base[key_off] = (unsigned int)out.lut_off.size();
-                    int kinds[kDim];
-                    for (uint64_t r = 0; r < c.arr_b; ++r) {
-                        unrank_arrangement(r, c.cnt_b, c.n_b, slots_b, c.arr_b, kinds);
-                        unsigned int e = 0;
-                        for (int s = 0; s < slots_b; ++s) e |= (unsigned int)kinds[s] << (2 * s);
-                        out.lut_off.push_back(e);
-                    }
-                }
-                unsigned int m_off, s_off, m_on, s_on;
-                magic28((unsigned int)c.arr_b, &m_off, &s_off);
-                magic28((unsigned int)c.arr_a, &m_on, &s_on);
-                f.a0 = (unsigned int)c.arr_a | (unsigned int)c.w << 16 | (unsigned int)c.free_n << 24 |
-                       (unsigned int)c.p_req << 31;
-                f.a1 = m_off;
-                f.a2 = m_on;
-                f.a3 = s_off | s_on << 8 | (unsigned int)cb.bucket[c.w] << 16;
-                f.b0 = on_base[key_on];
-                f.b1 = off_base[key_off];
-                const int v0 = c.val_a[0], v1 = c.n_a > 1 ? c.val_a[1] : c.val_a[0];
-                f.b2 = (unsigned int)v0 | (unsigned int)v1 << 8 | (unsigned int)v0 << 16 | (unsigned int)v1 << 24;
-                unsigned int vt_off = 0;
-                for (int j = 0; j < c.n_b; ++j) vt_off |= (unsigned int)c.val_b[j] << (8 * j);
-                f.b3 = vt_off;
-                f.c0 = float_bits(scale);
-            }
-        }
-        f.info = path | (unsigned int)c.shell << 2;
-        if (path == kPathSlow) slow += (double)c.card / (double)cb.total12;
-    }
-    out.slow_mass = slow;
 }
 
 }  // namespace llvq

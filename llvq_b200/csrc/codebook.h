@@ -90,51 +90,7 @@ uint64_t fingerprint_from_points(const Codebook& cb, const std::vector<uint64_t>
 
 }  // namespace llvq
 
-// ---------------------------------------------------------------------------
-// Tables of the class-sorted fast decoders (cap-12 ball only).
-// ---------------------------------------------------------------------------
 namespace llvq {
-
-enum FastPath : unsigned int {
-    kPathSlow = 0,  // handed to the generic decoder (rare classes)
-    kPathOdd2 = 1,  // odd coset, at most 3 kinds: 2 thresholds per slot
-    kPathOdd3 = 2,  // odd coset, 4 kinds: 3 thresholds per slot
-    kPathEven = 3   // even coset served from the arrangement tables
-};
-
-constexpr unsigned int kOffLutCap = 131072;  // largest off-support arrangement count tabulated
-
-// 64-byte record of one cap-12 class, read as four 16-byte quads.
-//   q0  off_lo, off_hi : class offset;  arr : m_arr (odd) / a_off (even);
-//       info : bits 0-1 FastPath, bits 2-5 shell
-//   q1  odd : cum  = cumulative kind counts C0,C1,C2 in bytes 0-2 (absent kinds read 24)
-//             sv   = signed kind values sv0..sv3 in bytes (the value a coordinate takes
-//                    where the codeword bit is 1; it is negated where the bit is 0)
-//             scale= 1/sqrt(16 m) as float bits;  rcp = 1/m_arr as float bits
-//       even: geom = a_on | w << 16 | free_n << 24 | p_req << 31
-//             m_off, m_on = magic multipliers for division by a_off / a_on
-//             sh   = s_off | s_on << 8 | golay_base << 16
-//   q2  even: on_base, off_base = first entry of the class's arrangement tables;
-//             vt_on  = bytes {v0, v1, v0, v1}: |value| indexed by the low 2 bits of a
-//                      support slot's code (sign << 1 | kind)
-//             vt_off = bytes {f0, f1, f2, 0} indexed by off-support kind (zero run = 0)
-//   q3  even: scale as float bits
-struct alignas(16) FastClass {
-    unsigned int off_lo, off_hi, arr, info;
-    unsigned int a0, a1, a2, a3;
-    unsigned int b0, b1, b2, b3;
-    unsigned int c0, c1, c2, c3;
-};
-static_assert(sizeof(FastClass) == 64, "FastClass must stay 64 bytes");
-
-struct FastTablesHost {
-    std::vector<FastClass> cls;         // 301
-    std::vector<unsigned int> lut_on;   // on-support arrangements: kind bit of slot s at bit 2s
-    std::vector<unsigned int> lut_off;  // off-support arrangements: kind of slot s at bits 2s..2s+1
-    double slow_mass = 0.0;             // fraction of the ball served by the generic decoder
-};
-
-void build_fast_tables(const Codebook& cb, FastTablesHost& out);
 
 // Magic division of q < 2^28 by d: q / d == umulhi(q << 4, m) >> s.
 void magic28(unsigned int d, unsigned int* m, unsigned int* s);

@@ -40,6 +40,7 @@ __device__ __forceinline__ float warp_min_f(float v) {
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_kernel(__half* __restrict__ x, const __half* __restrict__ delta, const __half* __restrict__ w,
                    __half* __restrict__ y, int n, float eps) {
+    llvq_dependent_enter();
     __shared__ float red[32];
     constexpr int kMaxPairs = 8;  // up to 16 384 elements
     const int pairs = n >> 1;
@@ -109,6 +110,7 @@ __global__ void qkv_rope_cache_kernel(const __half* __restrict__ qkv, const __ha
                                       const float* __restrict__ sin_t, const long long* __restrict__ pos_ptr,
                                       __half* __restrict__ q_out, KvCacheView kc, KvCacheView vc, int n_heads, int n_kv,
                                       float eps) {
+    llvq_dependent_enter();
     constexpr int V = HD / 32;
     const int head = blockIdx.x, lane = threadIdx.x;
     const long long pos = *pos_ptr;
@@ -147,6 +149,7 @@ __global__ void qkv_rope_cache_kernel(const __half* __restrict__ qkv, const __ha
 }
 
 __global__ void silu_mul_kernel(const __half* __restrict__ gu, __half* __restrict__ y, int inter) {
+    llvq_dependent_enter();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= inter) return;
     const float g = __half2float(gu[i]), u = __half2float(gu[inter + i]);

@@ -31,7 +31,7 @@
 #include <cstdint>
 #include <cstring>
 
-#include "decode_fast.cuh"
+#include "decode_util.cuh"
 #include "tab_tables.h"
 
 namespace llvq {

@@ -13,42 +13,69 @@
 #pragma once
 #include <cuda_fp16.h>
 
-#include "decode_fast.cuh"
-#include "decode_generic.cuh"
+#include "decode_tab.cuh"
 #include "kernels_generic.cuh"
 
 namespace llvq {
 
-__global__ void __launch_bounds__(256)
-dequant_dense_kernel(FastTables F, DevTables G, MatrixView mv, __half* __restrict__ out, int* __restrict__ err_flag) {
-    const size_t item = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+// Persistent CTAs of 512 threads with the decoder tables in shared memory; a thread takes one block at a time
+// (class search, then its family's decoder: the lanes of a warp may run different families one after the other,
+// which this transient path accepts) and writes its 24 weights with three 16-byte stores when the row allows.
+constexpr int kDenseThreads = 512;
+__global__ void __launch_bounds__(kDenseThreads)
+dequant_dense_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* __restrict__ lut_off,
+                     const unsigned long long* __restrict__ lut_on3, TabLayout L, MatrixView mv, __half* __restrict__ out,
+                     int* __restrict__ err_flag) {
+    extern __shared__ __align__(128) unsigned char dense_smem[];
+    for (unsigned int o = threadIdx.x * 16u; o < L.total_bytes; o += kDenseThreads * 16u)
+        *reinterpret_cast<uint4*>(dense_smem + o) = __ldg(reinterpret_cast<const uint4*>(blob_g + o));
+    __syncthreads();
+    TabView T;
+    T.base = (unsigned int)__cvta_generic_to_shared(dense_smem);
+    T.lut_off = lut_off;
+    T.lut_on3 = lut_on3;
+    T.L = L;
     const int per_row = mv.nb + (mv.tail_w ? 1 : 0);
-    if (item >= (size_t)mv.d_out * per_row) return;
-    const int r = (int)(item / per_row), b = (int)(item % per_row);
-    __half* dst = out + (size_t)r * mv.d_in + (size_t)b * kDim;
-    const float rs = mv.rscale[r];
-    if (b == mv.nb) {  // the tail columns of this row, already in weight units
-        for (int t = 0; t < mv.tail_w; ++t) {
-            const float w = mv.tail_f16 ? __half2float(((const __half*)mv.tail)[(size_t)r * mv.tail_w + t])
-                                        : ((const float*)mv.tail)[(size_t)r * mv.tail_w + t];
-            dst[t] = __float2half_rn(w);
+    const size_t n_items = (size_t)mv.d_out * per_row;
+    const bool vec_ok = (mv.d_in & 7) == 0 && ((uintptr_t)out & 15u) == 0;  // 48-byte blocks on 16-byte boundaries
+    for (size_t item = (size_t)blockIdx.x * kDenseThreads + threadIdx.x; item < n_items; item += (size_t)gridDim.x * kDenseThreads) {
+        const int r = (int)(item / per_row), b = (int)(item % per_row);
+        __half* dst = out + (size_t)r * mv.d_in + (size_t)b * kDim;
+        if (b == mv.nb) {  // the tail columns of this row, already in weight units
+            for (int t = 0; t < mv.tail_w; ++t) {
+                const float w = mv.tail_f16 ? __half2float(((const __half*)mv.tail)[(size_t)r * mv.tail_w + t])
+                                            : ((const float*)mv.tail)[(size_t)r * mv.tail_w + t];
+                dst[t] = __float2half_rn(w);
+            }
+            continue;
         }
-        return;
-    }
-    const unsigned long long v = load_code48(mv.codes, (size_t)r * mv.nb + b);
-    const float2 cent = mv.cent[r];
-    const float gain = (v & 1ull) ? cent.y : cent.x;
-    float w[kDim];
-    float scale = 0.0f, slow_scale = 0.0f;
-    const int path = decode_fast_any(
-        F, v >> 1, [&](int pos, float val) { w[pos] = val; },
-        [&](unsigned long long idx) { decode_generic12(G, idx, [&](int pos, int val) { w[pos] = (float)val; }, &slow_scale); },
-        &scale);
-    if (path == (int)kPathSlow) scale = slow_scale;
-    if (path == -2 && err_flag) atomicExch(err_flag, 1);  // an index outside the ball decodes to zeros
-    const float f = gain * scale * rs;
+        const unsigned long long v = load_code48(mv.codes, (size_t)r * mv.nb + b);
+        const float2 cent = mv.cent[r];
+        unsigned int V[6];
+        float scale = 0.0f;
+        const int fam = tab_decode_any(T, v >> 1, V, &scale);
+        if (fam == -2 && err_flag) atomicExch(err_flag, 1);  // an index outside the ball decodes to zeros
+        const float f = ((v & 1ull) ? cent.y : cent.x) * scale * mv.rscale[r];
+        unsigned int h[12];
 #pragma unroll
-    for (int pos = 0; pos < kDim; ++pos) dst[pos] = __float2half_rn(w[pos] * f);
+        for (int k = 0; k < 6; ++k) {
+            const int w = (int)V[k];
+            const __half2 lo = __floats2half2_rn((float)(signed char)(w & 0xff) * f, (float)(signed char)((w >> 8) & 0xff) * f);
+            const __half2 hi = __floats2half2_rn((float)(signed char)((w >> 16) & 0xff) * f, (float)(w >> 24) * f);
+            h[2 * k] = *reinterpret_cast<const unsigned int*>(&lo);
+            h[2 * k + 1] = *reinterpret_cast<const unsigned int*>(&hi);
+        }
+        if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 3; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 12; ++j) {
+                reinterpret_cast<unsigned short*>(dst)[2 * j] = (unsigned short)(h[j] & 0xffffu);
+                reinterpret_cast<unsigned short*>(dst)[2 * j + 1] = (unsigned short)(h[j] >> 16);
+            }
+        }
+    }
 }
 
 constexpr int kHeadThreads = 256;   // 8 warps, one embedding row per warp and step
@@ -66,6 +93,7 @@ __device__ __forceinline__ bool head_better(float v, int r, float bv, int br) { 
 __global__ void __launch_bounds__(kHeadThreads)
 lm_head_argmax_kernel(const __half* __restrict__ embed, const __half* __restrict__ h, int rows, int hidden,
                       HeadBest* __restrict__ partial) {
+    llvq_dependent_enter();
     __shared__ __align__(16) __half hs[kHeadMaxHidden];
     __shared__ HeadBest red[kHeadThreads / 32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -119,6 +147,7 @@ __global__ void __launch_bounds__(kHeadThreads)
 lm_head_argmax_q8_kernel(const unsigned char* __restrict__ wq, const __half* __restrict__ scales,
                          const __half* __restrict__ biases, const __half* __restrict__ h, int rows, int hidden,
                          HeadBest* __restrict__ partial) {
+    llvq_dependent_enter();
     __shared__ __align__(16) float hs[kHeadMaxHidden];
     __shared__ HeadBest red[kHeadThreads / 32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -165,6 +194,7 @@ lm_head_argmax_q8_kernel(const unsigned char* __restrict__ wq, const __half* __r
 __global__ void embed_gather_q8_kernel(const unsigned char* __restrict__ wq, const __half* __restrict__ scales,
                                        const __half* __restrict__ biases, const long long* __restrict__ ids,
                                        __half* __restrict__ y, int hidden, int rows) {
+    llvq_dependent_enter();
     long long row = ids[blockIdx.x];
     if (row < 0 || row >= rows) row = 0;  // a token outside the vocabulary reads row 0 instead of foreign memory
     const int gpr = (hidden + 63) / 64;
@@ -179,6 +209,7 @@ __global__ void embed_gather_q8_kernel(const unsigned char* __restrict__ wq, con
 __global__ void __launch_bounds__(kHeadMaxGrid)
 lm_head_pick_kernel(const HeadBest* __restrict__ partial, int n, long long row_offset, float* __restrict__ val_out,
                     long long* __restrict__ idx_out) {
+    llvq_dependent_enter();
     __shared__ HeadBest red[32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     HeadBest b = threadIdx.x < n ? partial[threadIdx.x] : HeadBest{-INFINITY, 0x7fffffff};

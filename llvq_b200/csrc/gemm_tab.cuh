@@ -19,7 +19,7 @@
 //             accumulate in TMEM and commits them onto an mbarrier; the tiles are free
 //             again when that barrier completes.
 // After the last chunk of a unit the f32 accumulators are read back with tcgen05.ld and
-// stored as split-K partials; gemm_reduce_kernel (gemm_tc.cuh) adds the partials in a fixed
+// stored as split-K partials; gemm_reduce_kernel adds the partials in a fixed
 // order, applies the row scale and the tail columns, and narrows to f16 once.
 //
 // Every wait is bounded; on a time-out the kernel raises the error word, still frees its
@@ -27,10 +27,41 @@
 #pragma once
 #include <cuda_fp16.h>
 
-#include "gemm_tc.cuh"    // tile geometry, descriptors, GemmArgs, gemm_reduce_kernel
 #include "gemv_pipe.cuh"  // bulk copies, bounded mbarrier waits
 
 namespace llvq {
+
+constexpr int kGM = 128;                  // rows of W per CTA = MMA M
+constexpr int kGKB = 8;                   // blocks per row and chunk: 8 * 24 = 192 = 3 * 64 columns
+constexpr int kGItems = kGM * kGKB;       // 1024 blocks per chunk
+constexpr int kGMaxN = 64;                // padded batch per launch = MMA N
+constexpr int kGPanelA = kGM * 128;       // bytes of one 64-column A panel
+constexpr int kGPanelB = kGMaxN * 128;    // bytes of one 64-column B panel
+constexpr unsigned int kGTmemCols = 64;   // accumulator columns (power of two >= 32)
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ unsigned long long umma_desc_k128_at(unsigned long long addr) {
+    unsigned long long d = (addr & 0x3FFFFull) >> 4;  // start address, 16-byte units
+    d |= 1ull << 16;                                   // leading byte offset (unused with swizzle)
+    d |= (1024ull >> 4) << 32;                         // stride byte offset between 8-row groups
+    d |= 1ull << 46;                                   // descriptor version of sm_100
+    d |= 2ull << 61;                                   // SWIZZLE_128B
+    return d;
+}
+
+// Byte offset of 16-byte chunk `gc` (0..23 over the three panels) of row `r` in a swizzled tile.
+__device__ __forceinline__ unsigned int swz_offset(int r, int gc, int panel_bytes) {
+    return (unsigned int)((gc >> 3) * panel_bytes + r * 128 + (((gc & 7) ^ (r & 7)) << 4));
+}
+
+struct GemmArgs {
+    const __half* x;     // [batch, d_in]
+    float* ws;           // [splits, n_pad, d_out] split-K partials
+    int batch;           // valid rows of x
+    int n_pad;           // batch rounded up to 16 (MMA N)
+    int x_vec_ok;        // x rows allow 16-byte loads
+};
+
 
 constexpr int kTGThreads = 1024;
 constexpr int kTGWarps = kTGThreads / 32;
@@ -465,6 +496,24 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
         if (!ok) atomicOr(err_flag, 2);
         if (C.error) atomicOr(err_flag, 1);
     }
+}
+
+// y[n, r] = f16( (sum_s ws[s, n, r]) * rscale[r] + tail[r, :] . x[n, 24 nb :] ), partials added in split order.
+__global__ void gemm_reduce_kernel(MatrixView mv, const __half* __restrict__ x, const float* __restrict__ ws,
+                                   __half* __restrict__ y, int batch, int n_pad, int splits) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n = blockIdx.y;
+    if (r >= mv.d_out || n >= batch) return;
+    float s = 0.0f;
+    for (int k = 0; k < splits; ++k) s += ws[((size_t)k * n_pad + n) * mv.d_out + r];
+    float t = 0.0f;
+    const __half* xt = x + (size_t)n * mv.d_in + (size_t)mv.nb * kDim;
+    for (int q = 0; q < mv.tail_w; ++q) {
+        const float w = mv.tail_f16 ? __half2float(((const __half*)mv.tail)[(size_t)r * mv.tail_w + q])
+                                    : ((const float*)mv.tail)[(size_t)r * mv.tail_w + q];
+        t = fmaf(w, __half2float(xt[q]), t);
+    }
+    y[(size_t)n * mv.d_out + r] = __float2half_rn(fmaf(s, mv.rscale[r], t));
 }
 
 // Shared-memory plan and the split of the column chunks into work units for a grid of `grid` CTAs: the

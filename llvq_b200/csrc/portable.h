@@ -34,3 +34,14 @@ LLVQ_HD unsigned int umulhi32(unsigned int a, unsigned int b) {
 }
 
 }  // namespace llvq
+
+#if defined(__CUDACC__)
+// First statement of a kernel that is launched with programmatic stream serialisation: lets the next
+// launch of the stream start its own preamble at once, then waits until the previous launch of the
+// stream has completed and its writes are visible. A no-op pair in an ordinary launch.
+__device__ __forceinline__ void llvq_dependent_enter() {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+#endif
+

@@ -13,6 +13,8 @@
 #include <cstdint>
 #include <cuda_fp16.h>
 
+#include "portable.h"
+
 namespace llvq {
 
 constexpr int kRotThreads = 1024;
@@ -144,6 +146,7 @@ __device__ __forceinline__ void rot_first_pass_store(float* s, const unsigned in
 __global__ void __launch_bounds__(kRotThreads)
 rot_apply_kernel(const __half* __restrict__ x, const unsigned int* __restrict__ signbits, const float* __restrict__ small,
                  float* __restrict__ out, int n, int m, int k, float inv) {
+    llvq_dependent_enter();
     extern __shared__ float rot_s[];
     float* s = rot_s;
     float* q = rot_s + rot_vec_words(n);
@@ -180,6 +183,7 @@ __global__ void __launch_bounds__(kRotThreads)
 add_rmsnorm_rotate_kernel(__half* __restrict__ x, const __half* __restrict__ delta, const __half* __restrict__ w,
                           const unsigned int* __restrict__ signbits, const float* __restrict__ small,
                           float* __restrict__ out, int n, int m, int k, float inv, float eps) {
+    llvq_dependent_enter();
     extern __shared__ float rot_s[];
     __shared__ float red[32];
     float* s = rot_s;
@@ -231,6 +235,7 @@ add_rmsnorm_rotate_kernel(__half* __restrict__ x, const __half* __restrict__ del
 __global__ void __launch_bounds__(kRotThreads)
 silu_mul_rotate_kernel(const __half* __restrict__ gu, const unsigned int* __restrict__ signbits,
                        const float* __restrict__ small, float* __restrict__ out, int n, int m, int k, float inv) {
+    llvq_dependent_enter();
     extern __shared__ float rot_s[];
     float* s = rot_s;
     float* q = rot_s + rot_vec_words(n);

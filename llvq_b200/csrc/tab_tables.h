@@ -48,6 +48,7 @@ constexpr unsigned int kT3S2 = 8;                      // bytes per state: (T0, 
 constexpr unsigned int kT3S1 = kT3D2 * kT3S2;
 constexpr unsigned int kT3S0 = kT3D1 * kT3S1;
 constexpr int kTailSlots = 6;                          // slots served by the tail tables
+constexpr unsigned int kOffLutCap = 131072;            // largest off-support arrangement count tabulated
 
 struct TabLayout {
     // byte offsets of the sections inside the blob; every section starts 16-byte aligned

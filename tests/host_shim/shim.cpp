@@ -8,7 +8,6 @@
 
 #include "../../llvq_b200/csrc/codebook.cpp"
 #include "../../llvq_b200/csrc/decode_generic.cuh"
-#include "../../llvq_b200/csrc/decode_fast.cuh"
 #include "../../llvq_b200/csrc/tab_tables.cpp"
 #include "../../llvq_b200/csrc/decode_tab.cuh"
 
@@ -67,45 +66,6 @@ uint64_t shim_fingerprint(void) {
     shim_decode_indices(probes.data(), (int64_t)probes.size(), pts.data(), shell.data(), 13);
     for (size_t i = 0; i < probes.size(); ++i) ok[i] = shell[i] != 255;
     return fingerprint_from_points(t.cb, probes, pts.data(), ok.data());
-}
-
-// The class-specialised decoders: returns per index the path taken
-// (0 slow, 1 odd/2 thresholds, 2 odd/3 thresholds, 3 even tables, -1 origin, -2 refused).
-void shim_decode_fast(const uint64_t* idx, int64_t n, int8_t* points, int8_t* path) {
-    static FastTablesHost fh;
-    static FastTables F;
-    static bool ready = false;
-    HostTables& t = tables();
-    if (!ready) {
-        build_fast_tables(t.cb, fh);
-        F.cls = fh.cls.data();
-        F.ends = (const unsigned long long*)t.cb.ends.data();
-        F.lut = t.lut.data();
-        F.golay = t.cb.golay;
-        F.lut_on = fh.lut_on.data();
-        F.lut_off = fh.lut_off.data();
-        F.lut_shift = 35;
-        ready = true;
-    }
-    for (int64_t b = 0; b < n; ++b) {
-        int8_t* out = points + b * kDim;
-        float scale;
-        path[b] = (int8_t)decode_fast_any(
-            F, idx[b], [&](int pos, float v) { out[pos] = (int8_t)v; },
-            [&](unsigned long long i) {
-                float s2;
-                decode_generic12(t.T, i, [&](int pos, int val) { out[pos] = (int8_t)val; }, &s2);
-            },
-            &scale);
-    }
-}
-
-void shim_fast_table_sizes(int64_t* out) {
-    FastTablesHost fh;
-    build_fast_tables(tables().cb, fh);
-    out[0] = (int64_t)fh.lut_on.size();
-    out[1] = (int64_t)fh.lut_off.size();
-    out[2] = (int64_t)(fh.slow_mass * 1e12);
 }
 
 // The state-table decoders the fused GEMV and GEMM run: per index the 24 coordinates and the family

@@ -148,46 +148,6 @@ def test_synthetic_generator_is_the_scalar_splitmix64():
     assert sh.d_out == 4 and sh.codes.size == 4 * 3 * 6 and np.array_equal(sh.tail, m.tail[2:6])
 
 
-def _shim_decode_fast(shim, idx):
-    idx = np.ascontiguousarray(idx, np.uint64)
-    pts = np.zeros((idx.size, 24), np.int8)
-    path = np.zeros(idx.size, np.int8)
-    shim.shim_decode_fast(idx.ctypes.data_as(C.c_void_p), C.c_int64(idx.size), pts.ctypes.data_as(C.c_void_p),
-                          path.ctypes.data_as(C.c_void_p))
-    return pts, path
-
-
-def test_class_specialised_decoders_match_oracle_on_every_class(shim, oracle):
-    """Both ends of all 301 classes, their neighbours and 200 draws inside each."""
-    idx = probe_indices(oracle, per_class_random=200, cap=12)
-    pts, path = _shim_decode_fast(shim, idx)
-    ref_pts, _ = _shim_decode(shim, idx, 12)  # generic decoder, itself pinned to the oracle above
-    assert np.array_equal(pts, ref_pts)
-    for k in range(0, idx.size, 37):
-        assert np.array_equal(pts[k], oracle.decode_index(int(idx[k])))
-    assert set(path.tolist()) >= {-1, 0, 1, 2, 3}  # every family was exercised
-    pts, path = _shim_decode_fast(shim, np.array([0, oracle.N12 + 1, (1 << 47) - 1], np.uint64))
-    assert path.tolist() == [-1, -2, -2] and not pts.any()
-
-
-def test_class_specialised_decoders_match_oracle_on_uniform_draws(shim, oracle):
-    from llvq_b200 import synth
-    g = synth.SplitMix64(0xFA57)
-    idx = g.take(400_000) % np.uint64(oracle.N12 + 1)
-    pts, path = _shim_decode_fast(shim, idx)
-    ref_pts, _, _, bad = oracle.decode_codes(synth.pack_codes(idx, np.zeros_like(idx)))
-    assert bad == 0 and np.array_equal(pts, ref_pts)
-    frac = {p: float((path == p).mean()) for p in (0, 1, 2, 3)}
-    assert frac[0] < 2e-3 and frac[3] > 0.45 and frac[1] > 0.2 and frac[2] > 0.2
-
-
-def test_fast_tables_are_small_and_cover_the_ball(shim):
-    out = (C.c_int64 * 3)()
-    shim.shim_fast_table_sizes(out)
-    assert out[0] < 10_000 and out[1] < 400_000   # entries of the on / off arrangement tables
-    assert out[2] / 1e12 < 1e-3                    # mass left to the generic decoder
-
-
 def _shim_decode_tab(shim, idx):
     idx = np.ascontiguousarray(idx, np.uint64)
     pts = np.zeros((idx.size, 24), np.int8)
