@@ -200,8 +200,13 @@ def decode_section(rt, torch, prompt_len=128, new_tokens=256, rotations=False, e
             torch.cuda.synchronize()
             times.append((t1 - t0, time.perf_counter() - t1))
         prefill_s, decode_s = min(t[0] for t in times), min(t[1] for t in times)
+        # the token step by phase, each phase's launches replayed apart at the last position (ms per token)
+        model._pos -= 1
+        phases = {k: round(v, 4) for k, v in model.phase_split().items()}
+        model._pos += 1
         return {"tok_per_s": (new_tokens - 1) / decode_s, "ms_per_token": decode_s / (new_tokens - 1) * 1e3,
-                "prefill_ms": prefill_s * 1e3, "prefill_tok_per_s": prompt_len / prefill_s, "distinct_tokens": len(set(out))}
+                "prefill_ms": prefill_s * 1e3, "prefill_tok_per_s": prompt_len / prefill_s, "distinct_tokens": len(set(out)),
+                "phases_ms": phases}
 
     held = [{k: blk.pop(k) for k in list(blk) if k.startswith("rot_")} for blk in model.blocks]
     res = {"workload": "qwen3-4b-greedy-decode", "prompt_tokens": prompt_len, "new_tokens": new_tokens, "kv_cache": "int8 g64",

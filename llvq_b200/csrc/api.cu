@@ -707,7 +707,8 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
         if (st) return st;
     }
     const MatrixView mv = m->view();
-    const int grid = plan.units < rt->sm_count ? plan.units : rt->sm_count;
+    const int want_ctas = (plan.units + kTGHalves - 1) / kTGHalves;  // every CTA runs two unit streams
+    const int grid = want_ctas < rt->sm_count ? want_ctas : rt->sm_count;
     for (int b0 = 0; b0 < batch; b0 += kGMaxN) {
         const int nb_rows = batch - b0 < kGMaxN ? batch - b0 : kGMaxN;
         GemmArgs ga;

@@ -4,54 +4,69 @@
 //   Y[B, d_out] = X[B, d_in] * W^T,  B >= 16 (speculative tree verify, prefill slices)
 //
 // Every code is decoded ONCE per batch. One persistent CTA of 1024 threads per SM keeps
-// the decoder tables in shared memory and walks a static list of work units: a unit is
-// 128 rows of W times a range of column chunks (192 columns = 8 blocks per row = 1024
-// blocks per chunk, one per thread). Per chunk
+// the decoder tables in shared memory and runs as TWO independent halves of 16 warps, each
+// with its own operand tiles, lists, barriers and accumulator columns (what two CTAs per
+// SM would be, if two copies of the tables fitted): while one half waits for its slowest
+// warp or for its tensor-core work to drain, the other half decodes. A half walks a static
+// list of work units: a unit is 128 rows of W times a range of column chunks (96 columns =
+// 4 blocks per row = 512 blocks per chunk, one per thread of the half). Per chunk
 //   decode    warps draw batches of 32 same-family blocks (lists written one chunk
 //             ahead), run that family's decoder, scale the 24 signed bytes by
 //             gain centroid / sqrt(16 m) and write them as f16 into the A tile in shared
-//             memory (K-major, 128-byte swizzle, three 64-column panels); the X chunk
-//             goes into the B tile in the same layout;
+//             memory (K-major, 64-byte swizzle, three 32-column panels); the X chunk,
+//             loaded one chunk ahead, becomes the B tile in the same layout;
 //   classify  the warps that are done classify the NEXT chunk (48-bit record -> class ->
 //             family list) instead of waiting at the barrier: items, lists and counters
-//             are double (triple) buffered;
-//   MMA       one thread issues 12 tcgen05.mma (M = 128, N = padded batch, K = 16) that
+//             are double (triple) buffered, the groups of 32 blocks are handed out by tickets;
+//   MMA       one thread issues 6 tcgen05.mma (M = 128, N = padded batch, K = 16) that
 //             accumulate in TMEM and commits them onto an mbarrier; the tiles are free
 //             again when that barrier completes.
 // After the last chunk of a unit the f32 accumulators are read back with tcgen05.ld and
 // stored as split-K partials; gemm_reduce_kernel adds the partials in a fixed
 // order, applies the row scale and the tail columns, and narrows to f16 once.
 //
-// Every wait is bounded; on a time-out the kernel raises the error word, still frees its
-// TMEM columns and returns.
+// Every wait is bounded; on a time-out the half raises the error word and stops, the CTA still
+// frees its TMEM columns and returns.
 #pragma once
 #include <cuda_fp16.h>
 
-#include "gemv_pipe.cuh"  // bulk copies, bounded mbarrier waits
+#include "gemv_pipe.cuh"  // bulk copies, bounded mbarrier waits, group barriers
 
 namespace llvq {
 
-constexpr int kGM = 128;                  // rows of W per CTA = MMA M
-constexpr int kGKB = 8;                   // blocks per row and chunk: 8 * 24 = 192 = 3 * 64 columns
-constexpr int kGItems = kGM * kGKB;       // 1024 blocks per chunk
+constexpr int kGM = 128;                  // rows of W per unit = MMA M
+constexpr int kGKB = 4;                   // blocks per row and chunk: 4 * 24 = 96 = 3 * 32 columns
+constexpr int kGItems = kGM * kGKB;       // 512 blocks per chunk
 constexpr int kGMaxN = 64;                // padded batch per launch = MMA N
-constexpr int kGPanelA = kGM * 128;       // bytes of one 64-column A panel
-constexpr int kGPanelB = kGMaxN * 128;    // bytes of one 64-column B panel
-constexpr unsigned int kGTmemCols = 64;   // accumulator columns (power of two >= 32)
+constexpr int kGPanelA = kGM * 64;        // bytes of one 32-column A panel
+constexpr int kGPanelB = kGMaxN * 64;     // bytes of one 32-column B panel
+constexpr unsigned int kGTmemCols = 64;   // accumulator columns of one half (power of two >= 32)
+constexpr int kTGThreads = 1024;
+constexpr int kTGHalves = 2;
+constexpr int kTGHalfThreads = kTGThreads / kTGHalves;
+constexpr int kTGHalfWarps = kTGHalfThreads / 32;
+static_assert(kGItems == kTGHalfThreads, "one block of a chunk per thread of a half");
+static_assert(kGMaxN * 12 <= 2 * kTGHalfThreads, "two pieces of the B tile per thread");
+static_assert(kTGHalfThreads == kGroupThreads, "the halves use the group barriers of gemv_pipe.cuh");
+// A row's 4 records of a chunk (24 bytes, 2-byte aligned) are fetched as the 16-byte aligned range around
+// them: at most 14 + 24 bytes, rounded up to 48.
+constexpr unsigned int kGSlabLine = 48;
+constexpr int kGSlabThreads = kGM * 3;  // one 16-byte piece of the slab per thread
 
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ unsigned long long umma_desc_k128_at(unsigned long long addr) {
+// Shared-memory matrix descriptor: K-major operand, 64-byte swizzle, 8-row groups 512 bytes apart.
+__device__ __forceinline__ unsigned long long umma_desc_k64_at(unsigned long long addr) {
     unsigned long long d = (addr & 0x3FFFFull) >> 4;  // start address, 16-byte units
     d |= 1ull << 16;                                   // leading byte offset (unused with swizzle)
-    d |= (1024ull >> 4) << 32;                         // stride byte offset between 8-row groups
+    d |= (512ull >> 4) << 32;                          // stride byte offset between 8-row groups
     d |= 1ull << 46;                                   // descriptor version of sm_100
-    d |= 2ull << 61;                                   // SWIZZLE_128B
+    d |= 4ull << 61;                                   // SWIZZLE_64B
     return d;
 }
 
-// Byte offset of 16-byte chunk `gc` (0..23 over the three panels) of row `r` in a swizzled tile.
+// Byte offset of 16-byte piece `gc` (0..11 over the three panels) of row `r` in a tile of 64-byte rows with
+// the 64-byte swizzle: inside every 512-byte group of 8 rows, address bits 4-5 are XORed with bits 7-8.
 __device__ __forceinline__ unsigned int swz_offset(int r, int gc, int panel_bytes) {
-    return (unsigned int)((gc >> 3) * panel_bytes + r * 128 + (((gc & 7) ^ (r & 7)) << 4));
+    return (unsigned int)((gc >> 2) * panel_bytes + r * 64 + (((gc & 3) ^ ((r >> 1) & 3)) << 4));
 }
 
 struct GemmArgs {
@@ -62,28 +77,18 @@ struct GemmArgs {
     int x_vec_ok;        // x rows allow 16-byte loads
 };
 
-
-constexpr int kTGThreads = 1024;
-constexpr int kTGWarps = kTGThreads / 32;
-static_assert(kGMaxN * 24 <= 2 * kTGThreads, "two pieces of the B tile per thread");
-static_assert(kGItems == kTGThreads, "one block of a chunk per thread");
-// A row's 8 records of a chunk (48 bytes, 2-byte aligned) are fetched as the 16-byte aligned range around
-// them: at most 14 + 48 bytes, rounded up to 64.
-constexpr unsigned int kGSlabLine = 64;
-constexpr int kGSlabThreads = kGM * 4;  // one 16-byte piece of the slab per thread
-
 struct GemmTabPlan {
     unsigned int blob;    // decoder tables
-    unsigned int tiles;   // A panels (3 x 16 KB) then B panels (3 x 8 KB), 1024-byte aligned in the shared window
-    unsigned int items;   // 2 x 1024 x 8
-    unsigned int lists;   // 2 x 2 x 1024 x 2
-    unsigned int slab;    // packed codes of one chunk: 128 lines of 64 bytes
+    unsigned int tiles;   // per half: A panels (3 x 8 KB) then B panels (3 x 4 KB); 1024-byte aligned in the shared window
+    unsigned int items;   // per half: 2 x 512 x 8
+    unsigned int lists;   // per half: 2 x 2 x 512 x 2
+    unsigned int slab;    // per half: packed codes of one chunk, 128 lines of 48 bytes
     unsigned int ctrl;
     unsigned int total;
     int units, splits, chunks_per_split, row_tiles;
 };
 
-// Position of a CTA in its sequence of chunks: unit = row tile * splits + split.
+// Position of a half in its sequence of chunks: unit = row tile * splits + split.
 struct alignas(16) GemmTabIt {
     int unit, useq, c, c_end, row0, split;
     int valid, first, last, pad;
@@ -110,19 +115,21 @@ struct alignas(16) GemmTabIt {
     }
 };
 
-struct alignas(16) GemmTabCtrl {
+struct alignas(16) GemmTabShared {
     unsigned long long mbar_tab[2];  // decoder tables: classification part, decode part
-    unsigned long long mbar_mma;
-    unsigned long long mbar_slab;    // codes of chunk q: completion number q
     unsigned int tmem_base;
     int error;
+};
+struct alignas(16) GemmTabCtrl {     // one per half
+    unsigned long long mbar_mma;
+    unsigned long long mbar_slab;    // codes of chunk q: completion number q
     alignas(16) int count[3][4];     // items per family of chunk q at count[q % 3]
     int ticket[3];
     int cticket[3];                  // groups of 32 blocks of chunk q handed out for classification
-    unsigned int zero[2][kTGWarps];  // blocks of chunk q that decode to nothing, one bit per block, at zero[q & 1]
-    int done_row0, done_split;       // the unit whose accumulators are read back next (written by thread 0)
-    GemmTabIt it[3];                 // chunk q of this CTA at it[q % 3]; thread 0 writes chunk q + 2 during iteration q
-    float2 cent[2][kGM];             // gain centroids of the rows of the k-th unit of this CTA at cent[k & 1]
+    unsigned int zero[2][kTGHalfWarps];  // blocks of chunk q that decode to nothing, one bit per block, at zero[q & 1]
+    int done_row0, done_split;       // the unit whose accumulators are read back next (written by the half's thread 0)
+    GemmTabIt it[3];                 // chunk q of this half at it[q % 3]; thread 0 writes chunk q + 2 during iteration q
+    float2 cent[2][kGM];             // gain centroids of the rows of the k-th unit of this half at cent[k & 1]
 };
 
 __device__ __forceinline__ unsigned int gemm_tab_list_slot(unsigned int lists, unsigned int fam, int i) {
@@ -138,12 +145,15 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
                      int* __restrict__ err_flag) {
     extern __shared__ __align__(128) unsigned char gts_raw[];
     const unsigned int sbase = pipe_smem_addr(gts_raw);
+    const int tid = threadIdx.x;
+    const int half = tid / kTGHalfThreads;
+    const int gt = tid - half * kTGHalfThreads, lane = gt & 31, warp = gt >> 5;  // position inside the half
     // the swizzled panels need 1024-byte alignment in the shared window
     const unsigned int pad = (1024u - ((sbase + P.tiles) & 1023u)) & 1023u;
-    const unsigned int a_tile = sbase + P.tiles + pad;  // shared-window addresses
+    const unsigned int a_tile = sbase + P.tiles + pad + (unsigned int)half * (3u * kGPanelA + 3u * kGPanelB);  // shared-window addresses
     const unsigned int b_tile = a_tile + 3u * kGPanelA;
-    GemmTabCtrl& C = *reinterpret_cast<GemmTabCtrl*>(gts_raw + P.ctrl);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    GemmTabShared& S = *reinterpret_cast<GemmTabShared*>(gts_raw + P.ctrl);
+    GemmTabCtrl& C = reinterpret_cast<GemmTabCtrl*>(gts_raw + P.ctrl + sizeof(GemmTabShared))[half];
     const int nb = mv.nb;
     const int n_chunks = (nb + kGKB - 1) / kGKB;
 
@@ -154,18 +164,28 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
     T.L = L;
 
     if (tid == 0) {
-        C.error = 0;
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&C.mbar_tab[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&C.mbar_tab[1])));
+        S.error = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&S.mbar_tab[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&S.mbar_tab[1])));
+    }
+    if (gt == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&C.mbar_mma)));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pipe_smem_addr(&C.mbar_slab)), "r"(kGSlabThreads));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // The half's position in its chunk sequence lives in shared memory (every thread would otherwise carry it
+        // in registers across the decoders): thread 0 steps it two chunks ahead, barriers publish it.
+        GemmTabIt it;
+        it.open((int)blockIdx.x * kTGHalves + half, 0, P, n_chunks);
+        it.pad = 0;
+        C.it[0] = it;
+        if (it.valid) it.step(P, n_chunks, (int)gridDim.x * kTGHalves);
+        C.it[1] = it;
     }
-    if (tid < 12) (&C.count[0][0])[tid] = 0;
-    if (tid < 3) C.ticket[tid] = C.cticket[tid] = 0;
-    if (warp == 0) {  // one warp allocates the accumulator columns and gives the permit back
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pipe_smem_addr(&C.tmem_base)),
-                     "r"(kGTmemCols)
+    if (gt < 12) (&C.count[0][0])[gt] = 0;
+    if (gt < 3) C.ticket[gt] = C.cticket[gt] = 0;
+    if (tid < 32) {  // one warp allocates the accumulator columns of both halves and gives the permit back
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pipe_smem_addr(&S.tmem_base)),
+                     "r"(kGTmemCols * kTGHalves)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -173,27 +193,27 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (tid == 0) {
-        pipe_expect_tx(pipe_smem_addr(&C.mbar_tab[0]), L.classify_bytes);
-        pipe_bulk_copy(T.base, blob_g, L.classify_bytes, pipe_smem_addr(&C.mbar_tab[0]));
-        pipe_expect_tx(pipe_smem_addr(&C.mbar_tab[1]), L.total_bytes - L.classify_bytes);
+        pipe_expect_tx(pipe_smem_addr(&S.mbar_tab[0]), L.classify_bytes);
+        pipe_bulk_copy(T.base, blob_g, L.classify_bytes, pipe_smem_addr(&S.mbar_tab[0]));
+        pipe_expect_tx(pipe_smem_addr(&S.mbar_tab[1]), L.total_bytes - L.classify_bytes);
         pipe_bulk_copy(T.base + L.classify_bytes, blob_g + L.classify_bytes, L.total_bytes - L.classify_bytes,
-                       pipe_smem_addr(&C.mbar_tab[1]));
+                       pipe_smem_addr(&S.mbar_tab[1]));
     }
     bool ok = true;
     {
-        const bool landed = tid != 0 || pipe_mbar_wait(pipe_smem_addr(&C.mbar_tab[0]));
+        const bool landed = tid != 0 || pipe_mbar_wait(pipe_smem_addr(&S.mbar_tab[0]));
         ok = __syncthreads_and(landed);
     }
 
-    // Asynchronous copy of a chunk's packed codes into the slab: threads 0 .. 511 bring one 16-byte piece each
-    // (four pieces per row: the 16-byte aligned range around the row's 48 bytes; the code stream carries 64 bytes
-    // of padding, so the last piece may run past the last record) and arrive on the slab barrier when their
-    // piece has landed. A bulk copy per row would be 128 requests of 64 bytes per chunk, which the copy engine
-    // serves slower than a chunk is decoded.
-    const unsigned int slab = sbase + P.slab, bar_slab = pipe_smem_addr(&C.mbar_slab);
+    // Asynchronous copy of a chunk's packed codes into the slab: threads 0 .. 383 of the half bring one 16-byte
+    // piece each (three pieces per row: the 16-byte aligned range around the row's 24 bytes; the code stream
+    // carries 64 bytes of padding, so the last piece may run past the last record) and arrive on the slab barrier
+    // when their piece has landed. A bulk copy per row would be 128 small requests per chunk, which the copy
+    // engine serves slower than a chunk is decoded.
+    const unsigned int slab = sbase + P.slab + (unsigned int)half * (kGM * kGSlabLine), bar_slab = pipe_smem_addr(&C.mbar_slab);
     auto issue_slab = [&](const GemmTabIt& it) {
-        if (tid < kGSlabThreads) {
-            const int lr = tid >> 2, piece = tid & 3;
+        if (gt < kGSlabThreads) {
+            const int lr = gt / 3, piece = gt - 3 * lr;
             const int ncols = min(kGKB, nb - it.c * kGKB);
             if (it.row0 + lr < mv.d_out) {
                 const unsigned char* src = mv.codes + ((size_t)(it.row0 + lr) * nb + (size_t)it.c * kGKB) * 6;
@@ -212,17 +232,17 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
     // the warps with the long batches none. A block that decodes to nothing is noted in C.zero (its A entries
     // must read zero). Returns false when the wait for the codes ran out.
     auto classify = [&](const GemmTabIt& it, int q) -> bool {
-        const unsigned int items = sbase + P.items + (unsigned int)(q & 1) * (8u * kGItems);
-        const unsigned int lists = sbase + P.lists + (unsigned int)(q & 1) * (4u * kGItems);
+        const unsigned int items = sbase + P.items + (unsigned int)(2 * half + (q & 1)) * (8u * kGItems);
+        const unsigned int lists = sbase + P.lists + (unsigned int)(2 * half + (q & 1)) * (4u * kGItems);
         int* count = C.count[q % 3];
-        if (it.first && tid < kGM) C.cent[it.useq & 1][tid] = __ldg(mv.cent + min(it.row0 + tid, mv.d_out - 1));
+        if (it.first && gt < kGM) C.cent[it.useq & 1][gt] = __ldg(mv.cent + min(it.row0 + gt, mv.d_out - 1));
         if (!__all_sync(0xffffffffu, pipe_mbar_wait(bar_slab, (unsigned int)q & 1u))) return false;  // warp-uniform
         for (;;) {
             int g = 0;
             if (lane == 0) g = atomicAdd(&C.cticket[q % 3], 1);
             g = __shfl_sync(0xffffffffu, g, 0);
-            if (g >= kTGWarps) break;
-            const int f = 32 * g + lane, lr = f >> 3, kb = f & 7;
+            if (g >= kTGHalfWarps) break;
+            const int f = 32 * g + lane, lr = f >> 2, kb = f & 3;
             unsigned int fam = 4u;
             if (it.row0 + lr < mv.d_out && it.c * kGKB + kb < nb) {
                 const unsigned int sh = (unsigned int)((uintptr_t)(mv.codes + ((size_t)(it.row0 + lr) * nb + (size_t)it.c * kGKB) * 6) & 15u);
@@ -240,7 +260,7 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
                                  "r"((unsigned int)(cl.local2 >> 32) | (unsigned int)cl.ci << 13)
                                  : "memory");
                 } else if (cl.fam == -2) {
-                    C.error = 1;
+                    S.error = 1;
                 }
             }
             const unsigned int none = __ballot_sync(0xffffffffu, fam == 4u);
@@ -258,13 +278,13 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
         return true;
     };
 
-    // Piece i (of n_pad * 24 16-byte pieces) of a chunk's B tile: rows beyond the batch and columns beyond the
+    // Piece i (of n_pad * 12 16-byte pieces) of a chunk's B tile: rows beyond the batch and columns beyond the
     // last block read zero so that no stray NaN meets a zero weight.
     auto load_x = [&](const GemmTabIt& it, int i) -> uint4 {
-        const int n = i / 24, gc = i - n * 24;
+        const int n = i / 12, gc = i - n * 12;
         const int col = it.c * kGKB * kDim + gc * 8;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (i < ga.n_pad * 24 && n < ga.batch && col + 8 <= nb * kDim) {
+        if (i < ga.n_pad * 12 && n < ga.batch && col + 8 <= nb * kDim) {
             const __half* src = ga.x + (size_t)n * mv.d_in + col;
             if (ga.x_vec_ok) {
                 v = *reinterpret_cast<const uint4*>(src);
@@ -279,14 +299,15 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
         return v;
     };
     auto store_x = [&](int i, uint4 v) {
-        const int n = i / 24, gc = i - n * 24;
-        if (i < ga.n_pad * 24) sts128(b_tile + swz_offset(n, gc, kGPanelB), v);
+        const int n = i / 12, gc = i - n * 12;
+        if (i < ga.n_pad * 12) sts128(b_tile + swz_offset(n, gc, kGPanelB), v);
     };
 
-    // Accumulators of a finished unit -> split-K partials ws[split][n][row] (warps 0-3: TMEM lanes 32 w .. 32 w + 31).
+    // Accumulators of a finished unit -> split-K partials ws[split][n][row] (warps 0-3 of the half: a warp may
+    // touch the TMEM lanes 32 (warp % 4) .. + 31, and warps 0-3 of either half have warp % 4 = their index).
     auto store_unit = [&]() {
         if (warp < 4) {
-            const unsigned int tmem = C.tmem_base;
+            const unsigned int tmem = S.tmem_base + (unsigned int)half * kGTmemCols;
             const int row = C.done_row0 + 32 * warp + lane;
             float* dst = ga.ws + (size_t)C.done_split * ga.n_pad * mv.d_out + row;
             for (int n0 = 0; n0 < ga.n_pad; n0 += 4) {
@@ -304,63 +325,51 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     };
 
-    // The CTA's position in its chunk sequence lives in shared memory (every thread would otherwise carry it
-    // in registers across the decoders): thread 0 steps it two chunks ahead, barriers publish it.
-    if (tid == 0) {
-        GemmTabIt it;
-        it.open(blockIdx.x, 0, P, n_chunks);
-        it.pad = 0;
-        C.it[0] = it;
-        it.step(P, n_chunks, (int)gridDim.x);
-        C.it[1] = it;
-    }
-    __syncthreads();
     bool prev_last = false;  // the previous chunk closed its unit: read the accumulators back before the next MMA
     uint4 xr = make_uint4(0, 0, 0, 0);  // this thread's first piece of the next B tile, loaded one chunk ahead
     {
         bool landed = true;
         if (ok && C.it[0].valid) {
             issue_slab(C.it[0]);
-            xr = load_x(C.it[0], tid);
+            xr = load_x(C.it[0], gt);
             landed = classify(C.it[0], 0);
         }
         // the decode tables must have landed before the first decode; the first chunk's lists are complete
-        landed = landed && (tid != 0 || pipe_mbar_wait(pipe_smem_addr(&C.mbar_tab[1])));
+        landed = landed && (tid != 0 || pipe_mbar_wait(pipe_smem_addr(&S.mbar_tab[1])));
         ok = __syncthreads_and(landed && ok);
     }
-    
 
-    int q = 0;  // chunks issued so far = groups of MMAs committed on mbar_mma
+    int q = 0;  // chunks issued so far by this half = groups of MMAs committed on its mbar_mma
     for (; ok && C.it[q % 3].valid; ++q) {
         const GemmTabIt& cur = C.it[q % 3];
         // ---- the tiles are free once the previous chunk's MMAs have completed ----
         if (q > 0) {  // chunk q - 1 was commit number q - 1 on the barrier
-            const bool done = tid != 0 || pipe_mbar_wait(pipe_smem_addr(&C.mbar_mma), (unsigned int)((q - 1) & 1));
-            ok = __syncthreads_and(done);
+            const bool done = gt != 0 || pipe_mbar_wait(pipe_smem_addr(&C.mbar_mma), (unsigned int)((q - 1) & 1));
+            ok = pipe_group_sync_and(half, done);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        if (tid == 0) {  // counters and position of the chunk after the next one
+        if (gt == 0) {  // counters and position of the chunk after the next one
 #pragma unroll
             for (int k = 0; k < 4; ++k) C.count[(q + 2) % 3][k] = 0;
             C.ticket[(q + 2) % 3] = 0;
             C.cticket[(q + 2) % 3] = 0;
             GemmTabIt it = C.it[(q + 1) % 3];
-            if (it.valid) it.step(P, n_chunks, (int)gridDim.x);
+            if (it.valid) it.step(P, n_chunks, (int)gridDim.x * kTGHalves);
             C.it[(q + 2) % 3] = it;
         }
-        const unsigned int items = sbase + P.items + (unsigned int)(q & 1) * (8u * kGItems);
-        const unsigned int lists = sbase + P.lists + (unsigned int)(q & 1) * (4u * kGItems);
+        const unsigned int items = sbase + P.items + (unsigned int)(2 * half + (q & 1)) * (8u * kGItems);
+        const unsigned int lists = sbase + P.lists + (unsigned int)(2 * half + (q & 1)) * (4u * kGItems);
         // the slab is free (chunk q was classified before the last barrier): fetch the next chunk's codes
         if (C.it[(q + 1) % 3].valid) issue_slab(C.it[(q + 1) % 3]);
         // zero the block nobody decodes; the X chunk, loaded an iteration ago, becomes the B tile
         if ((C.zero[q & 1][warp] >> lane) & 1u) {
 #pragma unroll
             for (int j = 0; j < 3; ++j)
-                sts128(a_tile + swz_offset(tid >> 3, 3 * (tid & 7) + j, kGPanelA), make_uint4(0, 0, 0, 0));
+                sts128(a_tile + swz_offset(gt >> 2, 3 * (gt & 3) + j, kGPanelA), make_uint4(0, 0, 0, 0));
         }
-        store_x(tid, xr);
-        if (tid + kTGThreads < ga.n_pad * 24) store_x(tid + kTGThreads, load_x(cur, tid + kTGThreads));  // batches beyond 42 rows
+        store_x(gt, xr);
+        if (gt + kTGHalfThreads < ga.n_pad * 12) store_x(gt + kTGHalfThreads, load_x(cur, gt + kTGHalfThreads));  // batches beyond 42 rows
         // the finished unit's accumulators are overwritten by this chunk's first MMA (after the next barrier)
         if (prev_last) store_unit();
 
@@ -401,13 +410,12 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
                     scale = tab_decode_odd3(T, ci, local, V);
                 else if (fam == kFamOdd4)
                     scale = tab_decode_odd4(T, ci, local, V);
-                else
-                    {
+                else {
                     const TabRareBlock r = tab_decode_rare_call(T.base, lut_off, lut_on3, L, ci, local);
                     V[0] = r.v0; V[1] = r.v1; V[2] = r.v2; V[3] = r.v3; V[4] = r.v4; V[5] = r.v5;
                     scale = r.scale;
                 }
-                const int lr = (int)((f & 0xffffu) >> 3), kb = (int)(f & 7u);
+                const int lr = (int)((f & 0xffffu) >> 2), kb = (int)(f & 3u);
                 const float2 cg = C.cent[cur.useq & 1][lr];
                 const __half2 s2 = __float2half2_rn(scale * ((f >> 16) ? cg.y : cg.x));
                 // signed byte b -> f16: the byte, offset to 0..255, dropped into the mantissa of 1024 gives
@@ -434,32 +442,32 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
         const GemmTabIt& nxt = C.it[(q + 1) % 3];
         bool landed = true;
         if (nxt.valid) {
-            xr = load_x(nxt, tid);  // in flight during the classification
+            xr = load_x(nxt, gt);  // in flight during the classification
             landed = classify(nxt, q + 1);
         }
 
         // generic-proxy writes must be visible to the tensor core's asynchronous reads
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        ok = __syncthreads_and(landed);
+        ok = pipe_group_sync_and(half, landed);
         if (!ok) break;
 
-        // ---- MMA: 3 panels x 4 K-steps of 16, accumulating in TMEM ----
-        if (tid == 0) {
+        // ---- MMA: 3 panels x 2 K-steps of 16, accumulating in TMEM ----
+        if (gt == 0) {
             if (cur.last) {  // read by warps 0-3 after the next barrier
                 C.done_row0 = cur.row0;
                 C.done_split = cur.split;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned int tmem = C.tmem_base;
+            const unsigned int tmem = S.tmem_base + (unsigned int)half * kGTmemCols;
             // instruction descriptor: D = f32, A = B = f16, both K-major, N = n_pad, M = 128
             const unsigned int idesc = (1u << 4) | ((unsigned int)(ga.n_pad >> 3) << 17) | ((unsigned int)(kGM >> 4) << 24);
 #pragma unroll
             for (int p = 0; p < 3; ++p) {
-                const unsigned long long da = umma_desc_k128_at(a_tile + p * kGPanelA), db = umma_desc_k128_at(b_tile + p * kGPanelB);
+                const unsigned long long da = umma_desc_k64_at(a_tile + p * kGPanelA), db = umma_desc_k64_at(b_tile + p * kGPanelB);
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
+                for (int kk = 0; kk < 2; ++kk) {
                     const unsigned int accumulate = (cur.first == 0 || p > 0 || kk > 0) ? 1u : 0u;
-                    // +32 bytes (two 16-byte units) per K-step inside a swizzled 128-byte row
+                    // +32 bytes (two 16-byte units) per K-step inside a swizzled 64-byte row
                     asm volatile(
                         "{\n\t.reg .pred p;\n\t"
                         "setp.ne.b32 p, %4, 0;\n\t"
@@ -476,25 +484,22 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
         prev_last = cur.last != 0;
     }
 
-    // ---- the last unit: wait for its MMAs, read the accumulators, store the partials ----
+    // ---- the half's last unit: wait for its MMAs, read the accumulators, store the partials ----
     if (ok && q > 0) {
-        const bool done = tid != 0 || pipe_mbar_wait(pipe_smem_addr(&C.mbar_mma), (unsigned int)((q - 1) & 1));
-        ok = __syncthreads_and(done);
+        const bool done = gt != 0 || pipe_mbar_wait(pipe_smem_addr(&C.mbar_mma), (unsigned int)((q - 1) & 1));
+        ok = pipe_group_sync_and(half, done);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) store_unit();
     }
-    if (q == 0) {
-        // nothing to decode, but the table copy must not outlive the CTA
-        const bool landed = tid != 0 || pipe_mbar_wait(pipe_smem_addr(&C.mbar_tab[1]));
-        __syncthreads_and(landed);
-    }
+    // the halves meet again: the table copy must not outlive the CTA, TMEM is freed once nobody reads it
+    if (tid == 0) pipe_mbar_wait(pipe_smem_addr(&S.mbar_tab[1]));
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 0)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(C.tmem_base), "r"(kGTmemCols) : "memory");
+    const bool any_failed = __syncthreads_or(!ok);
+    if (tid < 32)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(S.tmem_base), "r"(kGTmemCols * kTGHalves) : "memory");
     if (tid == 0) {
-        if (!ok) atomicOr(err_flag, 2);
-        if (C.error) atomicOr(err_flag, 1);
+        if (any_failed) atomicOr(err_flag, 2);
+        if (S.error) atomicOr(err_flag, 1);
     }
 }
 
@@ -516,27 +521,28 @@ __global__ void gemm_reduce_kernel(MatrixView mv, const __half* __restrict__ x, 
     y[(size_t)n * mv.d_out + r] = __float2half_rn(fmaf(s, mv.rscale[r], t));
 }
 
-// Shared-memory plan and the split of the column chunks into work units for a grid of `grid` CTAs: the
-// split count that minimises the chunks of the busiest CTA (plus a small charge per unit for its read-back),
-// fewer splits on a tie.
+// Shared-memory plan and the split of the column chunks into work units for a grid of `grid` CTAs (two halves
+// each): the split count that minimises the chunks of the busiest half (plus a small charge per unit for its
+// read-back), fewer splits on a tie.
 inline GemmTabPlan gemm_tab_plan(const TabLayout& L, int d_out, int nb, int grid) {
     GemmTabPlan p{};
     unsigned int at = 0;
     p.blob = at;
     at += (L.total_bytes + 127u) & ~127u;
     p.items = at;
-    at += 2u * 8u * kGItems;
+    at += kTGHalves * 2u * 8u * kGItems;
     p.lists = at;
-    at += 2u * 4u * kGItems;
+    at += kTGHalves * 2u * 4u * kGItems;
     p.slab = at;
-    at += kGM * kGSlabLine;
+    at += kTGHalves * kGM * kGSlabLine;
     p.ctrl = at;
-    at += (unsigned int)((sizeof(GemmTabCtrl) + 15) & ~(size_t)15);
+    at += (unsigned int)((sizeof(GemmTabShared) + kTGHalves * sizeof(GemmTabCtrl) + 15) & ~(size_t)15);
     p.tiles = at;
-    at += 3u * kGPanelA + 3u * kGPanelB + 1024u;  // room to round the panels up to a 1024-byte boundary
+    at += kTGHalves * (3u * kGPanelA + 3u * kGPanelB) + 1024u;  // room to round the panels up to a 1024-byte boundary
     p.total = at;
     p.row_tiles = (d_out + kGM - 1) / kGM;
     const int chunks = (nb + kGKB - 1) / kGKB;
+    const int streams = grid * kTGHalves;
     p.splits = 0;
     p.chunks_per_split = 1;
     double best = 0.0;
@@ -545,8 +551,8 @@ inline GemmTabPlan gemm_tab_plan(const TabLayout& L, int d_out, int nb, int grid
         const int real = (chunks + cps - 1) / cps;
         if (real != s) continue;
         const long long units = (long long)p.row_tiles * s;
-        const long long waves = (units + grid - 1) / grid;
-        const double cost = (double)waves * (cps + 0.25);
+        const long long waves = (units + streams - 1) / streams;
+        const double cost = (double)waves * (cps + 0.5);
         if (p.splits == 0 || cost < best - 1e-9) {
             best = cost;
             p.splits = s;

@@ -446,60 +446,117 @@ class FusedQwen3:
 
     def _fused_step(self):
         """One token: 4 fused GEMV launches and 4 small fused kernels per block (+ 4 all-gathers of row
-        shards on a tensor-parallel model), then the greedy head."""
+        shards on a tensor-parallel model), then the greedy head. With self._only set to a phase name only
+        that phase's launches are issued (phase_split times them apart)."""
         import ctypes as C
         import torch
         from ._lib import check
         L, cfg, tp = self.ops, self.cfg, self.tp
         st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         p = lambda t: C.c_void_p(t.data_ptr())
-        self._x.copy_(self.emb.lookup(self._tok)[0])
+        only = getattr(self, "_only", None)
+        on = lambda phase: only is None or only == phase
+        if on("embed"):
+            self._x.copy_(self.emb.lookup(self._tok)[0])
         delta = None
 
         def norm_then(blk, name, ln, delta, out):
             """x += delta; RMSNorm; the group's projection: with a rotation, normalisation and rotation are one kernel."""
             rot = blk.get("rot_" + name)
             if rot is None:
-                check(L.llvq_op_add_rmsnorm_h(p(self._x), p(delta) if delta is not None else None, p(blk[ln]), p(self._h),
-                                              cfg.hidden, cfg.eps, st))
-                self.gemv(blk[name], self._h, out=out)
+                if on("norm"):
+                    check(L.llvq_op_add_rmsnorm_h(p(self._x), p(delta) if delta is not None else None, p(blk[ln]), p(self._h),
+                                                  cfg.hidden, cfg.eps, st))
+                if on("projections"):
+                    self.gemv(blk[name], self._h, out=out)
             else:
                 xr = self._xr[cfg.hidden]
-                check(L.llvq_op_add_rmsnorm_rotate_h(p(self._x), p(delta) if delta is not None else None, p(blk[ln]), rot._h,
-                                                     p(xr), cfg.hidden, cfg.eps, st))
-                self.gemv_rotated(blk[name], xr, out=out)
+                if on("norm"):
+                    check(L.llvq_op_add_rmsnorm_rotate_h(p(self._x), p(delta) if delta is not None else None, p(blk[ln]), rot._h,
+                                                         p(xr), cfg.hidden, cfg.eps, st))
+                if on("projections"):
+                    self.gemv_rotated(blk[name], xr, out=out)
 
         for blk, cache in zip(self.blocks, self.caches):
             norm_then(blk, "qkv", "ln1", delta, self._qkv)
-            check(L.llvq_op_qkv_rope_cache_h(p(self._qkv), p(blk["q_norm"]), p(blk["k_norm"]), p(self.cos), p(self.sin),
-                                             p(self._pos), p(self._q), p(cache.q[0]), p(cache.s[0]), p(cache.b[0]),
-                                             p(cache.q[1]), p(cache.s[1]), p(cache.b[1]), self.h_loc, self.kv_loc,
-                                             cfg.head_dim, cfg.eps, st))
-            check(L.llvq_op_attn_decode_int8_h(p(self._q), p(cache.q[0]), p(cache.s[0]), p(cache.b[0]), p(cache.q[1]),
-                                               p(cache.s[1]), p(cache.b[1]), p(self._pos), p(self._ctx_loc), self.h_loc,
-                                               self.kv_loc, cfg.head_dim, self.attn_splits, p(self._attn_ws), st))
-            if tp:
+            if on("rope_kv_write"):
+                check(L.llvq_op_qkv_rope_cache_h(p(self._qkv), p(blk["q_norm"]), p(blk["k_norm"]), p(self.cos), p(self.sin),
+                                                 p(self._pos), p(self._q), p(cache.q[0]), p(cache.s[0]), p(cache.b[0]),
+                                                 p(cache.q[1]), p(cache.s[1]), p(cache.b[1]), self.h_loc, self.kv_loc,
+                                                 cfg.head_dim, cfg.eps, st))
+            if on("attention"):
+                check(L.llvq_op_attn_decode_int8_h(p(self._q), p(cache.q[0]), p(cache.s[0]), p(cache.b[0]), p(cache.q[1]),
+                                                   p(cache.s[1]), p(cache.b[1]), p(self._pos), p(self._ctx_loc), self.h_loc,
+                                                   self.kv_loc, cfg.head_dim, self.attn_splits, p(self._attn_ws), st))
+            if tp and on("gathers"):
                 tp.gather_into(0, self._ctx, self._ctx_loc)
-            self._gemv(blk, "o", self._ctx, self._o_loc)
-            if tp:
+            if on("projections"):
+                self._gemv(blk, "o", self._ctx, self._o_loc)
+            if tp and on("gathers"):
                 tp.gather_into(1, self._o, self._o_loc)
             norm_then(blk, "gate_up", "ln2", self._o, self._gu)
             rot_down = blk.get("rot_down")
             if rot_down is not None and not tp:  # one rank holds the whole SwiGLU product: gate, rotate, project
                 xr = self._xr[cfg.inter]
-                check(L.llvq_op_silu_mul_rotate_h(p(self._gu), rot_down._h, p(xr), cfg.inter, st))
-                self.gemv_rotated(blk["down"], xr, out=self._down_loc)
+                if on("swiglu"):
+                    check(L.llvq_op_silu_mul_rotate_h(p(self._gu), rot_down._h, p(xr), cfg.inter, st))
+                if on("projections"):
+                    self.gemv_rotated(blk["down"], xr, out=self._down_loc)
             else:
-                check(L.llvq_op_silu_mul_h(p(self._gu), p(self._act_loc), self.inter_loc, st))
-                if tp:
+                if on("swiglu"):
+                    check(L.llvq_op_silu_mul_h(p(self._gu), p(self._act_loc), self.inter_loc, st))
+                if tp and on("gathers"):
                     tp.gather_into(2, self._act, self._act_loc)
-                self._gemv(blk, "down", self._act, self._down_loc)
-            if tp:
+                if on("projections"):
+                    self._gemv(blk, "down", self._act, self._down_loc)
+            if tp and on("gathers"):
                 tp.gather_into(3, self._down, self._down_loc)
             delta = self._down
-        check(L.llvq_op_add_rmsnorm_h(p(self._x), p(delta), p(self.final_norm), p(self._h), cfg.hidden, cfg.eps, st))
-        self._tok.copy_(self.pick(self._h))
-        self._pos += 1
+        if on("head"):
+            check(L.llvq_op_add_rmsnorm_h(p(self._x), p(delta), p(self.final_norm), p(self._h), cfg.hidden, cfg.eps, st))
+            self._tok.copy_(self.pick(self._h))
+        if only is None:
+            self._pos += 1
+
+    PHASES = ("embed", "norm", "projections", "rope_kv_write", "attention", "swiglu", "gathers", "head")
+
+    def phase_split(self, reps: int = 10) -> dict:
+        """Device time of one token step by phase, in ms: every phase's launches (all layers) captured as a graph
+        of their own and replayed `reps` times between two events, at the current position and token. The
+        phases run apart here, so their sum leaves out what the whole step gains by overlapping a kernel's
+        preamble with its predecessor and adds nothing for the gaps between kernels of different phases. The
+        counterpart of the reference's per-phase token timing (llvq-llm/tests/phase_timing.rs). Not for a
+        tensor-parallel model under NCCL gathers (a collective inside a partial graph needs every rank)."""
+        import torch
+        out = {}
+        tok0 = self._tok.clone()
+        for phase in self.PHASES:
+            if phase == "gathers" and not self.tp:
+                continue
+            self._only = phase
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    self._fused_step()
+                torch.cuda.current_stream().wait_stream(side)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._fused_step()
+                g.replay()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                for _ in range(reps):
+                    g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                out[phase] = e0.elapsed_time(e1) / reps
+            finally:
+                self._only = None
+                self._tok.copy_(tok0)
+        out["sum"] = sum(out.values())
+        return out
 
     def _graph_step(self):
         import torch

@@ -101,6 +101,24 @@ def test_graph_replay_gives_the_eager_tokens(rt):
     assert a.generate(prompt, 0) == []
 
 
+def test_phase_split_times_every_phase_and_leaves_the_model_untouched(rt):
+    """phase_split replays each phase's launches apart (graphs of their own): every phase of a single-GPU step is
+    reported, the sum is positive, and token, position and the tokens generated afterwards are what they were."""
+    import torch
+    from llvq_b200.model import Qwen3Config, synthetic_model
+    cfg = Qwen3Config(hidden=24 * 10 + 16, inter=24 * 20 + 16, n_heads=4, n_kv=2, head_dim=64, layers=2, vocab=512)
+    model, _ = synthetic_model(rt, cfg, config_id=2, capacity=64, row_scale_gain=40.0)
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    want = model.generate(prompt, 12, use_graph=True)
+    first = model.generate(prompt, 5, use_graph=True)
+    tok, pos = int(model._tok), int(model._pos)
+    ph = model.phase_split(reps=3)
+    assert set(ph) == {"embed", "norm", "projections", "rope_kv_write", "attention", "swiglu", "head", "sum"}
+    assert all(v > 0 for v in ph.values()) and abs(ph["sum"] - sum(v for k, v in ph.items() if k != "sum")) < 1e-6
+    assert (int(model._tok), int(model._pos)) == (tok, pos)
+    assert first == want[:5] and model.generate(prompt, 12, use_graph=True) == want
+
+
 def test_int8_kv_cache_matches_the_reference_scheme():
     """u8 affine, groups of 64, f16 scale and bias, constant groups exact (llvq-llm/src/kvq.rs:110-165)."""
     import torch
