@@ -718,14 +718,14 @@ int llvq_gemm_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t batch, l
         ga.n_pad = (nb_rows + 15) & ~15;
         ga.x_vec_ok = ((m->d_in & 7) == 0 && ((uintptr_t)ga.x & 15u) == 0) ? 1 : 0;
         if (splits > 0) {
-            llvq_gemm_tab_kernel<<<grid, kTGThreads, plan.total, s>>>((const unsigned char*)rt->d_tab_blob, (const OffEntry*)rt->d_tab_off,
-                                                                      (const unsigned long long*)rt->d_tab_on3, rt->TL, mv, ga, plan,
-                                                                      rt->d_err);
+            CUDA_TRY(launch_dep(llvq_gemm_tab_kernel, dim3(grid), dim3(kTGThreads), plan.total, s, (const unsigned char*)rt->d_tab_blob,
+                                (const OffEntry*)rt->d_tab_off, (const unsigned long long*)rt->d_tab_on3, rt->TL, mv, ga, plan,
+                                rt->d_err));
             g_launches++;
             CUDA_TRY(cudaGetLastError());
         }
-        gemm_reduce_kernel<<<dim3((m->d_out + 127) / 128, nb_rows), 128, 0, s>>>(
-            mv, ga.x, rt->gemm_ws, (__half*)y + (size_t)b0 * m->d_out, nb_rows, ga.n_pad, splits);
+        CUDA_TRY(launch_dep(gemm_reduce_kernel, dim3((m->d_out + 127) / 128, nb_rows), dim3(128), 0, s, mv, ga.x, rt->gemm_ws,
+                            (__half*)y + (size_t)b0 * m->d_out, nb_rows, ga.n_pad, splits));
         g_launches++;
         CUDA_TRY(cudaGetLastError());
     }

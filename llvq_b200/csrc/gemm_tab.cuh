@@ -192,6 +192,9 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // Programmatic dependent launch: the next kernel of the stream (the reduce kernel, then the next projection)
+    // may be scheduled as soon as this CTA leaves its SM; this launch came this far under the previous kernel's tail.
+    asm volatile("griddepcontrol.launch_dependents;");
     if (tid == 0) {
         pipe_expect_tx(pipe_smem_addr(&S.mbar_tab[0]), L.classify_bytes);
         pipe_bulk_copy(T.base, blob_g, L.classify_bytes, pipe_smem_addr(&S.mbar_tab[0]));
@@ -329,8 +332,12 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
     uint4 xr = make_uint4(0, 0, 0, 0);  // this thread's first piece of the next B tile, loaded one chunk ahead
     {
         bool landed = true;
+        if (ok && C.it[0].valid) issue_slab(C.it[0]);
+        // x may be the previous kernel's output and the split-K workspace may still be read by the previous
+        // projection's reduce kernel: from here on the previous kernel of the stream has completed (no-op for an
+        // ordinary launch). Tables and codes, all that was touched so far, are constant.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         if (ok && C.it[0].valid) {
-            issue_slab(C.it[0]);
             xr = load_x(C.it[0], gt);
             landed = classify(C.it[0], 0);
         }
@@ -506,6 +513,7 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
 // y[n, r] = f16( (sum_s ws[s, n, r]) * rscale[r] + tail[r, :] . x[n, 24 nb :] ), partials added in split order.
 __global__ void gemm_reduce_kernel(MatrixView mv, const __half* __restrict__ x, const float* __restrict__ ws,
                                    __half* __restrict__ y, int batch, int n_pad, int splits) {
+    llvq_dependent_enter();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     const int n = blockIdx.y;
     if (r >= mv.d_out || n >= batch) return;
