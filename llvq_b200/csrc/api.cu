@@ -1220,9 +1220,8 @@ int llvq_tp_exchange(llvq_tp_ctx* c, int32_t site, size_t buf_offset, const void
     int st = tp_fill_call(calls.c[0], c, site, buf_offset, src, shard_bytes);
     if (st) return st;
     DeviceGuard g(c->device);
-    tp_exchange_kernel<<<1, 32 * kTpMaxWorld, 0, (cudaStream_t)stream>>>(calls);
+    CUDA_TRY(launch_dep(tp_exchange_kernel, dim3(1), dim3(32 * kTpMaxWorld), 0, (cudaStream_t)stream, calls));
     g_launches++;
-    CUDA_TRY(cudaGetLastError());
     return LLVQ_OK;
 }
 

@@ -22,6 +22,8 @@
 #pragma once
 #include <cstdint>
 
+#include "portable.h"
+
 namespace llvq {
 
 constexpr int kTpMaxWorld = 8;
@@ -60,6 +62,9 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
 // grid = ranks carried by this launch (1 in production), block = 32 * kTpMaxWorld threads.
 __global__ void __launch_bounds__(32 * kTpMaxWorld)
 tp_exchange_kernel(TpCalls calls) {
+    // launched as a programmatic dependent in production: the consumer of the gathered buffer may load its tables
+    // while this kernel waits for the peers; nothing here runs before the kernels ahead in the stream are complete
+    llvq_dependent_enter();
     const TpCall& c = calls.c[blockIdx.x];
     const int lane = threadIdx.x & 31, p = threadIdx.x >> 5;
     const unsigned int seq = *reinterpret_cast<volatile unsigned int*>(c.r.seq) + 1u;

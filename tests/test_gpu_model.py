@@ -237,6 +237,26 @@ def test_chunked_prefill_and_library_attention_keep_the_tokens(rt):
     assert ((big.float() - small.float()).abs().max()).item() < 5e-3
 
 
+def test_rotated_prefill_stays_close_to_the_token_by_token_run(rt):
+    """With rotations on, a prompt of several rows goes through the batched GEMM, which takes f16 activations: the
+    rotated activation is rounded to f16 once per projection group, where the one-row path (and the reference,
+    which serves prompt rows as f32-activation matvecs: llvq-llm/src/model.rs:497-536) keeps f32. The test bounds
+    what that rounding costs: last-token logits of the prompt in one chunk against the same prompt fed row by row
+    (each row through the one-row path, attending to the cache written so far), and the same greedy token."""
+    import torch
+    from llvq_b200.model import Qwen3Config, synthetic_model
+    cfg = Qwen3Config(hidden=24 * 10 + 16, inter=24 * 20 + 16, n_heads=4, n_kv=2, head_dim=64, layers=2, vocab=512)
+    g = np.random.default_rng(31)
+    prompt = [int(t) for t in g.integers(0, cfg.vocab, 24)]
+    batched, _ = synthetic_model(rt, cfg, config_id=2, capacity=64, rotations=True, row_scale_gain=40.0)
+    rowwise, _ = synthetic_model(rt, cfg, config_id=2, capacity=64, rotations=True, row_scale_gain=40.0)
+    rowwise.prefill_chunk = 1
+    hb, hr = batched.prefill(prompt), rowwise.prefill(prompt)
+    lb, lr = batched.logits_last(hb), rowwise.logits_last(hr)
+    assert ((lb - lr).norm() / lr.norm()).item() < 1e-2
+    assert int(lb.argmax()) == int(lr.argmax())
+
+
 def _tp_gpu_worker(rank, world, port, q):
     """Child of the two-GPU test. Every outcome, an exception included, goes back through the queue, and the
     process leaves through os._exit so that a failed rank never waits on its peer in a teardown."""
