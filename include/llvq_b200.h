@@ -382,15 +382,16 @@ int llvq_tp_poll_error(llvq_tp_ctx* ctx, int32_t* out);
 /* llvq_gemv_h with parts of the kernel left out, for timing what the rest costs: the reference's
  * "floor" kernels (llvq-cuda/kernels/nullk.cu:61: same grid, staging and reduction, no weights;
  * llvq-cuda/kernels/llvq_floor.cuh:133-135: stream only / + table / + shared-memory reads).
- * mode 0 = the full kernel; 1 = no decoders (records are read and classified, activations staged,
- * rows summed and stored); 2 = no class search (records are only read); 3 = neither. y is NOT the
- * product for mode > 0. */
+ * mode is a bit set: 0 = the full kernel; bit 0 = no decoders (records are read and classified,
+ * activations staged, rows summed and stored); bit 1 = no class search (records are only read);
+ * bit 2 = no decode batches at all (0 to 7). y is NOT the product for mode > 0. */
 int llvq_gemv_probe_h(llvq_matrix* m, const uint16_t* x_dev, uint16_t* y_dev, int32_t mode, llvq_stream_t stream);
 
 /* One launch of the f16 GEMV kernel (mode as in llvq_gemv_probe_h) with time stamps: for each of
- * the first max_ctas CTAs, 64 uint64 nanosecond readings of the GPU's global timer: [0] kernel
- * entry, [1] tables and first codes landed, [2 + 2 i] end of pipeline interval i (after its barrier),
- * [3 + 2 i] arrival of one warp at that barrier; 0 where an event did not occur. The per-phase timing
+ * the first max_ctas CTAs, 64 uint64 nanosecond readings of the GPU's global timer taken by thread 0
+ * (first warp group): [0] kernel entry, [1] classification tables landed and first tile staged, then
+ * three readings per tile of that group: [2 + 3 i] end of its classification phase, [3 + 3 i] end of
+ * its decode phase, [4 + 3 i] end of its row sums; 0 where an event did not occur. The per-phase timing
  * the reference prints for a token (generate_phased, llvq-llm/src/model.rs:1116-1163), at the scale
  * of one kernel. Allocates and frees a device buffer; synchronises the stream. */
 #define LLVQ_TRACE_EVENTS 64
