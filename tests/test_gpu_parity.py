@@ -537,3 +537,40 @@ def test_overlapped_launches_keep_stream_order(rt):
         for p in projs:
             p.free()
     assert not rt.poll_range_error()
+
+
+def test_two_runtimes_on_two_devices_in_one_process(oracle):
+    """The opt-in shared-memory size of a kernel is a per-device setting: a second runtime on another GPU of the
+    same process must raise it again (and every launch must run on its runtime's device, whatever device is
+    current). One GEMV, one batched GEMM, one rotation and one attention-free decode-step kernel on each."""
+    torch = _torch()
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from llvq_b200 import FusedRuntime, synth
+    m = synth.make_matrix(300, 24 * 110 + 16, 0x2D0)
+    x = synth.make_activation(m.d_in, 9, np.float16)
+    tail16 = m.tail.astype(np.float16).astype(np.float32)
+    ref = oracle.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales, tail16, x.astype(np.float64))
+    outs = []
+    rts = [FusedRuntime(0), FusedRuntime(1)]
+    try:
+        for dev, r in enumerate(rts):
+            with torch.cuda.device(1 - dev):  # the "wrong" current device on purpose
+                proj = r.upload(m, tail_f16=True)
+                xd = torch.from_numpy(x).to(f"cuda:{dev}")
+                with torch.cuda.device(dev):
+                    y = r.forward(proj, xd)
+                    yb = r.forward_batch(proj, xd[None, :].repeat(16, 1).contiguous())
+                    rot = r.rotation(m.d_in, 77)
+                    xr = r.rotate(rot, xd)
+                    torch.cuda.synchronize()
+                assert rel_l2(y.cpu().numpy(), ref) <= TOL_F16
+                assert rel_l2(yb[3].cpu().numpy(), ref) <= TOL_F16
+                outs.append((y.cpu(), xr.cpu()))
+                rot.free()
+                proj.free()
+                assert not r.poll_range_error()
+        assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    finally:
+        for r in rts:
+            r.close()
