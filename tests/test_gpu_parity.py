@@ -547,7 +547,7 @@ def test_two_runtimes_on_two_devices_in_one_process(oracle):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     from llvq_b200 import FusedRuntime, synth
-    m = synth.make_matrix(300, 24 * 110 + 16, 0x2D0)
+    m = synth.make_matrix(300, 2560, 0x2D0)  # 106 blocks + 16 tail columns; 2560 = 512 * 5 has a servable rotation
     x = synth.make_activation(m.d_in, 9, np.float16)
     tail16 = m.tail.astype(np.float16).astype(np.float32)
     ref = oracle.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales, tail16, x.astype(np.float64))
