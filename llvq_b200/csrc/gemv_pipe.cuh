@@ -1,18 +1,20 @@
 // Persistent fused dequant-GEMV for sm_100a.
 //
 // One CTA of 1024 threads per SM owns a contiguous range of output rows and keeps
-// the decoder tables (tab_tables.h, 111 KB) in shared memory. Its rows are cut into
-// tiles of at most tile_max blocks (rows x a chunk of the columns, the whole row where its activation
-// digits fit the digit buffer; as many blocks
-// as the rest of shared memory holds: about 5 000). A tile goes through three
-// phases separated by CTA-wide barriers:
+// the decoder tables (tab_tables.h, 106 KB) in shared memory. The CTA runs as
+// kPipeGroups groups of warps, each with its own share of the rows, its own tile
+// buffers and its own named barrier. A group's rows are cut into tiles of at most
+// tile_max blocks (rows x a chunk of the columns: the whole row where its activation
+// digits fit the digit buffer; as many blocks as the group's share of the remaining
+// shared memory holds: about 2 400). A tile goes through three phases separated by
+// the group's barrier:
 //
 //   classify   the tile's packed codes are already in shared memory (one bulk
 //              asynchronous copy per contiguous range, cp.async.bulk completing on an
 //              mbarrier, started while the previous tile was being decoded). Every
 //              warp takes 32 blocks at a time: 48-bit record -> class -> family, an
 //              8-byte item at the block's own slot, the slot appended to its family's
-//              list (match.any + one shared-memory atomic per family and warp). A few
+//              list (ballots + one shared-memory atomic per family and warp). A few
 //              warps first turn the tile's activation columns into fixed-point digits
 //              and stage its rows' centroids, row scales and tail-column products.
 //   decode     warps draw batches of 32 same-family items, longest family first,
@@ -27,6 +29,10 @@
 // split into byte digits; sum_j v_j x_j is then exact in integers for the quantised
 // x (relative error per term 2^-16 resp. 2^-24 of the block's largest activation),
 // and independent of the order of evaluation.
+//
+// The kernel is launched with programmatic stream serialisation: it lets the next
+// launch of the stream start as soon as its own tables are on their way, and waits
+// for the previous launch only before it first touches the activation.
 #pragma once
 #include <cuda_fp16.h>
 
