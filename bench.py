@@ -269,6 +269,7 @@ def run_reference(args):
     val = nbytes / t / 1e9
     sample = "each step = the 7 projections of one layer (4 185 600 blocks) on all host threads"
     blocks = sum(m.n_blocks for m in mats)
+    gpu_kernel = reference_gpu_kernel(args)
     emit(({
         "impl": "reference", "metric": "dequant_gemv_algorithmic_GBps", "value": val, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
@@ -281,7 +282,63 @@ def run_reference(args):
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        # the reference's own serving kernel on its transcoded layout, where it was built (oracle/_ref): a side
+        # measurement of another format on this GPU, not the path of `value`
+        "reference_gpu_kernel": gpu_kernel,
     }))
+
+
+def reference_gpu_kernel(args, layers=4):
+    """The reference's serving GEMV (`tv_planes_h`, llvq-llm/kernels/tv_planes_h.cu:38-72, compiled by nvcc from the
+    reference's sources into oracle/_ref/libref_planes.so) on its Planes14 layout (14 bytes per block, written from the
+    same archive codes by oracle/planes14.py, the reference's own transcoder being Rust): one launch per projection,
+    `layers` distinct layers of the Qwen3-4B shapes (235 MB of records per pass, larger than L2), f32 activations in and
+    f16 out as its forward_rotated; device-timed. Reported with its parity against the f64 CPU reference."""
+    try:
+        import torch
+        from oracle import planes14, ref
+        from llvq_b200 import synth
+        if not planes14.available():
+            return {"unavailable": "oracle/_ref/libref_planes.so is not built (no checkout of the reference where the tree was built)"}
+        if not torch.cuda.is_available():
+            return {"unavailable": "no CUDA device"}
+        runner = planes14.Planes14Runner(0)
+        hs, xs, worst = [], [], 0.0
+        for l in range(layers):
+            for i, (name, m) in enumerate(synth.make_layer(MODEL, CONFIG_ID, l).items()):
+                h = runner.upload(m)
+                x = torch.from_numpy(synth.make_activation(m.d_in, 0x1000 + i, np.float32)).cuda()
+                if l == 0:  # every projection shape once against the CPU reference, before anything is timed
+                    y = runner.forward(h, x).float().cpu().numpy().astype(np.float64)
+                    want = ref.gemv_f64(m.codes, m.d_out, m.d_in, m.centroids, m.row_scales,
+                                        m.tail.astype(np.float16).astype(np.float32), x.cpu().numpy().astype(np.float64))
+                    worst = max(worst, float(np.linalg.norm(y - want) / np.linalg.norm(want)))
+                hs.append(h)
+                xs.append(x)
+        if not worst <= 1e-3:
+            return {"unavailable": f"the reference kernel's result differs from the CPU reference (relative L2 {worst:.3g})"}
+        ys = [torch.empty(h["d_out"], dtype=torch.float16, device="cuda") for h in hs]
+
+        def run():
+            for h, x, y in zip(hs, xs, ys):
+                runner.forward(h, x, out=y)
+        for _ in range(max(args.warmup, 3)):
+            run()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(max(args.steps, 5)):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / max(args.steps, 5)
+        blocks = sum(h["d_out"] * h["nb"] for h in hs)
+        return {"kernel": "tv_planes_h (reference, Planes14 layout, 14 bytes per block)", "layers_per_pass": layers,
+                "launches_per_pass": len(hs), "ms_per_pass": ms, "gblocks_per_s": blocks / ms / 1e6,
+                "layout_bytes_GBps": blocks * 14 / ms / 1e6, "archive_code_equiv_GBps": blocks * 6.54 / ms / 1e6,
+                "worst_rel_l2_vs_cpu_reference": worst}
+    except Exception as e:  # a side measurement must not take the arm down
+        return {"unavailable": f"{type(e).__name__}: {e}"}
 
 
 def run_tp_decode(args):

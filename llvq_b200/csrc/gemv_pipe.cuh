@@ -57,6 +57,10 @@ constexpr int kDigitBytes = 24576;    // shared memory given to the activation d
 constexpr int kTileRowsMax = 128;     // rows per tile
 constexpr int kStageWarps = 4 / kPipeGroups > 0 ? 4 / kPipeGroups : 1;  // warps of a group that stage the next tile's digits and row data
 constexpr unsigned int kPipeSpinLimit = 1u << 22;
+#ifndef LLVQ_CLS_GROUPS
+#define LLVQ_CLS_GROUPS 2
+#endif
+constexpr int kClsGroups = LLVQ_CLS_GROUPS;  // groups of 32 blocks a warp classifies per iteration (independent look-up chains)
 
 template <typename XT>
 struct XDigits;
@@ -588,11 +592,11 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
             // two groups of 32 blocks per iteration: their table look-ups are independent, so the scheduler can
             // overlap the shared-memory latency of one with the arithmetic of the other
 #pragma unroll 1
-            for (unsigned int f0 = 32u * warp; f0 < blocks; f0 += 64u * kGroupWarps) {
-                unsigned int fams[2], fs[2];
-                uint2 its[2];
+            for (unsigned int f0 = 32u * warp; f0 < blocks; f0 += 32u * kClsGroups * kGroupWarps) {
+                unsigned int fams[kClsGroups], fs[kClsGroups];
+                uint2 its[kClsGroups];
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
+                for (int u = 0; u < kClsGroups; ++u) {
                     const unsigned int f = f0 + 32u * kGroupWarps * u + lane;
                     fs[u] = f;
                     fams[u] = 4u;  // 4: nothing to decode
@@ -628,7 +632,7 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
+                for (int u = 0; u < kClsGroups; ++u) {
                     const unsigned int f = fs[u], fam = fams[u];
                     if (f < blocks)
                         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(items + 8u * f), "r"(its[u].x), "r"(its[u].y) : "memory");

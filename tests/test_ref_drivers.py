@@ -171,3 +171,54 @@ def test_gemv_tail_epilogue_against_the_reference_kernel_text(rt, vec, tw):
     assert np.array_equal(bits(y), bits(D.tail_dot_f32(tail, xt, fused=True)))
     mag = (np.abs(tail.view(np.float16).astype(np.float64)) * np.abs(xt.astype(np.float64))).sum(axis=1)
     assert (np.abs(y.astype(np.float64) - want) <= tw * 2.0 ** -24 * mag + 1e-45).all()
+
+
+# ---- the reference's served layout and its own serving kernel ---------------------------------------------
+
+def test_planes14_transcoder_round_trips_every_class(oracle):
+    """oracle/planes14.py writes the reference's 14-byte records (llvq-cuda/kernels/llvq_planes.cuh:1-40) from archive
+    codes; read back with the kernel's own field arithmetic they give the oracle's weights, on both ends of every class."""
+    from conftest import probe_indices
+    from llvq_b200 import synth
+    from oracle import planes14
+    idx = probe_indices(oracle, per_class_random=20, cap=12)
+    idx = idx[idx <= oracle.N12]
+    gain = (np.arange(idx.size) & 1).astype(np.uint64)
+    codes = synth.pack_codes(idx, gain)
+    words = planes14.transcode(codes)
+    assert words.dtype == np.uint32 and words.size * 4 == idx.size * 14 + 16
+    w, g = planes14.decode_stream(words, idx.size)
+    pts, shell, gain_ref, bad = oracle.decode_codes(codes)
+    assert bad == 0 and np.array_equal(g, gain_ref)
+    want = np.where(shell[:, None] > 0, pts / np.sqrt(16.0 * np.maximum(shell[:, None], 1)), 0.0).astype(np.float32)
+    assert np.array_equal(w, want)
+    tab, _, _ = planes14.class_tables()
+    assert tab.shape == (512, 6) and tab[:302, :5].max() <= 1.0 and (tab[302:, :5] == 0).all()
+
+
+@pytest.mark.gpu
+def test_reference_serving_kernel_agrees_with_the_fused_gemv(rt, oracle):
+    """The reference's own tv_planes_h (llvq-llm/kernels/tv_planes_h.cu:38-72), compiled from its sources and run on
+    its Planes14 layout of the same weights, against the f64 oracle and against this library's GEMV on the archive
+    codes: both within the f16 tolerance of the path, and of each other."""
+    import torch
+    from llvq_b200 import synth
+    from oracle import planes14
+    if not planes14.available():
+        pytest.skip("oracle/_ref/libref_planes.so is not built (no checkout of the reference where the tree was built)")
+    runner = planes14.Planes14Runner(0)
+    for d_out, d_in in ((256, 2560), (64, 24 * 140 + 8), (8, 24 * 3)):
+        m = synth.make_matrix(d_out, d_in, 0x914 + d_out)
+        x32 = synth.make_activation(d_in, 5, np.float32)
+        tail16 = m.tail.astype(np.float16).astype(np.float32)
+        ref = oracle.gemv_f64(m.codes, d_out, d_in, m.centroids, m.row_scales, tail16, x32.astype(np.float64))
+        h = runner.upload(m)
+        y_ref = runner.forward(h, torch.from_numpy(x32).cuda())
+        proj = rt.upload(m, tail_f16=True)
+        y_own = rt.forward_rotated(proj, torch.from_numpy(x32).cuda())  # f32 in, f16 out: the same signature
+        torch.cuda.synchronize()
+        a, b = y_ref.float().cpu().numpy().astype(np.float64), y_own.float().cpu().numpy().astype(np.float64)
+        assert np.linalg.norm(a - ref) <= 1e-3 * np.linalg.norm(ref)
+        assert np.linalg.norm(b - ref) <= 1e-3 * np.linalg.norm(ref)
+        assert np.linalg.norm(a - b) <= 1e-3 * np.linalg.norm(ref)
+        proj.free()
