@@ -68,6 +68,7 @@ struct DeviceGuard {
 };
 
 constexpr int kLutShift = 35;
+constexpr int kManySegments = 4;  // result segments of llvq_gemv_h_host_many
 
 // Launch with programmatic stream serialisation (see llvq_runtime_set_overlap): the kernel may be scheduled
 // while the previous kernel of the stream is still running; it orders itself behind that kernel with
@@ -132,6 +133,8 @@ struct llvq_runtime {
     int overlap_launches = 1;      // GEMV launches carry the programmatic-serialisation attribute
     // staging of llvq_gemv_h_host_many: one pinned host buffer and its device twin, grown on demand
     std::mutex many_mu;
+    cudaStream_t many_stream = nullptr;   // copy stream of llvq_gemv_h_host_many and its per-segment events
+    cudaEvent_t many_ready[4] = {nullptr, nullptr, nullptr, nullptr}, many_done[4] = {nullptr, nullptr, nullptr, nullptr};
     unsigned char* many_host = nullptr;
     unsigned char* many_dev = nullptr;
     size_t many_bytes = 0;
@@ -415,6 +418,13 @@ void llvq_runtime_destroy(llvq_runtime* rt) {
     cudaFree(rt->gemm_ws);
     cudaFreeHost(rt->many_host);
     cudaFree(rt->many_dev);
+    if (rt->many_stream) {
+        for (int k = 0; k < kManySegments; ++k) {
+            cudaEventDestroy(rt->many_ready[k]);
+            cudaEventDestroy(rt->many_done[k]);
+        }
+        cudaStreamDestroy(rt->many_stream);
+    }
     cudaFree(rt->d_tab_blob);
     cudaFree(rt->d_tab_off);
     cudaFree(rt->d_tab_on3);
@@ -1292,13 +1302,37 @@ int llvq_gemv_h_host_many(const llvq_host_call* calls, int32_t n, llvq_stream_t 
     }
     for (int i = 0; i < n; ++i) std::memcpy(rt->many_host + xo[i], calls[i].x_host, (size_t)calls[i].m->d_in * sizeof(__half));
     CUDA_TRY(cudaMemcpyAsync(rt->many_dev, rt->many_host, x_bytes, cudaMemcpyHostToDevice, s));
-    for (int i = 0; i < n; ++i) {
-        int st = launch_gemv<__half, __half>(calls[i].m, (const __half*)(rt->many_dev + xo[i]), (__half*)(rt->many_dev + yo[i]), s);
-        if (st) return st;
+    // The results come back in a few segments on a copy stream of the runtime: a segment's copy waits (event) for
+    // its last launch and runs while the next segment computes, and the host scatters a segment as soon as its
+    // copy has landed. Only the last segment's copy and scatter are left after the last kernel.
+    if (!rt->many_stream) {
+        CUDA_TRY(cudaStreamCreateWithFlags(&rt->many_stream, cudaStreamNonBlocking));
+        for (int k = 0; k < kManySegments; ++k) {
+            CUDA_TRY(cudaEventCreateWithFlags(&rt->many_ready[k], cudaEventDisableTiming));
+            CUDA_TRY(cudaEventCreateWithFlags(&rt->many_done[k], cudaEventDisableTiming));
+        }
     }
-    CUDA_TRY(cudaMemcpyAsync(rt->many_host + x_bytes, rt->many_dev + x_bytes, at - x_bytes, cudaMemcpyDeviceToHost, s));
-    CUDA_TRY(cudaStreamSynchronize(s));
-    for (int i = 0; i < n; ++i) std::memcpy(calls[i].y_host, rt->many_host + yo[i], (size_t)calls[i].m->d_out * sizeof(__half));
+    const int segs = n < kManySegments ? n : kManySegments;
+    int first[kManySegments + 1];
+    for (int k = 0; k <= segs; ++k) first[k] = (int)((long long)n * k / segs);
+    for (int k = 0; k < segs; ++k) {
+        for (int i = first[k]; i < first[k + 1]; ++i) {
+            int st = launch_gemv<__half, __half>(calls[i].m, (const __half*)(rt->many_dev + xo[i]), (__half*)(rt->many_dev + yo[i]), s);
+            if (st) return st;
+        }
+        const size_t lo = yo[first[k]], hi = first[k + 1] < n ? yo[first[k + 1]] : at;
+        CUDA_TRY(cudaEventRecord(rt->many_ready[k], s));
+        CUDA_TRY(cudaStreamWaitEvent(rt->many_stream, rt->many_ready[k], 0));
+        CUDA_TRY(cudaMemcpyAsync(rt->many_host + lo, rt->many_dev + lo, hi - lo, cudaMemcpyDeviceToHost, rt->many_stream));
+        CUDA_TRY(cudaEventRecord(rt->many_done[k], rt->many_stream));
+    }
+    for (int k = 0; k < segs; ++k) {
+        CUDA_TRY(cudaEventSynchronize(rt->many_done[k]));
+        for (int i = first[k]; i < first[k + 1]; ++i)
+            std::memcpy(calls[i].y_host, rt->many_host + yo[i], (size_t)calls[i].m->d_out * sizeof(__half));
+    }
+    // the caller's stream has nothing pending from this call; later work on it must also see the copy stream done
+    CUDA_TRY(cudaStreamWaitEvent(s, rt->many_done[segs - 1], 0));
     return LLVQ_OK;
 }
 
