@@ -119,6 +119,34 @@ def test_phase_split_times_every_phase_and_leaves_the_model_untouched(rt):
     assert first == want[:5] and model.generate(prompt, 12, use_graph=True) == want
 
 
+def test_dependent_launches_do_not_change_a_token(rt):
+    """Every kernel of the token step is launched as a programmatic dependent of the kernel before it (its preamble
+    may run early; it waits for that kernel before touching memory). The tokens and the final hidden state are
+    those of ordinary launches, eagerly and from a captured graph, with and without rotations."""
+    import torch
+    from llvq_b200.model import Qwen3Config, synthetic_model
+    cfg = Qwen3Config(hidden=24 * 10 + 16, inter=24 * 20 + 16, n_heads=4, n_kv=2, head_dim=64, layers=3, vocab=512)
+    prompt = [int(t) for t in np.random.default_rng(77).integers(0, cfg.vocab, 18)]
+    for rotations in (False, True):
+        runs = {}
+        for overlap in (False, True):
+            for use_graph in (False, True):
+                rt.set_overlap(overlap)
+                try:
+                    model, _ = synthetic_model(rt, cfg, config_id=2, capacity=64, rotations=rotations, row_scale_gain=40.0)
+                    toks = model.generate(prompt, 30, use_graph=use_graph)
+                    torch.cuda.synchronize()
+                    runs[(overlap, use_graph)] = (toks, model._x.clone())
+                finally:
+                    rt.set_overlap(True)
+        want_t, want_x = runs[(False, False)]
+        assert len(set(want_t)) > 4
+        for key, (toks, x) in runs.items():
+            assert toks == want_t, (rotations, key)
+            assert torch.equal(x, want_x), (rotations, key)
+    assert not rt.poll_range_error()
+
+
 def test_int8_kv_cache_matches_the_reference_scheme():
     """u8 affine, groups of 64, f16 scale and bias, constant groups exact (llvq-llm/src/kvq.rs:110-165)."""
     import torch
