@@ -1,6 +1,6 @@
 // Probe kernels and the class-agnostic fused GEMV built on decode_generic.
 // One thread decodes one block; nothing here is tuned. These kernels define the
-// semantics; the class-sorted kernels in gemv_sorted.cuh must agree with them.
+// semantics; the fused kernels (gemv_pipe.cuh, gemm_tab.cuh) must agree with them.
 #pragma once
 #include <cuda_fp16.h>
 

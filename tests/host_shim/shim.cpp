@@ -47,16 +47,6 @@ void shim_decode_indices(const uint64_t* idx, int64_t n, int8_t* points, uint8_t
     }
 }
 
-// The 32-bit generic decoder of the cap-12 ball.
-void shim_decode_generic12(const uint64_t* idx, int64_t n, int8_t* points, uint8_t* shell) {
-    const DevTables& T = tables().T;
-    for (int64_t b = 0; b < n; ++b) {
-        int8_t* out = points + b * kDim;
-        float scale;
-        shell[b] = (uint8_t)decode_generic12(T, idx[b], [&](int pos, int val) { out[pos] = (int8_t)val; }, &scale);
-    }
-}
-
 uint64_t shim_fingerprint(void) {
     HostTables& t = tables();
     std::vector<uint64_t> probes;

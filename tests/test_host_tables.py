@@ -111,19 +111,6 @@ def test_host_compiled_device_decoder_matches_oracle(shim, oracle):
     assert shell[0] == 13 and shell[1] == 255
 
 
-def test_host_compiled_32bit_generic_decoder_matches_oracle(shim, oracle):
-    """decode_generic12: every class of the cap-12 ball, both ends and 100 draws inside each."""
-    idx = probe_indices(oracle, per_class_random=100, cap=12)
-    pts = np.zeros((idx.size, 24), np.int8)
-    shell = np.zeros(idx.size, np.uint8)
-    shim.shim_decode_generic12(idx.ctypes.data_as(C.c_void_p), C.c_int64(idx.size), pts.ctypes.data_as(C.c_void_p),
-                               shell.ctypes.data_as(C.c_void_p))
-    ref_pts, ref_shell = _shim_decode(shim, idx, 12)
-    assert np.array_equal(pts, ref_pts) and np.array_equal(shell, ref_shell)
-    for k in range(0, idx.size, 53):
-        assert np.array_equal(pts[k], oracle.decode_index(int(idx[k])))
-
-
 def test_synthetic_generator_is_the_scalar_splitmix64():
     from llvq_b200 import synth
 
