@@ -12,11 +12,15 @@ every step streams far more than the 126 MB L2 and no matrix is re-read warm.
 
 Reported: `value` = algorithmic GB/s (codes + f32 tails + f64 row scales + x + y
 bytes over the device time of the pass, inputs resident in HBM); `e2e` = the same
-metric through the host-buffer C ABI call (x copied in from pinned host memory and
-y copied back inside the timed region, per GEMV); `roofline` for the GEMV kernel;
+metric through the host-buffer C ABI call (every x copied in from pinned host memory
+and every y copied back inside the timed region); `roofline` for the GEMV kernel;
 `cpu_baseline` = the CPU oracle (the C++ restatement of the reference's Rust path)
-timed on this box's host cores on a bounded sample. `--impl reference` times that
-CPU path alone, as the reference arm.
+timed on this box's host cores on a bounded sample; `gemm` = configuration 3 (batched
+GEMM), `decode` = configuration 2 (greedy decode, with the token step split by phase),
+`tp` = configuration 4 on the ranks of the run (row-sharded GEMV pass and tensor-parallel
+decode; tp1 figures at N = 1). `--impl reference` times the CPU path alone, as the
+reference arm, and adds as a side measurement the reference's own serving kernel on its
+transcoded layout where that kernel was built from the reference's sources.
 """
 from __future__ import annotations
 
