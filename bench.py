@@ -870,11 +870,18 @@ def main():
 
     verified = verify_before_timing(rt, torch, synth, rank) if rank == 0 else None
 
-    for _ in range(max(args.warmup, 3)):
-        step_device()
+    # clocks and throttle reasons are sampled (100 ms apart) from before the warm-up to the end of the timed passes:
+    # the warm-up runs the same passes, at least W of them and for at least 0.6 s, so that the samples see the load
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    t_warm, n_warm = time.perf_counter(), 0
+    while n_warm < max(args.warmup, 3) or time.perf_counter() - t_warm < 0.6:
+        step_device()
+        n_warm += 1
+        if n_warm % 8 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
     launches0 = lib.llvq_launch_count()
     ms_total = timed(step_device, args.steps)
     launches = lib.llvq_launch_count() - launches0
