@@ -13,8 +13,8 @@
 //   decode    warps draw batches of 32 same-family blocks (lists written one chunk
 //             ahead), run that family's decoder, scale the 24 signed bytes by
 //             gain centroid / sqrt(16 m) and write them as f16 into the A tile in shared
-//             memory (K-major, 64-byte swizzle, three 32-column panels); the X chunk,
-//             loaded one chunk ahead, becomes the B tile in the same layout;
+//             memory (K-major, 64-byte swizzle, three 32-column panels); the X chunk goes
+//             into the B tile in the same layout by cp.async, under the decoding;
 //   classify  the warps that are done classify the NEXT chunk (48-bit record -> class ->
 //             family list) instead of waiting at the barrier: items, lists and counters
 //             are double (triple) buffered, the groups of 32 blocks are handed out by tickets;
@@ -281,29 +281,34 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
         return true;
     };
 
-    // Piece i (of n_pad * 12 16-byte pieces) of a chunk's B tile: rows beyond the batch and columns beyond the
-    // last block read zero so that no stray NaN meets a zero weight.
-    auto load_x = [&](const GemmTabIt& it, int i) -> uint4 {
-        const int n = i / 12, gc = i - n * 12;
-        const int col = it.c * kGKB * kDim + gc * 8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (i < ga.n_pad * 12 && n < ga.batch && col + 8 <= nb * kDim) {
-            const __half* src = ga.x + (size_t)n * mv.d_in + col;
+    // The X chunk of a chunk becomes the B tile: piece i (of n_pad * 12 16-byte pieces) goes from global memory
+    // straight to its swizzled place with cp.async, so the copy runs under the decode phase and takes no register;
+    // rows beyond the batch and columns beyond the last block are zero-filled (src-size 0) so that no stray NaN
+    // meets a zero weight. Activations whose rows do not allow 16-byte loads take the slow path through registers.
+    auto stage_x = [&](const GemmTabIt& it) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int i = gt + k * kTGHalfThreads;
+            if (i >= ga.n_pad * 12) break;
+            const int n = i / 12, gc = i - n * 12;
+            const int col = it.c * kGKB * kDim + gc * 8;
+            const bool live = n < ga.batch && col + 8 <= nb * kDim;
+            const __half* src = ga.x + (live ? (size_t)n * mv.d_in + col : 0);
+            const unsigned int dst = b_tile + swz_offset(n, gc, kGPanelB);
             if (ga.x_vec_ok) {
-                v = *reinterpret_cast<const uint4*>(src);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(live ? 16 : 0) : "memory");
             } else {
-                const unsigned short* e = reinterpret_cast<const unsigned short*>(src);
-                v.x = e[0] | (unsigned int)e[1] << 16;
-                v.y = e[2] | (unsigned int)e[3] << 16;
-                v.z = e[4] | (unsigned int)e[5] << 16;
-                v.w = e[6] | (unsigned int)e[7] << 16;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (live) {
+                    const unsigned short* e = reinterpret_cast<const unsigned short*>(src);
+                    v.x = e[0] | (unsigned int)e[1] << 16;
+                    v.y = e[2] | (unsigned int)e[3] << 16;
+                    v.z = e[4] | (unsigned int)e[5] << 16;
+                    v.w = e[6] | (unsigned int)e[7] << 16;
+                }
+                sts128(dst, v);
             }
         }
-        return v;
-    };
-    auto store_x = [&](int i, uint4 v) {
-        const int n = i / 12, gc = i - n * 12;
-        if (i < ga.n_pad * 12) sts128(b_tile + swz_offset(n, gc, kGPanelB), v);
     };
 
     // Accumulators of a finished unit -> split-K partials ws[split][n][row] (warps 0-3 of the half: a warp may
@@ -329,7 +334,6 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
     };
 
     bool prev_last = false;  // the previous chunk closed its unit: read the accumulators back before the next MMA
-    uint4 xr = make_uint4(0, 0, 0, 0);  // this thread's first piece of the next B tile, loaded one chunk ahead
     {
         bool landed = true;
         if (ok && C.it[0].valid) issue_slab(C.it[0]);
@@ -338,7 +342,6 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
         // ordinary launch). Tables and codes, all that was touched so far, are constant.
         asm volatile("griddepcontrol.wait;" ::: "memory");
         if (ok && C.it[0].valid) {
-            xr = load_x(C.it[0], gt);
             landed = classify(C.it[0], 0);
         }
         // the decode tables must have landed before the first decode; the first chunk's lists are complete
@@ -369,14 +372,13 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
         const unsigned int lists = sbase + P.lists + (unsigned int)(2 * half + (q & 1)) * (4u * kGItems);
         // the slab is free (chunk q was classified before the last barrier): fetch the next chunk's codes
         if (C.it[(q + 1) % 3].valid) issue_slab(C.it[(q + 1) % 3]);
-        // zero the block nobody decodes; the X chunk, loaded an iteration ago, becomes the B tile
+        // zero the block nobody decodes; start the X chunk on its way into the B tile
         if ((C.zero[q & 1][warp] >> lane) & 1u) {
 #pragma unroll
             for (int j = 0; j < 3; ++j)
                 sts128(a_tile + swz_offset(gt >> 2, 3 * (gt & 3) + j, kGPanelA), make_uint4(0, 0, 0, 0));
         }
-        store_x(gt, xr);
-        if (gt + kTGHalfThreads < ga.n_pad * 12) store_x(gt + kTGHalfThreads, load_x(cur, gt + kTGHalfThreads));  // batches beyond 42 rows
+        stage_x(cur);  // lands while the chunk is decoded
         // the finished unit's accumulators are overwritten by this chunk's first MMA (after the next barrier)
         if (prev_last) store_unit();
 
@@ -449,11 +451,12 @@ llvq_gemm_tab_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* _
         const GemmTabIt& nxt = C.it[(q + 1) % 3];
         bool landed = true;
         if (nxt.valid) {
-            xr = load_x(nxt, gt);  // in flight during the classification
             landed = classify(nxt, q + 1);
         }
 
-        // generic-proxy writes must be visible to the tensor core's asynchronous reads
+        // this thread's pieces of the B tile have landed; generic-proxy writes must be visible to the tensor core's
+        // asynchronous reads
+        asm volatile("cp.async.wait_all;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         ok = pipe_group_sync_and(half, landed);
         if (!ok) break;
