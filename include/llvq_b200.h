@@ -155,6 +155,18 @@ int llvq_gemv_f32(llvq_matrix* m, const float* x_dev, float* y_dev, llvq_stream_
  * y_dev are IEEE binary16 passed as uint16_t. */
 int llvq_gemv_h(llvq_matrix* m, const uint16_t* x_dev, uint16_t* y_dev, llvq_stream_t stream);
 
+/* llvq_gemv_h with the activation produced inside the kernel, for the two places of a decode step where
+ * a projection follows an elementwise step (Block::forward_cached, llvq-llm/src/model.rs:778-834):
+ *   llvq_gemv_norm_h  y = W (RMSNorm(resid + delta) * norm_w); resid_out = resid + delta (delta may be
+ *                     NULL; resid_out must not alias resid). Bit-identical to llvq_op_add_rmsnorm_h
+ *                     followed by llvq_gemv_h. All vectors 16-byte aligned, d_in even, up to 16384.
+ *   llvq_gemv_silu_h  y = W (silu(gate) * up), gate_up = [gate | up], d_in values each, d_in a
+ *                     multiple of 8. Bit-identical to llvq_op_silu_mul_h followed by llvq_gemv_h.
+ * LLVQ_ERR_UNSUPPORTED for a matrix the pipelined kernel does not serve (no whole block of 24 columns). */
+int llvq_gemv_norm_h(llvq_matrix* m, const uint16_t* resid_dev, const uint16_t* delta_dev, const uint16_t* norm_w_dev, float eps,
+                     uint16_t* resid_out_dev, uint16_t* y_dev, llvq_stream_t stream);
+int llvq_gemv_silu_h(llvq_matrix* m, const uint16_t* gate_up_dev, uint16_t* y_dev, llvq_stream_t stream);
+
 /* f32 (rotated) activation, f16 result: the exact signature of tv_planes_h,
  * llvq-llm/kernels/tv_planes_h.cu:38-72, which FusedRuntime::forward_rotated
  * launches (llvq-llm/src/fused_cuda.rs:384-402). */

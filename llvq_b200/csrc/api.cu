@@ -193,13 +193,13 @@ int launch_gemv_generic(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s) {
 }
 
 // The persistent pipelined kernel: one CTA per SM, rows split evenly over the CTAs.
-template <typename XT, typename YT>
+template <typename XT, typename YT, int XOP = kXPlain>
 int launch_pipe(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s, PipePlan plan, int probe = 0,
-                unsigned long long* trace = nullptr) {
+                unsigned long long* trace = nullptr, PipeXOp xop = PipeXOp{}) {
     plan.probe = probe;
     plan.trace = trace;
     llvq_runtime* rt = m->rt;
-    auto kern = llvq_gemv_pipe_kernel<XT, YT>;
+    auto kern = llvq_gemv_pipe_kernel<XT, YT, XOP>;
     int st = ensure_dyn_smem((const void*)kern, plan.total);
     if (st) return st;
     const int grid = (m->d_out + plan.rows_per_cta - 1) / plan.rows_per_cta;
@@ -218,7 +218,7 @@ int launch_pipe(llvq_matrix* m, const XT* x, YT* y, cudaStream_t s, PipePlan pla
     cfg.attrs = attr;
     cfg.numAttrs = rt->overlap_launches ? 1 : 0;
     CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, (const unsigned char*)rt->d_tab_blob, (const OffEntry*)rt->d_tab_off,
-                                (const unsigned long long*)rt->d_tab_on3, rt->TL, m->view(), x, y, plan, rt->d_err));
+                                (const unsigned long long*)rt->d_tab_on3, rt->TL, m->view(), x, y, plan, xop, rt->d_err));
     g_launches++;
     return LLVQ_OK;
 }
@@ -242,6 +242,16 @@ int gemv_entry(llvq_matrix* m, const XT* x, YT* y, llvq_stream_t stream) {
     if (((uintptr_t)x % sizeof(XT)) || ((uintptr_t)y % sizeof(YT))) return fail(LLVQ_ERR_INVALID, "gemv: misaligned buffer");
     DeviceGuard g(m->rt->device);
     return launch_gemv<XT, YT>(m, x, y, (cudaStream_t)stream);
+}
+
+// The projection with its activation produced in the kernel's staging step (f16, pipelined kernel only).
+template <int XOP>
+int gemv_xop_entry(llvq_matrix* m, const __half* x, __half* y, const PipeXOp& xop, cudaStream_t s, const char* what) {
+    llvq_runtime* rt = m->rt;
+    DeviceGuard g(rt->device);
+    const PipePlan plan = pipe_plan<__half>(rt->TL, rt->max_smem_optin, m->d_out, m->nb, rt->sm_count);
+    if (m->nb == 0 || plan.tile_max == 0) return fail(LLVQ_ERR_UNSUPPORTED, "%s: matrix not served by the pipelined kernel", what);
+    return launch_pipe<__half, __half, XOP>(m, x, y, s, plan, 0, nullptr, xop);
 }
 
 int check_desc(const llvq_matrix_desc& d) {
@@ -497,9 +507,11 @@ int llvq_runtime_create(int device, llvq_runtime** out) {
     // refuses it when it loads its kernels (llvq-cuda/src/gpu.rs:413-436, llvq-llm/src/fused_cuda.rs:229-239).
     {
         const struct { const char* name; const void* fn; } hot[] = {
-            {"llvq_gemv_pipe_kernel<f16,f16>", (const void*)llvq_gemv_pipe_kernel<__half, __half>},
-            {"llvq_gemv_pipe_kernel<f32,f16>", (const void*)llvq_gemv_pipe_kernel<float, __half>},
-            {"llvq_gemv_pipe_kernel<f32,f32>", (const void*)llvq_gemv_pipe_kernel<float, float>},
+            {"llvq_gemv_pipe_kernel<f16,f16>", (const void*)llvq_gemv_pipe_kernel<__half, __half, kXPlain>},
+            {"llvq_gemv_pipe_kernel<f16,f16,norm>", (const void*)llvq_gemv_pipe_kernel<__half, __half, kXNorm>},
+            {"llvq_gemv_pipe_kernel<f16,f16,silu>", (const void*)llvq_gemv_pipe_kernel<__half, __half, kXSilu>},
+            {"llvq_gemv_pipe_kernel<f32,f16>", (const void*)llvq_gemv_pipe_kernel<float, __half, kXPlain>},
+            {"llvq_gemv_pipe_kernel<f32,f32>", (const void*)llvq_gemv_pipe_kernel<float, float, kXPlain>},
             {"llvq_decode_tab_kernel", (const void*)llvq_decode_tab_kernel},
             {"llvq_gemm_tab_kernel", (const void*)llvq_gemm_tab_kernel},
         };
@@ -644,6 +656,33 @@ int llvq_gemv_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, llvq_stream_t s)
 }
 int llvq_gemv_f32x_h(llvq_matrix* m, const float* x, uint16_t* y, llvq_stream_t s) {
     return gemv_entry<float, __half>(m, x, (__half*)y, s);
+}
+
+int llvq_gemv_norm_h(llvq_matrix* m, const uint16_t* resid, const uint16_t* delta, const uint16_t* norm_w, float eps,
+                     uint16_t* resid_out, uint16_t* y, llvq_stream_t s) {
+    if (!m || !resid || !norm_w || !resid_out || !y) return fail(LLVQ_ERR_INVALID, "gemv_norm: null argument");
+    if (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)norm_w | (uintptr_t)resid_out) & 15u)
+        return fail(LLVQ_ERR_INVALID, "gemv_norm: the vectors must be 16-byte aligned");
+    if ((uintptr_t)y & 1u) return fail(LLVQ_ERR_INVALID, "gemv_norm: misaligned result");
+    if (resid_out == resid) return fail(LLVQ_ERR_INVALID, "gemv_norm: the updated stream must not alias the stream read");
+    if ((m->d_in & 1) || m->d_in > 16384) return fail(LLVQ_ERR_UNSUPPORTED, "gemv_norm: width %d (even, up to 16384)", m->d_in);
+    PipeXOp xop{};
+    xop.delta = (const __half*)delta;
+    xop.w = (const __half*)norm_w;
+    xop.x_out = (__half*)resid_out;
+    xop.eps = eps;
+    xop.n = m->d_in;
+    return gemv_xop_entry<kXNorm>(m, (const __half*)resid, (__half*)y, xop, (cudaStream_t)s, "gemv_norm");
+}
+
+int llvq_gemv_silu_h(llvq_matrix* m, const uint16_t* gate_up, uint16_t* y, llvq_stream_t s) {
+    if (!m || !gate_up || !y) return fail(LLVQ_ERR_INVALID, "gemv_silu: null argument");
+    if (((uintptr_t)gate_up & 15u) || (m->d_in & 7))
+        return fail(LLVQ_ERR_INVALID, "gemv_silu: gate and up must both start on 16 bytes (width a multiple of 8)");
+    if ((uintptr_t)y & 1u) return fail(LLVQ_ERR_INVALID, "gemv_silu: misaligned result");
+    PipeXOp xop{};
+    xop.n = m->d_in;
+    return gemv_xop_entry<kXSilu>(m, (const __half*)gate_up, (__half*)y, xop, (cudaStream_t)s, "gemv_silu");
 }
 
 int llvq_gemv_probe_h(llvq_matrix* m, const uint16_t* x, uint16_t* y, int32_t mode, llvq_stream_t s) {

@@ -141,6 +141,7 @@ struct alignas(16) PipeShared {
     unsigned long long mbar[2];       // decoder tables: classification part, decode part
     int error;
     float xs_tail[32];
+    float red[32];                    // per-warp sums of squares (activation produced in the kernel)
 };
 struct alignas(16) PipeCtrl {         // one per group
     unsigned long long slab_bar;      // code slab
@@ -225,23 +226,92 @@ __device__ __forceinline__ void sts128(unsigned int addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// Where the f16 activation comes from. kXPlain: x itself. kXNorm: x is the residual stream and the activation is
+// RMSNorm(x + delta) * w, computed by every CTA for itself with add_rmsnorm_kernel's arithmetic and order of
+// operations (same bits); CTA 0 also writes x + delta to x_out, which must not alias x (the other CTAs
+// still read x). kXSilu: x holds gate (n values) then up (n values) and the activation is silu(gate) * up,
+// rounded to f16 as silu_mul_kernel stores it.
+enum { kXPlain = 0, kXNorm = 1, kXSilu = 2 };
+struct PipeXOp {
+    const __half* delta;  // kXNorm: added to x first; may be null
+    const __half* w;      // kXNorm: norm weights
+    __half* x_out;        // kXNorm: the updated residual stream
+    float eps;            // kXNorm
+    int n;                // length of the activation
+};
+
+__device__ __forceinline__ float pipe_round_h(float v) { return __half2float(__float2half_rn(v)); }
+
+// Element e of the activation (r: 1 / rms of the updated residual stream, kXNorm only).
+template <int XOP>
+__device__ __forceinline__ float pipe_x_elem(const __half* __restrict__ x, int e, const PipeXOp& xop, float r) {
+    float v = __half2float(x[e]);
+    if constexpr (XOP == kXNorm) {
+        if (xop.delta) v = pipe_round_h(v + __half2float(xop.delta[e]));
+        v = pipe_round_h(v * r * __half2float(xop.w[e]));
+    } else if constexpr (XOP == kXSilu) {
+        const float u = __half2float(x[xop.n + e]);
+        v = pipe_round_h(v / (1.0f + __expf(-v)) * u);
+    }
+    return v;
+}
+
+__device__ __forceinline__ void pipe_load24_h(const __half* __restrict__ p, float (&v)[kDim]) {
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p + 8 * q);
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f2 = __half22float2(h[k]);
+            v[8 * q + 2 * k] = f2.x;
+            v[8 * q + 2 * k + 1] = f2.y;
+        }
+    }
+}
+
 // Digits of one 24-column block of the activation, written to `dst` (shared-window address):
 // kDigits planes of 24 bytes (most significant first: signed, then unsigned), then the float
 // that turns the integer dot product back into the activation's units.
-template <typename XT>
-__device__ __forceinline__ void pipe_prep_column(const XT* __restrict__ xcol, unsigned int dst, unsigned int dst_scale) {
+template <typename XT, int XOP>
+__device__ __forceinline__ void pipe_prep_column(const XT* __restrict__ x, size_t e0, const PipeXOp& xop, float r, unsigned int dst,
+                                                 unsigned int dst_scale) {
+    const XT* xcol = x + e0;
     float v[kDim];
-    if constexpr (sizeof(XT) == 2) {
+    __half2 vh[XOP == kXSilu ? kDim / 2 : 1];  // kXSilu keeps its values packed (they are f16 anyway): fewer live registers
+    auto val = [&](int j) -> float {
+        if constexpr (XOP == kXSilu)
+            return (j & 1) ? __high2float(vh[j >> 1]) : __low2float(vh[j >> 1]);
+        else
+            return v[j];
+    };
+    if constexpr (sizeof(XT) == 2 && XOP == kXSilu) {
+        // eight values at a time: gate and up of a piece are consumed before the next piece is loaded
+        const __half* g = reinterpret_cast<const __half*>(xcol);
 #pragma unroll
         for (int q = 0; q < 3; ++q) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(xcol + 8 * q);
-            const __half2* h = reinterpret_cast<const __half2*>(&raw);
+            const uint4 graw = *reinterpret_cast<const uint4*>(g + 8 * q);
+            const uint4 uraw = *reinterpret_cast<const uint4*>(g + xop.n + 8 * q);
+            const __half2* gh = reinterpret_cast<const __half2*>(&graw);
+            const __half2* uh = reinterpret_cast<const __half2*>(&uraw);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const float2 f2 = __half22float2(h[k]);
-                v[8 * q + 2 * k] = f2.x;
-                v[8 * q + 2 * k + 1] = f2.y;
+                const float2 gf = __half22float2(gh[k]), uf = __half22float2(uh[k]);
+                vh[4 * q + k] = __floats2half2_rn(gf.x / (1.0f + __expf(-gf.x)) * uf.x, gf.y / (1.0f + __expf(-gf.y)) * uf.y);
             }
+        }
+    } else if constexpr (sizeof(XT) == 2) {
+        pipe_load24_h(reinterpret_cast<const __half*>(xcol), v);
+        if constexpr (XOP == kXNorm) {
+            float t[kDim];
+            if (xop.delta) {
+                pipe_load24_h(xop.delta + e0, t);
+#pragma unroll
+                for (int j = 0; j < kDim; ++j) v[j] = pipe_round_h(v[j] + t[j]);
+            }
+            pipe_load24_h(xop.w + e0, t);
+#pragma unroll
+            for (int j = 0; j < kDim; ++j) v[j] = pipe_round_h(v[j] * r * t[j]);
         }
     } else {
 #pragma unroll
@@ -255,7 +325,7 @@ __device__ __forceinline__ void pipe_prep_column(const XT* __restrict__ xcol, un
     }
     float amax = 0.0f;
 #pragma unroll
-    for (int j = 0; j < kDim; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    for (int j = 0; j < kDim; ++j) amax = fmaxf(amax, fabsf(val(j)));
     constexpr int kDigits = XDigits<XT>::kDigits;
     constexpr float kFull = kDigits == 2 ? 32767.0f : 8388607.0f;
     // a zero block scales by 0; an infinite or NaN activation makes the block's factor NaN or inf,
@@ -271,7 +341,7 @@ __device__ __forceinline__ void pipe_prep_column(const XT* __restrict__ xcol, un
     for (int j = 0; j < kDim; ++j) {
         // the product of the largest magnitude with s may round one past kFull: clamp, or the top
         // digit would change sign
-        const int q = max(-(int)kFull, min((int)kFull, __float2int_rn(v[j] * s)));
+        const int q = max(-(int)kFull, min((int)kFull, __float2int_rn(val(j) * s)));
 #pragma unroll
         for (int d = 0; d < kDigits; ++d) {
             const unsigned int byte = ((unsigned int)q >> (8 * (kDigits - 1 - d))) & 0xffu;  // top digit keeps the sign
@@ -397,10 +467,11 @@ __device__ __forceinline__ int2 pipe_list_geom(unsigned int lists, int tile_max,
 
 // Staging of a tile's per-column and per-row data: activation digits of column c of the tile, and for row c
 // of the tile its centroids and, for the last column chunk of a row, its row scale and tail-column product.
-template <typename XT>
-__device__ __forceinline__ void pipe_stage_col(const XT* __restrict__ x, const PipeTile& t, unsigned int xbuf, unsigned int xscl, int c) {
+template <typename XT, int XOP>
+__device__ __forceinline__ void pipe_stage_col(const XT* __restrict__ x, const PipeXOp& xop, float r, const PipeTile& t, unsigned int xbuf,
+                                               unsigned int xscl, int c) {
     constexpr int kColBytes = XDigits<XT>::kColBytes;
-    if (c < t.cols) pipe_prep_column<XT>(x + (size_t)(t.col0 + c) * kDim, xbuf + c * kColBytes, xscl + 4u * c);
+    if (c < t.cols) pipe_prep_column<XT, XOP>(x, (size_t)(t.col0 + c) * kDim, xop, r, xbuf + c * kColBytes, xscl + 4u * c);
 }
 __device__ __forceinline__ void pipe_stage_row(const MatrixView& mv, const PipeTile& t, PipeCtrl& C, const float* xs_tail, int slot, int c) {
     if (c < t.rows) {
@@ -425,12 +496,13 @@ __device__ __forceinline__ void pipe_stage_row(const MatrixView& mv, const PipeT
     }
 }
 
-template <typename XT, typename YT>
+template <typename XT, typename YT, int XOP>
 __global__ void __launch_bounds__(kPipeThreads, 1)
 llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* __restrict__ lut_off,
                       const unsigned long long* __restrict__ lut_on3, TabLayout L, MatrixView mv,
-                      const XT* __restrict__ x, YT* __restrict__ y, PipePlan plan,
+                      const XT* __restrict__ x, YT* __restrict__ y, PipePlan plan, PipeXOp xop,
                       int* __restrict__ err_flag) {
+    static_assert(XOP == kXPlain || sizeof(XT) == 2, "an activation produced in the kernel is f16");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const unsigned int sbase = pipe_smem_addr(smem_raw);
     constexpr int kColBytes = XDigits<XT>::kColBytes;
@@ -527,27 +599,61 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
     // the activation may be the previous kernel's output, and y may be its input: from here on the previous
     // launch of the stream has completed and its writes are visible (no-op for an ordinary launch)
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    float xr = 0.0f;  // kXNorm: 1 / rms of the updated residual stream
+    if constexpr (XOP == kXNorm) {
+        // add_rmsnorm_kernel's first pass with its partition (thread t: pairs t, t + 1024, ...), its order of
+        // additions and its warp and CTA reductions, so that every CTA arrives at the bits that kernel produces
+        const __half2* x2 = reinterpret_cast<const __half2*>(x);
+        const __half2* d2 = reinterpret_cast<const __half2*>(xop.delta);
+        const int pairs = xop.n >> 1;
+        float ss = 0.0f;
+        for (int i = tid; i < pairs; i += kPipeThreads) {
+            __half2 h = x2[i];
+            if (d2) {
+                const float2 a = __half22float2(h), d = __half22float2(d2[i]);
+                h = __floats2half2_rn(a.x + d.x, a.y + d.y);
+            }
+            if (blockIdx.x == 0) reinterpret_cast<__half2*>(xop.x_out)[i] = h;
+            const float2 v = __half22float2(h);
+            ss += v.x * v.x + v.y * v.y;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if ((tid & 31) == 0) S.red[tid >> 5] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) tot += S.red[k];
+        xr = rsqrtf(tot / (float)xop.n + xop.eps);
+    }
     // the tail activations: every staging warp writes the same values and reads them back after its own
     // warp barrier (no CTA barrier stands between here and the staging below)
     if (warp >= kGroupWarps - kStageWarps) {
-        S.xs_tail[lane] = lane < mv.tail_w ? to_f32<XT>(x[mv.nb * kDim + lane]) : 0.0f;
+        float tv = 0.0f;
+        if (lane < mv.tail_w) {
+            if constexpr (XOP == kXPlain)
+                tv = to_f32<XT>(x[mv.nb * kDim + lane]);
+            else
+                tv = pipe_x_elem<XOP>(reinterpret_cast<const __half*>(x), mv.nb * kDim + lane, xop, xr);
+        }
+        S.xs_tail[lane] = tv;
         __syncwarp();
     }
     // the first tile's digits and row data are staged while the tables travel
+    if (ncc == 1) {
+        // one column chunk: the digits of the whole row, once, by every thread of the CTA (nothing else has
+        // work before the tables land)
+        PipeTile all;
+        all.col0 = 0;
+        all.cols = mv.nb;
+        for (int c = tid; c < mv.nb; c += kPipeThreads) pipe_stage_col<XT, XOP>(x, xop, xr, all, xbuf, xscl, c);
+    }
     if (warp >= kGroupWarps - kStageWarps) {
         const int sw = kGroupWarps - 1 - warp;  // 0 .. kStageWarps - 1
-        if (ncc == 1) {
-            // one column chunk: the digits of the whole row, once, by the staging warps of all groups together
-            PipeTile all;
-            all.col0 = 0;
-            all.cols = mv.nb;
-            for (int c = 32 * (grp * kStageWarps + sw) + lane; c < mv.nb; c += 32 * kStageWarps * kPipeGroups)
-                pipe_stage_col<XT>(x, all, xbuf, xscl, c);
-        }
         if (nt > 0) {
             const PipeTile t0 = C.tile[0];
             for (int c = 32 * sw + lane; c < max(t0.cols, t0.rows); c += 32 * kStageWarps) {
-                if (ncc > 1) pipe_stage_col<XT>(x, t0, xbuf, xscl, c);
+                if (ncc > 1) pipe_stage_col<XT, XOP>(x, xop, xr, t0, xbuf, xscl, c);
                 pipe_stage_row(mv, t0, C, S.xs_tail, 0, c);
             }
         }
@@ -673,7 +779,7 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
             const PipeTile tn = C.tile[(i + 1) & 1];
             const unsigned int xo = ncc > 1 ? (unsigned int)((i + 1) & 1) * xbuf_bytes : 0u;
             for (int c = 32 * (kGroupWarps - 1 - warp) + lane; c < max(tn.cols, tn.rows); c += 32 * kStageWarps) {
-                if (ncc > 1) pipe_stage_col<XT>(x, tn, xbuf + xo, xscl + xo, c);
+                if (ncc > 1) pipe_stage_col<XT, XOP>(x, xop, xr, tn, xbuf + xo, xscl + xo, c);
                 pipe_stage_row(mv, tn, C, S.xs_tail, (i + 1) & 1, c);
             }
         }

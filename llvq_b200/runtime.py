@@ -188,6 +188,29 @@ class FusedRuntime:
         check(fn(proj._h, x.data_ptr(), y.data_ptr(), self._stream()))
         return y
 
+    def forward_norm(self, proj: FusedProj, resid, delta, norm_w, eps: float, resid_out, out=None):
+        """y = W (RMSNorm(resid + delta) * norm_w) with the norm computed in the projection's kernel; resid + delta goes
+        to resid_out (not resid itself). f16 throughout; the bits of add_rmsnorm followed by forward. `delta` may be None."""
+        import torch
+        self._check_x(proj, resid, torch.float16)
+        for t in (delta, norm_w, resid_out):
+            if t is not None:
+                self._check_x(proj, t, torch.float16)
+        y = out if out is not None else torch.empty(proj.d_out, dtype=torch.float16, device=resid.device)
+        check(self.lib.llvq_gemv_norm_h(proj._h, resid.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                        norm_w.data_ptr(), eps, resid_out.data_ptr(), y.data_ptr(), self._stream()))
+        return y
+
+    def forward_silu(self, proj: FusedProj, gate_up, out=None):
+        """y = W (silu(gate) * up) for gate_up = [gate | up] (f16, 2 d_in values), the product formed in the projection's
+        kernel; the bits of silu_mul followed by forward."""
+        import torch
+        if gate_up.dtype != torch.float16 or gate_up.numel() != 2 * proj.d_in or not gate_up.is_contiguous() or not gate_up.is_cuda:
+            raise ValueError("forward_silu: gate_up must be a contiguous f16 CUDA tensor of 2 d_in values")
+        y = out if out is not None else torch.empty(proj.d_out, dtype=torch.float16, device=gate_up.device)
+        check(self.lib.llvq_gemv_silu_h(proj._h, gate_up.data_ptr(), y.data_ptr(), self._stream()))
+        return y
+
     def forward_batch(self, proj: FusedProj, x, out=None):
         """f16 [B, d_in] -> f16 [B, d_out]; every code is decoded once per batch."""
         import torch

@@ -147,6 +147,33 @@ def test_dependent_launches_do_not_change_a_token(rt):
     assert not rt.poll_range_error()
 
 
+def test_norm_and_swiglu_inside_the_projection_do_not_change_a_token(rt):
+    """Without rotations the token step lets the q/k/v and gate/up projections compute their RMSNorm (and the
+    residual add) and the down projection its SwiGLU product in the kernel's staging step. The tokens and the
+    final hidden state are those of the step with separate norm and SwiGLU kernels, eagerly and from a graph; the
+    width 2560 has 16 tail columns, the small model's inter of 496 is a multiple of 8."""
+    import torch
+    from llvq_b200.model import Qwen3Config, synthetic_model
+    for cfg, layers in ((Qwen3Config(hidden=24 * 10 + 16, inter=24 * 20 + 16, n_heads=4, n_kv=2, head_dim=64, layers=3, vocab=512), 3),
+                        (Qwen3Config.named("qwen3-4b"), 2)):
+        prompt = [int(t) for t in np.random.default_rng(5).integers(0, cfg.vocab, 12)]
+        runs = {}
+        for fuse in (False, True):
+            for use_graph in (False, True):
+                big = cfg.hidden > 1000  # drawn on the GPU, with the benchmark's row scales
+                model, _ = synthetic_model(rt, cfg, config_id=2, capacity=64, layers=layers, row_scale_gain=1.0 if big else 40.0,
+                                           device_codes=big, keep_host=False)
+                model.fuse_x = fuse
+                toks = model.generate(prompt, 20, use_graph=use_graph)
+                torch.cuda.synchronize()
+                runs[(fuse, use_graph)] = (toks, model._x.clone())
+        want_t, want_x = runs[(False, False)]
+        for key, (toks, x) in runs.items():
+            assert toks == want_t, key
+            assert torch.equal(x, want_x), key
+    assert not rt.poll_range_error()
+
+
 def test_int8_kv_cache_matches_the_reference_scheme():
     """u8 affine, groups of 64, f16 scale and bias, constant groups exact (llvq-llm/src/kvq.rs:110-165)."""
     import torch

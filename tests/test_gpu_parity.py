@@ -496,6 +496,52 @@ def test_gemv_column_chunks_and_odd_shapes(rt, oracle, d_out, d_in):
     assert not rt.poll_range_error()
 
 
+@pytest.mark.parametrize("d_out,d_in", [(640, 2560), (300, 9728), (96, 17408), (64, 48), (2000, 24 * 40 + 10)])
+def test_gemv_with_the_norm_or_the_swiglu_product_in_the_kernel(rt, d_out, d_in):
+    """llvq_gemv_norm_h and llvq_gemv_silu_h form the projection's activation in its staging step. Both give
+    the bits of the two-kernel sequence (llvq_op_add_rmsnorm_h or llvq_op_silu_mul_h, then llvq_gemv_h) and
+    the norm variant leaves x + delta in the other stream buffer, with and without a delta, for rows with a tail,
+    without one, and long enough to be cut into column chunks."""
+    import ctypes as C
+    torch = _torch()
+    from llvq_b200 import synth
+    from llvq_b200._lib import check
+    L = rt.lib
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: C.c_void_p(t.data_ptr())
+    m = synth.make_matrix(d_out, d_in, 0x5EED + d_in)
+    proj = rt.upload(m, tail_f16=True)
+    g = torch.Generator(device="cuda").manual_seed(d_in)
+    resid = (torch.randn(d_in, device="cuda", generator=g) * 1.7).half()
+    delta = (torch.randn(d_in, device="cuda", generator=g) * 0.4).half()
+    w = (1.0 + 0.05 * torch.randn(d_in, device="cuda", generator=g)).half()
+    eps = 1e-6
+    if d_in % 2 == 0 and d_in <= 16384:  # the norm kernels' limit
+        for d in (delta, None):
+            x = resid.clone()
+            h = torch.empty_like(x)
+            check(L.llvq_op_add_rmsnorm_h(p(x), p(d) if d is not None else None, p(w), p(h), d_in, eps, st))
+            want = rt.forward(proj, h).clone()
+            x_out = torch.full_like(resid, float("nan"))
+            got = rt.forward_norm(proj, resid, d, w, eps, x_out)
+            assert torch.equal(x_out, x)
+            assert torch.equal(got, want)
+            assert torch.equal(rt.forward_norm(proj, resid, d, w, eps, x_out), want)
+        with pytest.raises(RuntimeError):
+            rt.forward_norm(proj, resid, delta, w, eps, resid)  # in place: refused
+    if d_in % 8 == 0:
+        gu = (torch.randn(2 * d_in, device="cuda", generator=g) * 2.0).half()
+        act = torch.empty(d_in, dtype=torch.float16, device="cuda")
+        check(L.llvq_op_silu_mul_h(p(gu), p(act), d_in, st))
+        want = rt.forward(proj, act).clone()
+        assert torch.equal(rt.forward_silu(proj, gu), want)
+    else:
+        with pytest.raises(RuntimeError):
+            rt.forward_silu(proj, torch.zeros(2 * d_in, dtype=torch.float16, device="cuda"))
+    proj.free()
+    assert not rt.poll_range_error()
+
+
 def test_overlapped_launches_keep_stream_order(rt):
     """Back-to-back fused GEMVs are launched with programmatic stream serialisation: the next launch's prologue
     runs while the previous launch drains. A chain in which every launch reads the previous launch's output
