@@ -91,6 +91,8 @@ struct PipePlan {
     int tile_max;             // blocks per tile
     int cols_max, ncc;        // columns per chunk, column chunks (two digit buffers when ncc > 1)
     int rows_per_cta;
+    int tcn;                  // columns of a full chunk
+    unsigned int mdiv_full, mdiv_last;  // PipeTile::mdiv of a full chunk and of the last chunk
     int probe;                // attribution probes: bit 0 = leave the decoders out, bit 1 = leave the class search out
     unsigned long long* trace;  // per CTA kTraceEvents time stamps (ns), or null
 };
@@ -114,9 +116,6 @@ struct PipeGeom {
     unsigned int mdiv_full, mdiv_last;
     int rg, cc;       // the tile next() returns
     __device__ __forceinline__ int tiles() const { return nrg * ncc; }
-    __device__ __forceinline__ static unsigned int reciprocal(int cols) {
-        return cols > 1 ? (unsigned int)((0x100000000ull + cols - 1) / cols) : 0u;
-    }
     __device__ __forceinline__ PipeTile next() {
         PipeTile t;
         t.row0 = r0 + rg * rpt;
@@ -496,6 +495,24 @@ __device__ __forceinline__ void pipe_stage_row(const MatrixView& mv, const PipeT
     }
 }
 
+// Before the kernel may read the activation it can already pull the constant row data of its first tile towards
+// the SM: prefetches hold no register across the wait for the previous launch.
+__device__ __forceinline__ void pipe_prefetch_row(const MatrixView& mv, const PipeTile& t, int c) {
+    if (c < t.rows) {
+        const int r = t.row0 + c;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(mv.cent + r));
+        if (t.last_chunk) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(mv.rscale + r));
+            if (mv.tail_w > 0) {
+                const size_t row_bytes = (size_t)mv.tail_w * (mv.tail_f16 ? 2u : 4u);
+                const char* p = (const char*)mv.tail + (size_t)r * row_bytes;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p + row_bytes - 1));
+            }
+        }
+    }
+}
+
 template <typename XT, typename YT, int XOP>
 __global__ void __launch_bounds__(kPipeThreads, 1)
 llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* __restrict__ lut_off,
@@ -526,6 +543,20 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
         ++trace_n;
     };
     stamp();
+    // The decoder tables start travelling before anything else is computed: the thread that initialises their
+    // mbarriers also issues the copies (what classification reads first), the others meet them at the first
+    // CTA barrier. The tables are constant, so this needs no ordering against the previous launch of the stream.
+    if (tid == 0) {
+        S.error = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&S.mbar[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&S.mbar[1])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        pipe_expect_tx(pipe_smem_addr(&S.mbar[0]), L.classify_bytes);
+        pipe_bulk_copy(T.base, blob_g, L.classify_bytes, pipe_smem_addr(&S.mbar[0]));
+        pipe_expect_tx(pipe_smem_addr(&S.mbar[1]), L.total_bytes - L.classify_bytes);
+        pipe_bulk_copy(T.base + L.classify_bytes, blob_g + L.classify_bytes, L.total_bytes - L.classify_bytes,
+                       pipe_smem_addr(&S.mbar[1]));
+    }
 
     // ---- rows of this CTA, of this group, and their tiling ----
     const int cta_r0 = blockIdx.x * plan.rows_per_cta;
@@ -534,7 +565,7 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
     const int grp_r0 = cta_r0 + grp * rpg;
     const int grp_nr = max(0, min(rpg, cta_r0 + cta_nr - grp_r0));
     const int ncc = plan.ncc;
-    const int tcn = (mv.nb + ncc - 1) / ncc;
+    const int tcn = plan.tcn;
     const int fit = max(1, min(kTileRowsMax, tile_max / tcn));
     const int nrg = (grp_nr + fit - 1) / fit;
     const int nt = grp_nr > 0 ? nrg * ncc : 0;
@@ -550,51 +581,44 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
     const unsigned int bar_slab = pipe_smem_addr(&C.slab_bar);
     bool failed = false;
 
-    // ---- prologue: start the table and code copies, stage the tail activations ----
-    if (gt < 4) C.list_lut[gt] = pipe_list_geom(lists, tile_max, (unsigned int)gt);
-    if (tid == 0) {
-        S.error = 0;
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&S.mbar[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pipe_smem_addr(&S.mbar[1])));
-    }
-    if (gt == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_slab));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        PipeGeom geo;
-        geo.nb = mv.nb;
-        geo.r0 = grp_r0;
-        geo.nr = grp_nr;
-        geo.ncc = ncc;
-        geo.tcn = tcn;
-        geo.nrg = nrg;
-        geo.rpt = (grp_nr + nrg - 1) / max(nrg, 1);
-        geo.mdiv_full = PipeGeom::reciprocal(tcn);
-        geo.mdiv_last = PipeGeom::reciprocal(mv.nb - (ncc - 1) * tcn);
-        geo.rg = 0;
-        geo.cc = 0;
-        if (nt > 0) C.tile[0] = geo.next();
-        C.geo = geo;
-    }
-    __syncthreads();
+    // ---- prologue: the first tile's codes start travelling, then the activation is staged ----
     // Programmatic dependent launch: the next launch of the stream may take this SM as soon as this CTA
-    // leaves it, and this launch has come this far while the previous one was still running. Nothing above
-    // or in the copies below reads what a previous kernel writes (tables and codes are constant).
+    // leaves it, and this launch comes as far as griddepcontrol.wait below while the previous one is still running.
+    // Nothing before that wait reads what a previous kernel writes (tables and codes are constant).
     asm volatile("griddepcontrol.launch_dependents;");
-    if (tid < 32) {
+    if (warp == 0) {
+        // the group's first warp lays out the tiles and starts the first code slab on its own
+        if (lane < 4) C.list_lut[lane] = pipe_list_geom(lists, tile_max, (unsigned int)lane);
         if (lane == 0) {
-            // what classification reads comes first; the decode tables land while the first tiles are classified
-            pipe_expect_tx(pipe_smem_addr(&S.mbar[0]), L.classify_bytes);
-            pipe_bulk_copy(T.base, blob_g, L.classify_bytes, pipe_smem_addr(&S.mbar[0]));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_slab));
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            PipeGeom geo;
+            geo.nb = mv.nb;
+            geo.r0 = grp_r0;
+            geo.nr = grp_nr;
+            geo.ncc = ncc;
+            geo.tcn = tcn;
+            geo.nrg = nrg;
+            geo.rpt = (grp_nr + nrg - 1) / max(nrg, 1);
+            geo.mdiv_full = plan.mdiv_full;
+            geo.mdiv_last = plan.mdiv_last;
+            geo.rg = 0;
+            geo.cc = 0;
+            if (nt > 0) C.tile[0] = geo.next();
+            C.geo = geo;
+        }
+        __syncwarp();
+        if (nt > 0) {
+            const PipeTile t0 = C.tile[0];
+            pipe_issue_slab(mv.codes, t0, mv.nb, slab, bar_slab, lane);
         }
     }
-    if (warp == 0 && nt > 0) {
+    __syncthreads();  // the tile geometry (and S.error = 0) is visible to every warp
+    // the staging warps pull the first tile's row data (constant) towards the SM before the wait
+    const bool stager = warp >= kGroupWarps - kStageWarps;
+    if (stager && nt > 0) {
         const PipeTile t0 = C.tile[0];
-        pipe_issue_slab(mv.codes, t0, mv.nb, slab, bar_slab, lane);
-    }
-    if (tid == 0) {
-        pipe_expect_tx(pipe_smem_addr(&S.mbar[1]), L.total_bytes - L.classify_bytes);
-        pipe_bulk_copy(T.base + L.classify_bytes, blob_g + L.classify_bytes, L.total_bytes - L.classify_bytes,
-                       pipe_smem_addr(&S.mbar[1]));
+        for (int c = 32 * (kGroupWarps - 1 - warp) + lane; c < t0.rows; c += 32 * kStageWarps) pipe_prefetch_row(mv, t0, c);
     }
     // the activation may be the previous kernel's output, and y may be its input: from here on the previous
     // launch of the stream has completed and its writes are visible (no-op for an ordinary launch)
@@ -648,14 +672,11 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
         all.cols = mv.nb;
         for (int c = tid; c < mv.nb; c += kPipeThreads) pipe_stage_col<XT, XOP>(x, xop, xr, all, xbuf, xscl, c);
     }
-    if (warp >= kGroupWarps - kStageWarps) {
-        const int sw = kGroupWarps - 1 - warp;  // 0 .. kStageWarps - 1
-        if (nt > 0) {
-            const PipeTile t0 = C.tile[0];
-            for (int c = 32 * sw + lane; c < max(t0.cols, t0.rows); c += 32 * kStageWarps) {
-                if (ncc > 1) pipe_stage_col<XT, XOP>(x, xop, xr, t0, xbuf, xscl, c);
-                pipe_stage_row(mv, t0, C, S.xs_tail, 0, c);
-            }
+    if (stager && nt > 0) {
+        const PipeTile t0 = C.tile[0];
+        for (int c = 32 * (kGroupWarps - 1 - warp) + lane; c < max(t0.cols, t0.rows); c += 32 * kStageWarps) {
+            if (ncc > 1) pipe_stage_col<XT, XOP>(x, xop, xr, t0, xbuf, xscl, c);
+            pipe_stage_row(mv, t0, C, S.xs_tail, 0, c);
         }
     }
     {
@@ -847,10 +868,17 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
         // ================= phase 3: fixed-order row sums =================
         for (int lr = warp; lr < tc.rows; lr += kGroupWarps) {
             float s = 0.0f;
-            for (int c = lane; c < tc.cols; c += 32) {
-                unsigned int u;
-                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u) : "r"(items + 8u * (unsigned int)(lr * tc.cols + c)));
-                s += __uint_as_float(u);
+            // four loads in flight, added in column order (the order of a one-by-one loop)
+            for (int c = lane; c < tc.cols; c += 128) {
+                unsigned int u[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    u[k] = 0u;  // an absent column adds +0.0f, which changes nothing: s starts at +0.0f and so is never -0.0f
+                    if (c + 32 * k < tc.cols)
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u[k]) : "r"(items + 8u * (unsigned int)(lr * tc.cols + c + 32 * k)));
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) s += __uint_as_float(u[k]);
             }
             s = warp_sum(s);
             if (lane == 0) {
@@ -913,6 +941,10 @@ inline PipePlan pipe_plan(const TabLayout& L, int smem_optin, int d_out, int nb,
     at += (unsigned int)kPipeGroups * p.slab_bytes;
     p.total = at;
     p.rows_per_cta = (d_out + sm_count - 1) / sm_count;
+    p.tcn = nb > 0 ? (nb + p.ncc - 1) / p.ncc : 1;
+    auto reciprocal = [](int cols) { return cols > 1 ? (unsigned int)((0x100000000ull + cols - 1) / cols) : 0u; };
+    p.mdiv_full = reciprocal(p.tcn);
+    p.mdiv_last = reciprocal(nb - (p.ncc - 1) * p.tcn);
     p.probe = 0;
     p.trace = nullptr;
     return p;
