@@ -472,25 +472,35 @@ __device__ __forceinline__ void pipe_stage_col(const XT* __restrict__ x, const P
     constexpr int kColBytes = XDigits<XT>::kColBytes;
     if (c < t.cols) pipe_prep_column<XT, XOP>(x, (size_t)(t.col0 + c) * kDim, xop, r, xbuf + c * kColBytes, xscl + 4u * c);
 }
+// PARTS: bit 0 = the centroids (the decode phase reads them), bit 1 = row scale and tail product (the row sums do).
+template <int PARTS>
 __device__ __forceinline__ void pipe_stage_row(const MatrixView& mv, const PipeTile& t, PipeCtrl& C, const float* xs_tail, int slot, int c) {
     if (c < t.rows) {
         const int r = t.row0 + c;
-        C.cent[slot][c] = __ldg(mv.cent + r);
-        if (t.last_chunk) {
+        if (PARTS & 1) C.cent[slot][c] = __ldg(mv.cent + r);
+        if ((PARTS & 2) && t.last_chunk) {
             // tail columns in ascending order, one fused multiply-add each: what the reference's
             // tail_dot_h (llvq-cuda/kernels/matvec.cu:329-341) compiles to under NVRTC's default
             // --fmad=true
-            float w[kDim - 1];  // all the row's tail loads are in flight before the first is used
-#pragma unroll
-            for (int k = 0; k < kDim - 1; ++k)
-                w[k] = k >= mv.tail_w ? 0.0f
-                       : mv.tail_f16  ? __half2float(__ldg((const __half*)mv.tail + (size_t)r * mv.tail_w + k))
-                                      : __ldg((const float*)mv.tail + (size_t)r * mv.tail_w + k);
+            const float rs = __ldg(mv.rscale + r);
             float tv = 0.0f;
+            // eight loads in flight at a time: this runs beside the decode phase, where registers are scarcer
+            // than time
 #pragma unroll
-            for (int k = 0; k < kDim - 1; ++k)
-                if (k < mv.tail_w) tv = fmaf(w[k], xs_tail[k], tv);
-            C.rowfix[slot][c] = make_float2(__ldg(mv.rscale + r), tv);
+            for (int k0 = 0; k0 < kDim - 1; k0 += 8) {
+                float w[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int k = k0 + j;
+                    w[j] = k >= mv.tail_w ? 0.0f
+                           : mv.tail_f16  ? __half2float(__ldg((const __half*)mv.tail + (size_t)r * mv.tail_w + k))
+                                          : __ldg((const float*)mv.tail + (size_t)r * mv.tail_w + k);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (k0 + j < mv.tail_w) tv = fmaf(w[j], xs_tail[k0 + j], tv);
+            }
+            C.rowfix[slot][c] = make_float2(rs, tv);
         }
     }
 }
@@ -676,7 +686,7 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
         const PipeTile t0 = C.tile[0];
         for (int c = 32 * (kGroupWarps - 1 - warp) + lane; c < max(t0.cols, t0.rows); c += 32 * kStageWarps) {
             if (ncc > 1) pipe_stage_col<XT, XOP>(x, xop, xr, t0, xbuf, xscl, c);
-            pipe_stage_row(mv, t0, C, S.xs_tail, 0, c);
+            pipe_stage_row<1>(mv, t0, C, S.xs_tail, 0, c);  // row scale and tail product follow under the decode phase
         }
     }
     {
@@ -795,13 +805,17 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
             const PipeTile tn = C.tile[(i + 1) & 1];
             pipe_issue_slab(mv.codes, tn, mv.nb, slab, bar_slab, lane);
         }
-        // ... and its digits and row data are staged by a few warps before they join the decoding
+        // ... and a few warps stage row data before they join the decoding: this tile's row scales and tail
+        // products, which only the row sums below need, then the next tile's digits and centroids
+        if (warp >= kGroupWarps - kStageWarps)
+            for (int c = 32 * (kGroupWarps - 1 - warp) + lane; c < tc.rows; c += 32 * kStageWarps)
+                pipe_stage_row<2>(mv, tc, C, S.xs_tail, i & 1, c);
         if (has_next && warp >= kGroupWarps - kStageWarps) {
             const PipeTile tn = C.tile[(i + 1) & 1];
             const unsigned int xo = ncc > 1 ? (unsigned int)((i + 1) & 1) * xbuf_bytes : 0u;
             for (int c = 32 * (kGroupWarps - 1 - warp) + lane; c < max(tn.cols, tn.rows); c += 32 * kStageWarps) {
                 if (ncc > 1) pipe_stage_col<XT, XOP>(x, xop, xr, tn, xbuf + xo, xscl + xo, c);
-                pipe_stage_row(mv, tn, C, S.xs_tail, (i + 1) & 1, c);
+                pipe_stage_row<1>(mv, tn, C, S.xs_tail, (i + 1) & 1, c);
             }
         }
         {
