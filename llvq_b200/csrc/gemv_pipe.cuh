@@ -14,10 +14,11 @@
 //              mbarrier, started while the previous tile was being decoded). Every
 //              warp takes 32 blocks at a time: 48-bit record -> class -> family, an
 //              8-byte item at the block's own slot, the slot appended to its family's
-//              list (ballots + one shared-memory atomic per family and warp). A few
-//              warps first turn the tile's activation columns into fixed-point digits
-//              and stage its rows' centroids, row scales and tail-column products.
-//   decode     warps draw batches of 32 same-family items, longest family first,
+//              list (ballots + one shared-memory atomic per family and warp).
+//   decode     a few warps first form this tile's row scales and tail-column products
+//              (only the row sums read them) and stage the next tile's centroids and,
+//              for rows cut into column chunks, its activation digits. Then all warps
+//              draw batches of 32 same-family items, longest family first,
 //              run that family's branch-free decoder (decode_tab.cuh) and dot the 24
 //              signed bytes against the activation digits with dp4a; the scaled block
 //              sum replaces the item.
@@ -31,8 +32,11 @@
 // and independent of the order of evaluation.
 //
 // The kernel is launched with programmatic stream serialisation: it lets the next
-// launch of the stream start as soon as its own tables are on their way, and waits
-// for the previous launch only before it first touches the activation.
+// launch of the stream start at once, and itself waits for the previous launch only
+// before it first touches the activation: table copies, tile layout, the first code
+// slab and a prefetch of the first rows' data all come before that wait. The
+// activation may also be formed in the staging step from the tensors an elementwise
+// step would have read (PipeXOp: RMSNorm of residual + delta, or silu(gate) * up).
 #pragma once
 #include <cuda_fp16.h>
 
