@@ -96,6 +96,7 @@ struct PipePlan {
     int cols_max, ncc;        // columns per chunk, column chunks (two digit buffers when ncc > 1)
     int rows_per_cta;
     int tcn;                  // columns of a full chunk
+    int fit;                  // rows of a tile (as many as the tile memory holds, at most kTileRowsMax)
     unsigned int mdiv_full, mdiv_last;  // PipeTile::mdiv of a full chunk and of the last chunk
     int probe;                // attribution probes: bit 0 = leave the decoders out, bit 1 = leave the class search out
     unsigned long long* trace;  // per CTA kTraceEvents time stamps (ns), or null
@@ -580,7 +581,7 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
     const int grp_nr = max(0, min(rpg, cta_r0 + cta_nr - grp_r0));
     const int ncc = plan.ncc;
     const int tcn = plan.tcn;
-    const int fit = max(1, min(kTileRowsMax, tile_max / tcn));
+    const int fit = plan.fit;
     const int nrg = (grp_nr + fit - 1) / fit;
     const int nt = grp_nr > 0 ? nrg * ncc : 0;
     // activation digits: buffers of cols_max columns (digits, then one float per column). A matrix with a single
@@ -600,8 +601,9 @@ llvq_gemv_pipe_kernel(const unsigned char* __restrict__ blob_g, const OffEntry* 
     // leaves it, and this launch comes as far as griddepcontrol.wait below while the previous one is still running.
     // Nothing before that wait reads what a previous kernel writes (tables and codes are constant).
     asm volatile("griddepcontrol.launch_dependents;");
-    if (warp == 0) {
-        // the group's first warp lays out the tiles and starts the first code slab on its own
+    if (warp == 1) {
+        // the group's second warp lays out the tiles and starts the first code slab on its own (thread 0 of the
+        // CTA, in the first warp, is busy issuing the table copies)
         if (lane < 4) C.list_lut[lane] = pipe_list_geom(lists, tile_max, (unsigned int)lane);
         if (lane == 0) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_slab));
@@ -961,6 +963,7 @@ inline PipePlan pipe_plan(const TabLayout& L, int smem_optin, int d_out, int nb,
     p.rows_per_cta = (d_out + sm_count - 1) / sm_count;
     p.tcn = nb > 0 ? (nb + p.ncc - 1) / p.ncc : 1;
     auto reciprocal = [](int cols) { return cols > 1 ? (unsigned int)((0x100000000ull + cols - 1) / cols) : 0u; };
+    p.fit = p.tile_max / p.tcn < 1 ? 1 : p.tile_max / p.tcn > kTileRowsMax ? kTileRowsMax : p.tile_max / p.tcn;
     p.mdiv_full = reciprocal(p.tcn);
     p.mdiv_last = reciprocal(nb - (p.ncc - 1) * p.tcn);
     p.probe = 0;
