@@ -766,6 +766,8 @@ def main():
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="--tp / --tp-decode: all-gathers of the row shards through peer memory (llvq_tp_exchange) or NCCL")
     ap.add_argument("--no-graph", action="store_true", help="--tp-decode: launch every token step eagerly")
+    ap.add_argument("--pass-eager", action="store_true",
+                    help="the GEMV pass as one library call per projection from Python instead of a replayed CUDA graph")
     ap.add_argument("--prompt", type=int, default=32768)
     ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--gpus", type=int, default=1)
@@ -875,16 +877,28 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    # the pass is replayed from a captured CUDA graph, as the decode loop replays its token step (--pass-eager:
+    # one library call per projection from Python instead); the launches of a replay are those of its capture
+    step_timed, launches_per_step = step_device, None
+    if not args.pass_eager:
+        step_device()
+        torch.cuda.synchronize()
+        launches0 = lib.llvq_launch_count()
+        pass_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(pass_graph):
+            step_device()
+        launches_per_step = lib.llvq_launch_count() - launches0
+        step_timed = pass_graph.replay
     t_warm, n_warm = time.perf_counter(), 0
     while n_warm < max(args.warmup, 3) or time.perf_counter() - t_warm < 0.6:
-        step_device()
+        step_timed()
         n_warm += 1
         if n_warm % 8 == 0:
             torch.cuda.synchronize()
     torch.cuda.synchronize()
     launches0 = lib.llvq_launch_count()
-    ms_total = timed(step_device, args.steps)
-    launches = lib.llvq_launch_count() - launches0
+    ms_total = timed(step_timed, args.steps)
+    launches = lib.llvq_launch_count() - launches0 if launches_per_step is None else launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
     assert not rt.poll_range_error(), "a synthetic index fell outside the ball"
 
@@ -925,6 +939,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": "qwen3-4b-layer-gemv", "layers_per_step": args.layers, "projections_per_step": 7 * args.layers,
                    "launches_per_step": projs_n, "grouping": "none" if args.no_groups else "q|k|v, o, gate|up, down",
+                   "launched_as": "one library call per projection" if args.pass_eager else "a captured CUDA graph of the pass, replayed per step",
                    "blocks_per_step": step_blocks, "algorithmic_bytes_per_step": step_bytes, "activations": "f16",
                    "l2": "every step streams %.0f MB of distinct codes (> 126 MB L2)" % (codes_bytes / 1e6),
                    "parallelism": f"replicas x{world}" if world > 1 else "single"},
