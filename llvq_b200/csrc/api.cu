@@ -68,7 +68,7 @@ struct DeviceGuard {
 };
 
 constexpr int kLutShift = 35;
-constexpr int kManySegments = 4;  // result segments of llvq_gemv_h_host_many
+constexpr int kManySegments = 8;  // segments of llvq_gemv_h_host_many (activations up, results back)
 
 // Launch with programmatic stream serialisation (see llvq_runtime_set_overlap): the kernel may be scheduled
 // while the previous kernel of the stream is still running; it orders itself behind that kernel with
@@ -133,8 +133,9 @@ struct llvq_runtime {
     int overlap_launches = 1;      // GEMV launches carry the programmatic-serialisation attribute
     // staging of llvq_gemv_h_host_many: one pinned host buffer and its device twin, grown on demand
     std::mutex many_mu;
-    cudaStream_t many_stream = nullptr;   // copy stream of llvq_gemv_h_host_many and its per-segment events
-    cudaEvent_t many_ready[4] = {nullptr, nullptr, nullptr, nullptr}, many_done[4] = {nullptr, nullptr, nullptr, nullptr};
+    cudaStream_t many_stream = nullptr;   // copy streams of llvq_gemv_h_host_many (results back, activations up)
+    cudaStream_t many_up = nullptr;       // and their per-segment events
+    cudaEvent_t many_ready[kManySegments] = {}, many_done[kManySegments] = {}, many_in[kManySegments] = {};
     unsigned char* many_host = nullptr;
     unsigned char* many_dev = nullptr;
     size_t many_bytes = 0;
@@ -431,9 +432,11 @@ void llvq_runtime_destroy(llvq_runtime* rt) {
     if (rt->many_stream) {
         for (int k = 0; k < kManySegments; ++k) {
             cudaEventDestroy(rt->many_ready[k]);
+            cudaEventDestroy(rt->many_in[k]);
             cudaEventDestroy(rt->many_done[k]);
         }
         cudaStreamDestroy(rt->many_stream);
+        cudaStreamDestroy(rt->many_up);
     }
     cudaFree(rt->d_tab_blob);
     cudaFree(rt->d_tab_off);
@@ -1310,11 +1313,13 @@ int llvq_gemv_h_host_many(const llvq_host_call* calls, int32_t n, llvq_stream_t 
             return fail(LLVQ_ERR_INVALID, "gemv_h_host_many: call %d has a null field or another runtime", i);
     DeviceGuard g(calls[0].m->rt->device);
     cudaStream_t s = (cudaStream_t)stream;
-    // One pinned host buffer and one device buffer of the runtime carry the whole list: the activations are
-    // packed on the host and go up in ONE copy, the GEMVs run launch behind launch (each one's prologue
-    // overlapping the previous one's tail), the results come back in ONE copy and are scattered on the host.
-    // (A copy per call costs about 2 us of stream time each way; a 252-projection token would spend more time in
-    // copies than in a fifth of its kernels.) The buffers grow on demand; calls on one runtime take turns.
+    // One pinned host buffer and one device buffer of the runtime carry the whole list. The list is cut into a few
+    // segments: a segment's activations are packed on the host and go up in one copy on an upload stream while the
+    // segment before it computes, its GEMVs run launch behind launch (each one's prologue overlapping the previous
+    // one's tail), its results come back in one copy on a second copy stream while the next segment computes, and the
+    // host scatters them as soon as they have landed. (A copy per call costs about 2 us of stream time each way; a
+    // 252-projection token would spend more time in copies than in a fifth of its kernels.) The buffers grow on
+    // demand; calls on one runtime take turns.
     llvq_runtime* rt = calls[0].m->rt;
     std::lock_guard<std::mutex> lock(rt->many_mu);
     std::vector<size_t> xo(n), yo(n);
@@ -1339,22 +1344,33 @@ int llvq_gemv_h_host_many(const llvq_host_call* calls, int32_t n, llvq_stream_t 
         CUDA_TRY(cudaMalloc((void**)&rt->many_dev, at));
         rt->many_bytes = at;
     }
-    for (int i = 0; i < n; ++i) std::memcpy(rt->many_host + xo[i], calls[i].x_host, (size_t)calls[i].m->d_in * sizeof(__half));
-    CUDA_TRY(cudaMemcpyAsync(rt->many_dev, rt->many_host, x_bytes, cudaMemcpyHostToDevice, s));
-    // The results come back in a few segments on a copy stream of the runtime: a segment's copy waits (event) for
-    // its last launch and runs while the next segment computes, and the host scatters a segment as soon as its
-    // copy has landed. Only the last segment's copy and scatter are left after the last kernel.
     if (!rt->many_stream) {
         CUDA_TRY(cudaStreamCreateWithFlags(&rt->many_stream, cudaStreamNonBlocking));
+        CUDA_TRY(cudaStreamCreateWithFlags(&rt->many_up, cudaStreamNonBlocking));
         for (int k = 0; k < kManySegments; ++k) {
             CUDA_TRY(cudaEventCreateWithFlags(&rt->many_ready[k], cudaEventDisableTiming));
+            CUDA_TRY(cudaEventCreateWithFlags(&rt->many_in[k], cudaEventDisableTiming));
             CUDA_TRY(cudaEventCreateWithFlags(&rt->many_done[k], cudaEventDisableTiming));
         }
     }
     const int segs = n < kManySegments ? n : kManySegments;
     int first[kManySegments + 1];
-    for (int k = 0; k <= segs; ++k) first[k] = (int)((long long)n * k / segs);
+    // short segments at both ends: what stands before the first kernel (one pack and copy) and behind the last one
+    // (one copy and scatter) is a thirty-second of the list
+    static const int kCut32[kManySegments + 1] = {0, 1, 4, 8, 16, 24, 28, 31, 32};
+    for (int k = 0; k <= segs; ++k)  // both forms increase strictly: no empty segment
+        first[k] = n >= 64 ? (int)((long long)n * kCut32[k] / 32) : (int)((long long)n * k / segs);
+    // the staging buffers may still be read or written by what the caller's stream holds (an earlier call's kernels)
+    CUDA_TRY(cudaEventRecord(rt->many_ready[0], s));
+    CUDA_TRY(cudaStreamWaitEvent(rt->many_up, rt->many_ready[0], 0));
     for (int k = 0; k < segs; ++k) {
+        // only the first segment's pack and copy stand before the first kernel
+        for (int i = first[k]; i < first[k + 1]; ++i)
+            std::memcpy(rt->many_host + xo[i], calls[i].x_host, (size_t)calls[i].m->d_in * sizeof(__half));
+        const size_t xlo = xo[first[k]], xhi = first[k + 1] < n ? xo[first[k + 1]] : x_bytes;
+        CUDA_TRY(cudaMemcpyAsync(rt->many_dev + xlo, rt->many_host + xlo, xhi - xlo, cudaMemcpyHostToDevice, rt->many_up));
+        CUDA_TRY(cudaEventRecord(rt->many_in[k], rt->many_up));
+        CUDA_TRY(cudaStreamWaitEvent(s, rt->many_in[k], 0));
         for (int i = first[k]; i < first[k + 1]; ++i) {
             int st = launch_gemv<__half, __half>(calls[i].m, (const __half*)(rt->many_dev + xo[i]), (__half*)(rt->many_dev + yo[i]), s);
             if (st) return st;

@@ -236,11 +236,22 @@ def test_host_buffer_list_entry_point(rt, oracle):
     xs = [synth.make_activation(m.d_in, 70 + i, np.float16) for i, m in enumerate(ms)]
     ys = [np.full(m.d_out, np.nan, np.float16) for m in ms]
     rt.forward_host_many(projs, xs, ys)
+    singles = []
     for m, p, x, y in zip(ms, projs, xs, ys):
         single = np.empty(m.d_out, np.float16)
         rt.forward_host(p, x, single)
         assert np.array_equal(y, single)
+        singles.append(single)
     rt.forward_host_many([], [], [])
+    # the list travels in up to eight segments (short ones at both ends from 64 calls on): every length around the
+    # switches gives every call its own result, twice in a row on the same staging buffers
+    for n in (1, 2, 7, 8, 9, 31, 63, 64, 65, 100, 257):
+        order = [(7 * i + n) % 3 for i in range(n)]
+        ys_n = [np.full(ms[k].d_out, np.nan, np.float16) for k in order]
+        for _ in range(2):
+            rt.forward_host_many([projs[k] for k in order], [xs[k] for k in order], ys_n)
+            for k, y in zip(order, ys_n):
+                assert np.array_equal(y, singles[k]), (n, k)
 
 
 def test_index_outside_the_ball_raises_the_range_flag(rt, oracle):
