@@ -190,12 +190,13 @@ int llvq_gemv_h_host(llvq_matrix* m, const uint16_t* x_host, uint16_t* y_host, l
 /* A whole list of host-buffer GEMVs (f16 in, f16 out) enqueued back to back with ONE
  * synchronisation at the end: what a layer or a token is for a plugin that holds host
  * tensors. The reference's loop also issues every launch of a token and synchronises once,
- * at the argmax read-back (llvq-llm/src/model.rs:1058-1072). The activations are packed into a
- * pinned buffer of the runtime and go up in one copy, the GEMVs run launch behind launch, the
- * results come back in four segments on a copy stream of the runtime (a segment's copy and its
- * scatter into y_host overlap the next segment's kernels) before the call returns (the buffers
- * are sized by the first call and grow on demand; calls on one runtime take turns). The
- * calls of a list are independent: no call reads another call's result. */
+ * at the argmax read-back (llvq-llm/src/model.rs:1058-1072). The list is served in up to eight
+ * segments (short ones at both ends): a segment's activations are packed into a pinned buffer
+ * of the runtime and go up in one copy on an upload stream while the segment before computes,
+ * its GEMVs run launch behind launch, and its results come back in one copy on a second copy
+ * stream and are scattered into y_host while the next segment computes, before the call returns
+ * (the buffers are sized by the first call and grow on demand; calls on one runtime take turns).
+ * The calls of a list are independent: no call reads another call's result. */
 typedef struct llvq_host_call {
     llvq_matrix* m;
     const uint16_t* x_host; /* d_in halves */
